@@ -1,0 +1,238 @@
+/* C ABI of the B200 prover core (libzkllm_b200.so).
+ *
+ * The reference implementation has no FFI layer: its operator surface is the set
+ * of C++ classes in its .cuh headers.  Each entry point below replaces the device
+ * work behind one of those methods; the comment in front of it names the method
+ * (file:line within the reference project).  The C++ classes of the same names
+ * in zkllm-ccs2024_b200/host/ forward to these calls.
+ *
+ * Conventions
+ *  - Every function returns ZKB_OK (0) or a negative ZKB_ERR_* code;
+ *    zkb_last_error() gives the text for the calling thread.  No exception
+ *    crosses this boundary.
+ *  - Pointers named d_* are device addresses, h_* are host addresses.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *    stream).  Calls that return values through h_* pointers synchronise the
+ *    stream before returning; all others are asynchronous on `stream`.
+ *  - Fr elements are 8 little-endian u32 limbs in STANDARD (non-Montgomery)
+ *    form, canonical in [0, r), 32 bytes, 16-byte aligned — the reference's
+ *    Fr_t / FrTensor layout (bls12-381.cuh:116-120).
+ *  - G1 points are Jacobian (X, Y, Z) triples of 12-limb Fq values in MONTGOMERY
+ *    form, 144 bytes; Z == 0 is the identity — the reference's G1Jacobian_t /
+ *    G1TensorJacobian layout (bls12-381.cuh:429-433).  Affine points are 96
+ *    bytes (X, Y).
+ *  - Challenge vectors are host arrays of Fr in standard form, in the order the
+ *    reference's functions take them.
+ */
+#ifndef ZKLLM_B200_H
+#define ZKLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZKB_OK            0
+#define ZKB_ERR_CUDA     (-1)  /* a CUDA call failed                                   */
+#define ZKB_ERR_DIM      (-2)  /* incompatible dimensions (reference: runtime_error)   */
+#define ZKB_ERR_VERIFY   (-3)  /* a verifier equation failed (reference: runtime_error) */
+#define ZKB_ERR_ARG      (-4)  /* invalid argument                                     */
+#define ZKB_ERR_LIMIT    (-5)  /* size beyond a documented limit                       */
+
+typedef struct { uint32_t val[8]; }  zkb_fr_t;        /* Fr_t          */
+typedef struct { uint32_t val[12]; } zkb_fq_t;        /* Fp_t          */
+typedef struct { zkb_fq_t x, y; }    zkb_g1_affine_t; /* G1Affine_t    */
+typedef struct { zkb_fq_t x, y, z; } zkb_g1_t;        /* G1Jacobian_t  */
+
+/* ---- library ---------------------------------------------------------------- */
+const char* zkb_last_error(void);
+int zkb_version(void);
+/* Number of kernels this library has launched in the calling process. */
+unsigned long long zkb_launch_count(void);
+
+/* ---- device memory (FrTensor/G1Tensor ctors, dtors, copies:
+ *      fr-tensor.cu:158-179, g1-tensor.cu:40-60,123-152) ------------------------- */
+int zkb_malloc(void** d_ptr, size_t bytes);
+int zkb_free(void* d_ptr);
+int zkb_memcpy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
+int zkb_memcpy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
+int zkb_memcpy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);
+int zkb_memset0(void* d_dst, size_t bytes, void* stream);
+int zkb_sync(void* stream);
+
+/* ---- fixed-point <-> Fr (fr-tensor.cu:186-236, 713-798) ------------------------ */
+int zkb_fr_from_i32(const int32_t* d_in, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_from_i64(const int64_t* d_in, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_to_i32(const zkb_fr_t* d_in, int32_t* d_out, size_t n, void* stream);
+int zkb_fr_to_i64(const zkb_fr_t* d_in, int64_t* d_out, size_t n, void* stream);
+int zkb_fr_from_f32(const float* d_in, uint64_t scale, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_from_f64(const double* d_in, uint64_t scale, zkb_fr_t* d_out, size_t n, void* stream);
+
+/* ---- elementwise field ops (FrTensor operators, fr-tensor.cu:257-373).
+ *      d_out may alias an input.  The *_scalar forms broadcast one host value. ---- */
+int zkb_fr_add(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_sub(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_mul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_neg(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_add_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_sub_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_mul_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream);
+/* FrTensor::mont / unmont (fr-tensor.cu:323-337): multiply by 2^256 / 2^-256 mod r */
+int zkb_fr_mont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream);
+int zkb_fr_unmont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream);
+/* Fr_elementwise_mont_mul (fr-tensor.cu:126): a*b*2^-256 mod r */
+int zkb_fr_mont_mul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_out, size_t n, void* stream);
+/* 1/(a + beta), zero mapped to zero (tlookup_inv_kernel, tlookup.cu:50-62) */
+int zkb_fr_inv_shifted(const zkb_fr_t* d_a, const zkb_fr_t* h_beta, zkb_fr_t* d_out, size_t n, void* stream);
+
+/* ---- reductions and multilinear folds ------------------------------------------ */
+/* FrTensor::sum (fr-tensor.cu:406-434) */
+int zkb_fr_sum(const zkb_fr_t* d_a, size_t n, zkb_fr_t* h_out, void* stream);
+/* FrTensor::operator()(u) (fr-tensor.cu:437-442): multilinear extension at u, u[0]
+ * binding the least-significant index bit; needs 2^(k-1) < n <= 2^k. */
+int zkb_fr_mle_eval(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                    zkb_fr_t* h_out, void* stream);
+/* FrTensor::partial_me(u, cur_dim, window_size) (fr-tensor.cu:518-560): the tensor
+ * is [n/(cur_dim*window), cur_dim, window]; the middle axis is folded away with u.
+ * d_out receives n/cur_dim elements. */
+int zkb_fr_partial_me(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                      size_t cur_dim, size_t window, zkb_fr_t* d_out, void* stream);
+/* FrTensor::partial_me(u, window_size) (fr-tensor.cu:512-516, 612-641): folds
+ * consecutive windows pairwise k times; d_out receives
+ * window * ceil(ceil(n/window) / 2^k) elements (*out_n is set to that count). */
+int zkb_fr_partial_me_window(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                             size_t window, zkb_fr_t* d_out, size_t* out_n, void* stream);
+/* FrTensor::multi_dim_me (fr-tensor.cu:643-652) for a [d0, d1] tensor:
+ * folds axis 1 with u1 (k1 values) and then axis 0 with u0 (k0 values). */
+int zkb_fr_mle_eval_2d(const zkb_fr_t* d_a, size_t d0, size_t d1,
+                       const zkb_fr_t* h_u0, unsigned k0, const zkb_fr_t* h_u1, unsigned k1,
+                       zkb_fr_t* h_out, void* stream);
+
+/* ---- layout (fr-tensor.cu:800-828, 885-900) -------------------------------------- */
+/* one level of FrTensor::pad: [rows, last] -> [rows, last_padded] filled with pad_val */
+int zkb_fr_pad_last(const zkb_fr_t* d_a, size_t rows, size_t last, size_t last_padded,
+                    const zkb_fr_t* h_pad_val, zkb_fr_t* d_out, void* stream);
+int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, void* stream);
+/* FrTensor::matmul / zkFC::operator() (fr-tensor.cu:831-881, zkfc.cu:44-58):
+ * C[M,P] = A[M,N] * B[N,P] over Fr */
+int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c,
+                  size_t M, size_t N, size_t P, void* stream);
+/* fcAddBiasKernel (zkfc.cu:36-41) */
+int zkb_fr_add_bias(zkb_fr_t* d_z, const zkb_fr_t* d_bias, size_t rows, size_t cols, void* stream);
+
+/* ---- sumchecks -------------------------------------------------------------------- */
+/* zkip (zkfc.cu:94-151): inner-product sumcheck of two length-n vectors, pairing
+ * (i, i + N/2) and consuming h_u from the back.  h_polys receives 3 coefficients
+ * per round (k rounds, round 0 first); *h_final is the returned claim.  Returns
+ * ZKB_ERR_VERIFY when a round fails claim == p(0) + p(1) ("claim != p(0) + p(1)").
+ * The inputs are not modified. */
+int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+             const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* Body of zkFC::prove (zkfc.cu:61-87) with the challenge vectors passed in
+ * (the reference draws them from random_vec).  X is [B, I], W is [I, O], Y is
+ * [B, O].  Outputs: h_polys (3 * ceilLog2(I) coefficients), h_claims[4] =
+ * {claim (Y at (u_batch,u_output)), final_claim, claim_X, claim_W}.
+ * ZKB_ERR_VERIFY when claim_X*claim_W != final_claim ("Claim does not match"). */
+int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y,
+                   size_t B, size_t I, size_t O,
+                   const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
+                   zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream);
+/* tLookup::prep (tlookup.cu:23-48): multiplicities of `indices` in a table of N */
+int zkb_tlookup_prep(const uint32_t* d_indices, size_t D, size_t N, zkb_fr_t* d_m, void* stream);
+/* tLookupRange::prep(FrTensor) (tlookup.cu:414-433): index = low limb of (v - low) */
+int zkb_tlookup_range_indices(const zkb_fr_t* d_vals, int32_t low, uint32_t* d_indices, size_t D, void* stream);
+/* tLookupRange ctor (tlookup.cu:372-391): table of `table_size` (a power of two)
+ * entries low, low+1, ..., repeating the last of the first `len` */
+int zkb_tlookup_range_table(int32_t low, size_t len, size_t table_size, zkb_fr_t* d_table, void* stream);
+/* lookuprangemapping_kernel (tlookup.cu:446-453): out[i] = vals[indices[i]] */
+int zkb_fr_gather(const uint32_t* d_indices, const zkb_fr_t* d_vals, zkb_fr_t* d_out, size_t D, void* stream);
+/* tLookup::prove (tlookup.cu:324-370 with phases :184-320).  S has D elements,
+ * table and m have N; D and N powers of two, N | D; u and v have log2(D)
+ * values.  h_polys receives 4 coefficients per round (log2 D rounds; the
+ * reference computes these and drops them); *h_final is the returned claim.
+ * ZKB_ERR_VERIFY: "tLookup_phase1: claim != p(0) + p(1)" / "tLookup_phase2: ...". */
+int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
+                      size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                      const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                      zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* multi_hadamard_sumchecks (proof.cu:190-241): K tensors of N (a power of two)
+ * elements; h_polys receives (K+1) coefficients per round, log2 N rounds. */
+int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,
+                       const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                       zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* hadamard_product_sumcheck / inner_product_sumcheck / binary_sumcheck
+ * (proof.cu:12-160), including the factor 2^-256 the reference leaves on the
+ * product terms.  h_proof receives 3*k + 2 (3*k + 1 for binary) elements. */
+int zkb_hadamard_product_sumcheck(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+                                  const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned k,
+                                  zkb_fr_t* h_proof, void* stream);
+int zkb_inner_product_sumcheck(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+                               const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_proof, void* stream);
+int zkb_binary_sumcheck(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                        unsigned k, zkb_fr_t* h_proof, void* stream);
+
+/* ---- Rescaling / softmax element kernels ------------------------------------------ */
+/* rescaling_kernel (rescaling.cu:8-21): out = round-to-nearest x / sf, rem = x - out*sf
+ * in [-sf/2, sf/2) */
+int zkb_rescale(const zkb_fr_t* d_in, uint64_t scaling_factor, zkb_fr_t* d_out, zkb_fr_t* d_rem,
+                size_t n, void* stream);
+/* zksoftmax_calculate_table (zksoftmax.cu:4-16) */
+int zkb_softmax_table(double theta_k, double scaling_factor_in, double d, double Bk, uint32_t bk,
+                      zkb_fr_t* d_table, void* stream);
+/* zksoftmax_shift (zksoftmax.cu:20-32): per row shift = round(sf*sqrt(d)*ln(sum exp(x/(sf*sqrt(d)))))
+ * with the row sum taken left to right in double precision; out = A - shift */
+int zkb_softmax_shift(const zkb_fr_t* d_A, zkb_fr_t* d_shift, zkb_fr_t* d_out, size_t rows, size_t cols,
+                      double scaling_factor_in, double d, void* stream);
+/* zksoftmax_decompose_kernel (zksoftmax.cu:95-109): mixed-radix digits of -X,
+ * digit i of element g stored at d_out[i*N + g] */
+int zkb_softmax_decompose(const zkb_fr_t* d_X, const uint32_t* h_bs, unsigned K, zkb_fr_t* d_out,
+                          size_t N, void* stream);
+
+/* ---- G1 tensors (g1-tensor.cu) ----------------------------------------------------- */
+int zkb_g1_fill(zkb_g1_t* d_out, const zkb_g1_t* h_val, size_t n, void* stream);
+int zkb_g1_neg(const zkb_g1_t* d_a, zkb_g1_t* d_out, size_t n, void* stream);
+int zkb_g1_add(const zkb_g1_t* d_a, const zkb_g1_t* d_b, zkb_g1_t* d_out, size_t n, void* stream);
+int zkb_g1_sub(const zkb_g1_t* d_a, const zkb_g1_t* d_b, zkb_g1_t* d_out, size_t n, void* stream);
+int zkb_g1_add_scalar(const zkb_g1_t* d_a, const zkb_g1_t* h_x, zkb_g1_t* d_out, size_t n, void* stream);
+int zkb_g1_from_affine(const zkb_g1_affine_t* d_a, zkb_g1_t* d_out, size_t n, void* stream);
+/* Jacobian -> affine (X/Z^2, Y/Z^3), identity -> (0,0).  Not in the reference:
+ * this is the normal form on which G1 results are compared. */
+int zkb_g1_to_affine(const zkb_g1_t* d_a, zkb_g1_affine_t* d_out, size_t n, void* stream);
+/* G1TensorJacobian::operator*(FrTensor) (g1-tensor.cu:445-480): out[i] = scalars[i] * g[i mod n_g] */
+int zkb_g1_mul(const zkb_g1_t* d_g, size_t n_g, const zkb_fr_t* d_scalars, size_t n, zkb_g1_t* d_out, void* stream);
+/* G1TensorJacobian::sum (g1-tensor.cu:391-443) */
+int zkb_g1_sum(const zkb_g1_t* d_a, size_t n, zkb_g1_t* h_out, void* stream);
+/* G1TensorJacobian::rowwise_sum (g1-tensor.cu:535-625) */
+int zkb_g1_rowwise_sum(const zkb_g1_t* d_a, size_t rows, size_t cols, zkb_g1_t* d_out, void* stream);
+/* G1TensorJacobian::operator()(u) (g1-tensor.cu:486-514).  The reference passes u
+ * through an un-Montgomery step first (g1-tensor.cu:491); reproduced. */
+int zkb_g1_mle_eval(const zkb_g1_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k, zkb_g1_t* h_out, void* stream);
+
+/* ---- commitment (commitment.cu) ----------------------------------------------------- */
+/* Commitment::commit_int (commitment.cu:31-58): m = n_scalars / n_gen row
+ * commitments; scalars are Fr encodings of int32 values. */
+int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
+                   zkb_g1_t* d_out, void* stream);
+/* Same with the scalars given directly as int32 (the weight .bin format,
+ * fileio_utils.py:4-12): skips the 8x larger Fr encoding. */
+int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
+                   zkb_g1_t* d_out, void* stream);
+/* Host-buffer form of the same call: copies generators and int32 scalars in,
+ * commits, copies the m Jacobian results out. */
+int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_scalars, size_t n_scalars,
+                        zkb_g1_t* h_out, void* stream);
+/* Commitment::commit (commitment.cu:22-29): full-width scalars */
+int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
+               zkb_g1_t* d_out, void* stream);
+/* Commitment::me_open (commitment.cu:79-129): t and generators have n elements,
+ * k challenges.  h_proof receives 3*k + 1 Jacobian points (the reference builds
+ * this vector and drops it); *h_out is the opening. */
+int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
+                zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKLLM_B200_H */

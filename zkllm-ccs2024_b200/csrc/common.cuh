@@ -1,0 +1,75 @@
+// Shared host-side plumbing for the C-ABI translation units: status codes,
+// error text, launch checking and the stream-ordered scratch pool.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <atomic>
+#include <cstdio>
+#include <string>
+
+#include "../../include/zkllm_b200.h"
+
+namespace zkb {
+
+// Thread-local text of the last failure, returned by zkb_last_error().
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define ZKB_CUDA(call)                                                    \
+    do {                                                                  \
+        cudaError_t e__ = (call);                                         \
+        if (e__ != cudaSuccess) return ::zkb::cuda_fail(e__, #call);      \
+    } while (0)
+
+#define ZKB_LAUNCH_CHECK(name)                                            \
+    do {                                                                  \
+        cudaError_t e__ = cudaGetLastError();                             \
+        if (e__ != cudaSuccess) return ::zkb::cuda_fail(e__, name);       \
+    } while (0)
+
+#define ZKB_TRY(expr)                                                     \
+    do {                                                                  \
+        int rc__ = (expr);                                                \
+        if (rc__ != ZKB_OK) return rc__;                                  \
+    } while (0)
+
+// Count of kernels launched by this library in this process (zkb_launch_count()).
+extern std::atomic<unsigned long long> g_launches;
+
+// Launch + count + check.  Usage: ZKB_LAUNCH(kernel, grid, block, smem, stream, args...)
+#define ZKB_LAUNCH(kernel, grid, block, smem, stream, ...)                \
+    do {                                                                  \
+        kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);       \
+        ::zkb::g_launches.fetch_add(1, std::memory_order_relaxed);        \
+        ZKB_LAUNCH_CHECK(#kernel);                                        \
+    } while (0)
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Scratch memory that lives for one entry-point call.  Blocks come from the
+// device's stream-ordered pool (cudaMallocAsync), so a call neither blocks the
+// device nor pays a cudaMalloc; every block is released in the destructor in
+// stream order.
+class Scratch {
+public:
+    explicit Scratch(cudaStream_t s) : stream_(s) {}
+    ~Scratch();
+    Scratch(const Scratch&) = delete;
+    Scratch& operator=(const Scratch&) = delete;
+    // returns nullptr and records the error on failure
+    void* get(size_t bytes);
+    template <class T> T* get_n(size_t n) { return static_cast<T*>(get(n * sizeof(T))); }
+private:
+    static constexpr int kMax = 256;
+    cudaStream_t stream_;
+    void* blocks_[kMax];
+    int n_ = 0;
+};
+
+inline unsigned div_up(size_t a, size_t b) { return (unsigned)((a + b - 1) / b); }
+
+}  // namespace zkb

@@ -1,0 +1,640 @@
+// FrTensor device work: conversions, elementwise field ops, sums, multilinear
+// folds expressed as dot products with eq-tables, layout utilities, matmul.
+//
+// All tensors hold standard-form values.  Products against a challenge use the
+// challenge in Montgomery form (montmul(x, u*R) = x*u), products of two tensor
+// values are corrected by one multiplication with R^2 per output.
+#include "frutil.cuh"
+#include "hostfr.hpp"
+
+#include <vector>
+
+namespace zkb {
+
+static constexpr unsigned kThreads = 256;
+
+// ---------------------------------------------------------------------------
+// elementwise
+// ---------------------------------------------------------------------------
+enum class BinOp { Add, Sub, Mul, MontMul };
+enum class UnOp { Neg, Mont, Unmont };
+
+template <BinOp OP>
+__global__ void __launch_bounds__(kThreads) fr_binary_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b,
+                                                              Fr* __restrict__ out, size_t n) {
+    const Fr r2 = fe_r2<FrP>();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        Fr x = fr_load(a + i), y = fr_load(b + i), z;
+        if (OP == BinOp::Add) z = fr_add(x, y);
+        else if (OP == BinOp::Sub) z = fr_sub(x, y);
+        else if (OP == BinOp::Mul) z = fr_mmul(fr_mmul(x, y), r2);
+        else z = fr_mmul(x, y);
+        fr_store(out + i, z);
+    }
+}
+
+// y is the broadcast operand; for Mul it arrives already in Montgomery form
+template <BinOp OP>
+__global__ void __launch_bounds__(kThreads) fr_scalar_kernel(const Fr* __restrict__ a, Fr y, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        Fr x = fr_load(a + i), z;
+        if (OP == BinOp::Add) z = fr_add(x, y);
+        else if (OP == BinOp::Sub) z = fr_sub(x, y);
+        else z = fr_mmul(x, y);
+        fr_store(out + i, z);
+    }
+}
+
+template <UnOp OP>
+__global__ void __launch_bounds__(kThreads) fr_unary_kernel(const Fr* __restrict__ a, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        Fr x = fr_load(a + i), z;
+        if (OP == UnOp::Neg) z = fr_neg(x);
+        else if (OP == UnOp::Mont) z = to_mont<FrP>(x);
+        else z = from_mont<FrP>(x);
+        fr_store(out + i, z);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// conversions
+// ---------------------------------------------------------------------------
+__global__ void fr_from_i32_kernel(const int32_t* __restrict__ in, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        fr_store(out + i, fr_from_i64((long long)in[i]));
+}
+__global__ void fr_from_i64_kernel(const int64_t* __restrict__ in, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        fr_store(out + i, fr_from_i64((long long)in[i]));
+}
+__global__ void fr_to_i32_kernel(const Fr* __restrict__ in, int32_t* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = fr_to_i32(fr_load(in + i));
+}
+__global__ void fr_to_i64_kernel(const Fr* __restrict__ in, int64_t* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = fr_to_i64(fr_load(in + i));
+}
+// float_to_scalar / double_to_scalar (fr-tensor.cu:749-768): scale in the input's
+// own precision, add +-0.5 in double precision, truncate toward zero.
+__global__ void fr_from_f32_kernel(const float* __restrict__ in, unsigned long scale, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float x = in[i] * scale;
+        long v = (x >= 0) ? static_cast<long>(x + 0.5) : static_cast<long>(x - 0.5);
+        fr_store(out + i, fr_from_i64(v));
+    }
+}
+__global__ void fr_from_f64_kernel(const double* __restrict__ in, unsigned long scale, Fr* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        double x = in[i] * scale;
+        long v = (x >= 0) ? static_cast<long>(x + 0.5) : static_cast<long>(x - 0.5);
+        fr_store(out + i, fr_from_i64(v));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// sums
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) fr_partial_sum_kernel(const Fr* __restrict__ a, size_t n, Fr* __restrict__ partial) {
+    __shared__ Fr red[32];
+    Fr acc = fr_zero();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        acc = fr_add(acc, fr_load(a + i));
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) fr_store(partial + blockIdx.x, acc);
+}
+__global__ void __launch_bounds__(kThreads) fr_final_sum_kernel(const Fr* __restrict__ a, size_t n, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc = fr_zero();
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) acc = fr_add(acc, fr_load(a + i));
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) fr_store(out, acc);
+}
+
+int launch_final_sum(const Fr* d_in, size_t n, Fr* d_out, cudaStream_t stream) {
+    ZKB_LAUNCH(fr_final_sum_kernel, 1, kThreads, 0, stream, d_in, n, d_out);
+    return ZKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// eq tables
+// ---------------------------------------------------------------------------
+__global__ void eq_table_kernel(Challenges ch, unsigned k, Fr* __restrict__ table) {
+    __shared__ Fr f1[32], f0[32];   // u_j * R and (1 - u_j) * R
+    if (threadIdx.x < k) {
+        Fr um = to_mont<FrP>(ch.u[threadIdx.x]);
+        f1[threadIdx.x] = um;
+        f0[threadIdx.x] = fr_sub(fe_mont_one<FrP>(), um);
+    }
+    __syncthreads();
+    const size_t n = (size_t)1 << k;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        Fr acc = fe_mont_one<FrP>();
+        for (unsigned j = 0; j < k; ++j) acc = fr_mmul(acc, ((i >> j) & 1) ? f1[j] : f0[j]);
+        fr_store(table + i, acc);
+    }
+}
+
+int build_eq_table(const zkb_fr_t* h_u, unsigned k, Fr* d_table, cudaStream_t stream) {
+    if (k > 32) return fail(ZKB_ERR_LIMIT, "eq table: more than 32 variables");
+    Challenges ch;
+    memset(&ch, 0, sizeof(ch));
+    for (unsigned j = 0; j < k; ++j) memcpy(ch.u[j].v, h_u[j].val, 32);
+    const size_t n = (size_t)1 << k;
+    ZKB_LAUNCH(eq_table_kernel, grid_for(n, kThreads), kThreads, 0, stream, ch, k, d_table);
+    return ZKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// dot products with eq tables
+// ---------------------------------------------------------------------------
+// out[o*window + w] = sum_{j<J} a[(o*J + j)*window + w] * E[j]    (E in Montgomery form)
+// window == 1: one block per output row, threads stride over j.
+__global__ void __launch_bounds__(kThreads) fr_rowdot_kernel(const Fr* __restrict__ a, const Fr* __restrict__ E,
+                                                              size_t rows, size_t J, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    for (size_t o = blockIdx.x; o < rows; o += gridDim.x) {
+        const Fr* row = a + o * J;
+        Fr acc = fr_zero();
+        for (size_t j = threadIdx.x; j < J; j += blockDim.x)
+            acc = fr_add(acc, fr_mmul(fr_load(row + j), fr_load(E + j)));
+        acc = block_sum(acc, red);
+        if (threadIdx.x == 0) fr_store(out + o, acc);
+    }
+}
+// window > 1: one thread per output element, loop over j (coalesced across w).
+// gridDim.y splits the j range; partial results go to out + blockIdx.y * (other*window).
+__global__ void __launch_bounds__(kThreads) fr_coldot_kernel(const Fr* __restrict__ a, const Fr* __restrict__ E,
+                                                              size_t other, size_t J, size_t window,
+                                                              size_t a_len, Fr* __restrict__ out) {
+    const size_t total = other * window;
+    const size_t jper = (J + gridDim.y - 1) / gridDim.y;
+    const size_t j0 = blockIdx.y * jper;
+    const size_t j1 = (j0 + jper < J) ? j0 + jper : J;
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < total; g += (size_t)gridDim.x * blockDim.x) {
+        const size_t o = g / window, w = g % window;
+        Fr acc = fr_zero();
+        for (size_t j = j0; j < j1; ++j) {
+            const size_t idx = (o * J + j) * window + w;
+            if (idx < a_len) acc = fr_add(acc, fr_mmul(fr_load(a + idx), fr_load(E + j)));
+        }
+        fr_store(out + blockIdx.y * total + g, acc);
+    }
+}
+// out[g] = sum_{s<S} part[s*total + g]
+__global__ void fr_sum_slices_kernel(const Fr* __restrict__ part, size_t total, unsigned S, Fr* __restrict__ out) {
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < total; g += (size_t)gridDim.x * blockDim.x) {
+        Fr acc = fr_load(part + g);
+        for (unsigned s = 1; s < S; ++s) acc = fr_add(acc, fr_load(part + s * total + g));
+        fr_store(out + g, acc);
+    }
+}
+
+// Full MLE evaluation: sum_i a[i] * Elo[i & (L-1)] * Ehi[i >> kl].  Each block
+// takes whole chunks of L elements so that the Ehi factor is applied once per
+// chunk and thread; block partials go to `partial`.
+__global__ void __launch_bounds__(kThreads) fr_mle_kernel(const Fr* __restrict__ a, size_t n,
+                                                           const Fr* __restrict__ Elo, unsigned kl,
+                                                           const Fr* __restrict__ Ehi, Fr* __restrict__ partial) {
+    __shared__ Fr red[32];
+    const size_t L = (size_t)1 << kl;
+    const size_t nchunks = (n + L - 1) >> kl;
+    Fr acc = fr_zero();
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const size_t base = c << kl;
+        Fr part = fr_zero();
+        for (size_t j = threadIdx.x; j < L && base + j < n; j += blockDim.x)
+            part = fr_add(part, fr_mmul(fr_load(a + base + j), fr_load(Elo + j)));
+        if (Ehi) part = fr_mmul(part, fr_load(Ehi + c));
+        acc = fr_add(acc, part);
+    }
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) fr_store(partial + blockIdx.x, acc);
+}
+
+static constexpr unsigned kEqLoBits = 12;   // low table: at most 4096 entries (128 KiB, L1/L2 resident)
+
+// d_out[0] = MLE of (d_a, n) at u; all device work on `stream`, no sync.
+static int mle_eval_device(const Fr* d_a, size_t n, const zkb_fr_t* h_u, unsigned k, Fr* d_out,
+                           Scratch& scratch, cudaStream_t stream) {
+    if (k > 32) return fail(ZKB_ERR_LIMIT, "mle_eval: more than 32 variables");
+    const unsigned kl = k < kEqLoBits ? k : kEqLoBits;
+    const unsigned kh = k - kl;
+    Fr* Elo = scratch.get_n<Fr>((size_t)1 << kl);
+    Fr* Ehi = kh ? scratch.get_n<Fr>((size_t)1 << kh) : nullptr;
+    if (!Elo || (kh && !Ehi)) return ZKB_ERR_CUDA;
+    ZKB_TRY(build_eq_table(h_u, kl, Elo, stream));
+    if (kh) ZKB_TRY(build_eq_table(h_u + kl, kh, Ehi, stream));
+    const size_t nchunks = (n + ((size_t)1 << kl) - 1) >> kl;
+    const unsigned grid = grid_for(nchunks, 1, 4);
+    Fr* partial = scratch.get_n<Fr>(grid);
+    if (!partial) return ZKB_ERR_CUDA;
+    ZKB_LAUNCH(fr_mle_kernel, grid, kThreads, 0, stream, d_a, n, Elo, kl, Ehi, partial);
+    return launch_final_sum(partial, grid, d_out, stream);
+}
+
+// d_out[other*window] = fold of the middle axis; see zkb_fr_partial_me.
+int partial_me_device(const Fr* d_a, size_t a_len, size_t other, size_t J, size_t window,
+                      const zkb_fr_t* h_u, unsigned k, Fr* d_out, Scratch& scratch, cudaStream_t stream) {
+    if (k > 24) return fail(ZKB_ERR_LIMIT, "partial_me: folded axis longer than 2^24");
+    Fr* E = scratch.get_n<Fr>((size_t)1 << k);
+    if (!E) return ZKB_ERR_CUDA;
+    ZKB_TRY(build_eq_table(h_u, k, E, stream));
+    if (window == 1 && (other * J) <= a_len) {
+        ZKB_LAUNCH(fr_rowdot_kernel, grid_for(other, 1, 8), kThreads, 0, stream, d_a, E, other, J, d_out);
+        return ZKB_OK;
+    }
+    const size_t total = other * window;
+    unsigned gx = grid_for(total, kThreads, 4);
+    // split the folded axis when there are too few outputs to fill the GPU
+    unsigned split = 1;
+    const size_t want = (size_t)sm_count() * 4;
+    if (gx < want && J >= 64) {
+        split = (unsigned)((want + gx - 1) / gx);
+        if (split > J / 16) split = (unsigned)(J / 16);
+        if (split < 1) split = 1;
+        if (split > 64) split = 64;
+    }
+    if (split == 1) {
+        ZKB_LAUNCH(fr_coldot_kernel, dim3(gx, 1), kThreads, 0, stream, d_a, E, other, J, window, a_len, d_out);
+        return ZKB_OK;
+    }
+    Fr* part = scratch.get_n<Fr>(total * split);
+    if (!part) return ZKB_ERR_CUDA;
+    ZKB_LAUNCH(fr_coldot_kernel, dim3(gx, split), kThreads, 0, stream, d_a, E, other, J, window, a_len, part);
+    ZKB_LAUNCH(fr_sum_slices_kernel, grid_for(total, kThreads), kThreads, 0, stream, part, total, split, d_out);
+    return ZKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// layout
+// ---------------------------------------------------------------------------
+__global__ void fr_pad_kernel(const Fr* __restrict__ a, size_t rows, size_t last, size_t last_p, Fr pad,
+                              Fr* __restrict__ out) {
+    const size_t n = rows * last_p;
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < n; g += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = g / last_p, c = g % last_p;
+        fr_store(out + g, c < last ? fr_load(a + r * last + c) : pad);
+    }
+}
+// 32x32 tile transpose through shared memory (coalesced both ways)
+__global__ void fr_transpose_kernel(const Fr* __restrict__ a, size_t M, size_t N, Fr* __restrict__ out) {
+    __shared__ Fr tile[32][33];
+    const size_t bx = blockIdx.x * 32, by = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const size_t row = by + r, col = bx + threadIdx.x;
+        if (row < M && col < N) tile[r][threadIdx.x] = fr_load(a + row * N + col);
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const size_t row = bx + r, col = by + threadIdx.x;   // in the transposed matrix [N, M]
+        if (row < N && col < M) fr_store(out + row * M + col, tile[threadIdx.x][r]);
+    }
+}
+__global__ void fr_add_bias_kernel(Fr* __restrict__ z, const Fr* __restrict__ bias, size_t rows, size_t cols) {
+    const size_t n = rows * cols;
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < n; g += (size_t)gridDim.x * blockDim.x)
+        fr_store(z + g, fr_add(fr_load(z + g), fr_load(bias + g % cols)));
+}
+__global__ void fr_gather_kernel(const uint32_t* __restrict__ idx, const Fr* __restrict__ vals, Fr* __restrict__ out, size_t n) {
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < n; g += (size_t)gridDim.x * blockDim.x)
+        fr_store(out + g, fr_load(vals + idx[g]));
+}
+
+// ---------------------------------------------------------------------------
+// matmul: C[M,P] = A[M,N] * B[N,P].  32x32 output tile per block of 16x16
+// threads, each thread owning a 2x2 micro-tile; the inner products are summed as
+// Montgomery products (each a*b/R) and multiplied by R^2 once per output.
+// ---------------------------------------------------------------------------
+static constexpr int kMmTile = 32, kMmK = 16;
+__global__ void __launch_bounds__(256) fr_matmul_kernel(const Fr* __restrict__ A, const Fr* __restrict__ B,
+                                                         Fr* __restrict__ C, size_t M, size_t N, size_t P) {
+    __shared__ Fr As[kMmTile][kMmK];
+    __shared__ Fr Bs[kMmK][kMmTile];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const size_t row0 = (size_t)blockIdx.y * kMmTile, col0 = (size_t)blockIdx.x * kMmTile;
+    Fr acc[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j] = fr_zero();
+    for (size_t k0 = 0; k0 < N; k0 += kMmK) {
+        // A tile: 32 rows x 16 k  (512 elements, 2 per thread); B tile: 16 k x 32 cols
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int la = threadIdx.x + e * 256;
+            const int ar = la >> 4, ak = la & 15;
+            const size_t gr = row0 + ar, gk = k0 + ak;
+            As[ar][ak] = (gr < M && gk < N) ? fr_load(A + gr * N + gk) : fr_zero();
+            const int bk = la >> 5, bc = la & 31;
+            const size_t gk2 = k0 + bk, gc = col0 + bc;
+            Bs[bk][bc] = (gk2 < N && gc < P) ? fr_load(B + gk2 * P + gc) : fr_zero();
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int kk = 0; kk < kMmK; ++kk) {
+            const Fr a0 = As[ty][kk], a1 = As[ty + 16][kk];
+            const Fr b0 = Bs[kk][tx], b1 = Bs[kk][tx + 16];
+            acc[0][0] = fr_add(acc[0][0], fr_mmul(a0, b0));
+            acc[0][1] = fr_add(acc[0][1], fr_mmul(a0, b1));
+            acc[1][0] = fr_add(acc[1][0], fr_mmul(a1, b0));
+            acc[1][1] = fr_add(acc[1][1], fr_mmul(a1, b1));
+        }
+        __syncthreads();
+    }
+    const Fr r2 = fe_r2<FrP>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const size_t r = row0 + ty + 16 * i, c = col0 + tx + 16 * j;
+            if (r < M && c < P) fr_store(C + r * P + c, fr_mmul(acc[i][j], r2));
+        }
+}
+
+// ---------------------------------------------------------------------------
+// 1/(a + beta) with one inversion per block (Montgomery's trick).
+// Values are treated as Montgomery forms of v/R, so no conversion is needed on
+// the way in; the block inverse is scaled by R^-2 once, which lands every
+// output in standard form.  A zero maps to zero, as with the reference's
+// exponentiation-based inverse.
+// ---------------------------------------------------------------------------
+static constexpr int kInvPerThread = 8;
+__global__ void __launch_bounds__(kThreads) fr_inv_shifted_kernel(const Fr* __restrict__ a, Fr beta, Fr* __restrict__ out, size_t n) {
+    __shared__ Fr pre[kThreads];    // inclusive prefix products over threads
+    __shared__ Fr suf[kThreads];    // inclusive suffix products over threads
+    __shared__ Fr inv_total;
+    const size_t tile = (size_t)kThreads * kInvPerThread;
+    Fr one = fr_zero();
+    one.v[0] = 1;
+    for (size_t base = blockIdx.x * tile; base < n; base += (size_t)gridDim.x * tile) {
+        Fr x[kInvPerThread], p[kInvPerThread];
+        unsigned zero_mask = 0;
+#pragma unroll
+        for (int e = 0; e < kInvPerThread; ++e) {
+            const size_t i = base + (size_t)e * kThreads + threadIdx.x;
+            Fr v = one;
+            if (i < n) {
+                v = fr_add(fr_load(a + i), beta);
+                if (fe_is_zero(v)) { zero_mask |= 1u << e; v = one; }
+            }
+            x[e] = v;
+            p[e] = e ? fr_mmul(p[e - 1], v) : v;
+        }
+        pre[threadIdx.x] = p[kInvPerThread - 1];
+        suf[threadIdx.x] = p[kInvPerThread - 1];
+        __syncthreads();
+        // Hillis-Steele scans in both directions
+        for (int off = 1; off < (int)kThreads; off <<= 1) {
+            Fr np = pre[threadIdx.x], ns = suf[threadIdx.x];
+            const bool hp = (int)threadIdx.x >= off, hs = threadIdx.x + off < kThreads;
+            if (hp) np = fr_mmul(np, pre[threadIdx.x - off]);
+            if (hs) ns = fr_mmul(ns, suf[threadIdx.x + off]);
+            __syncthreads();
+            pre[threadIdx.x] = np;
+            suf[threadIdx.x] = ns;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            Fr t = mont_inv<FrP>(pre[kThreads - 1]);
+            t = fr_mmul(fr_mmul(t, one), one);     // * R^-2
+            inv_total = t;
+        }
+        __syncthreads();
+        // inverse of this thread's own product: inv_total * prod(other threads)
+        Fr r = inv_total;
+        if (threadIdx.x > 0) r = fr_mmul(r, pre[threadIdx.x - 1]);
+        if (threadIdx.x + 1 < kThreads) r = fr_mmul(r, suf[threadIdx.x + 1]);
+#pragma unroll
+        for (int e = kInvPerThread - 1; e >= 0; --e) {
+            const size_t i = base + (size_t)e * kThreads + threadIdx.x;
+            Fr inv_e = e ? fr_mmul(r, p[e - 1]) : r;
+            if (e) r = fr_mmul(r, x[e]);
+            if (i < n) fr_store(out + i, ((zero_mask >> e) & 1u) ? fr_zero() : inv_e);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace zkb
+
+using namespace zkb;
+
+#define FR(p) reinterpret_cast<Fr*>(p)
+#define CFR(p) reinterpret_cast<const Fr*>(p)
+
+static inline Fr host_to_dev(const zkb_fr_t& x) {
+    Fr r;
+    memcpy(r.v, x.val, 32);
+    return r;
+}
+static inline Fr host_to_dev_mont(const zkb_fr_t& x) {
+    zkb_fr_t m = hfr::store(hfr::to_mont(hfr::load(x)));
+    return host_to_dev(m);
+}
+
+extern "C" {
+
+int zkb_fr_from_i32(const int32_t* d_in, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_from_i32_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), d_in, FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_from_i64(const int64_t* d_in, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_from_i64_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), d_in, FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_to_i32(const zkb_fr_t* d_in, int32_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_to_i32_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), CFR(d_in), d_out, n);
+    return ZKB_OK;
+}
+int zkb_fr_to_i64(const zkb_fr_t* d_in, int64_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_to_i64_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), CFR(d_in), d_out, n);
+    return ZKB_OK;
+}
+int zkb_fr_from_f32(const float* d_in, uint64_t scale, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_from_f32_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), d_in, (unsigned long)scale, FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_from_f64(const double* d_in, uint64_t scale, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_from_f64_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream), d_in, (unsigned long)scale, FR(d_out), n);
+    return ZKB_OK;
+}
+
+#define ZKB_BINARY(name, OP)                                                                         \
+    int name(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_out, size_t n, void* stream) {   \
+        if (!n) return ZKB_OK;                                                                       \
+        ZKB_LAUNCH(fr_binary_kernel<OP>, grid_for(n, kThreads), kThreads, 0, as_stream(stream),      \
+                   CFR(d_a), CFR(d_b), FR(d_out), n);                                                \
+        return ZKB_OK;                                                                               \
+    }
+ZKB_BINARY(zkb_fr_add, BinOp::Add)
+ZKB_BINARY(zkb_fr_sub, BinOp::Sub)
+ZKB_BINARY(zkb_fr_mul, BinOp::Mul)
+ZKB_BINARY(zkb_fr_mont_mul, BinOp::MontMul)
+
+int zkb_fr_add_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_scalar_kernel<BinOp::Add>, grid_for(n, kThreads), kThreads, 0, as_stream(stream),
+               CFR(d_a), host_to_dev(*h_x), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_sub_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_scalar_kernel<BinOp::Sub>, grid_for(n, kThreads), kThreads, 0, as_stream(stream),
+               CFR(d_a), host_to_dev(*h_x), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_mul_scalar(const zkb_fr_t* d_a, const zkb_fr_t* h_x, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_scalar_kernel<BinOp::Mul>, grid_for(n, kThreads), kThreads, 0, as_stream(stream),
+               CFR(d_a), host_to_dev_mont(*h_x), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_neg(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_unary_kernel<UnOp::Neg>, grid_for(n, kThreads), kThreads, 0, as_stream(stream), CFR(d_a), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_mont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_unary_kernel<UnOp::Mont>, grid_for(n, kThreads), kThreads, 0, as_stream(stream), CFR(d_a), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_unmont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_unary_kernel<UnOp::Unmont>, grid_for(n, kThreads), kThreads, 0, as_stream(stream), CFR(d_a), FR(d_out), n);
+    return ZKB_OK;
+}
+int zkb_fr_inv_shifted(const zkb_fr_t* d_a, const zkb_fr_t* h_beta, zkb_fr_t* d_out, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_inv_shifted_kernel, grid_for(n, kThreads * kInvPerThread, 4), kThreads, 0, as_stream(stream),
+               CFR(d_a), host_to_dev(*h_beta), FR(d_out), n);
+    return ZKB_OK;
+}
+
+int zkb_fr_sum(const zkb_fr_t* d_a, size_t n, zkb_fr_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n == 0) { memset(h_out, 0, sizeof(*h_out)); return ZKB_OK; }
+    Scratch scratch(s);
+    const unsigned grid = grid_for(n, kThreads * 8, 4);
+    Fr* partial = scratch.get_n<Fr>(grid + 1);
+    if (!partial) return ZKB_ERR_CUDA;
+    ZKB_LAUNCH(fr_partial_sum_kernel, grid, kThreads, 0, s, CFR(d_a), n, partial);
+    ZKB_TRY(launch_final_sum(partial, grid, partial + grid, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, partial + grid, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+int zkb_fr_mle_eval(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k > 32 || n == 0) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    const size_t full = (size_t)1 << k;
+    if (n <= full / 2 || n > full) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    Scratch scratch(s);
+    Fr* d_out = scratch.get_n<Fr>(1);
+    if (!d_out) return ZKB_ERR_CUDA;
+    ZKB_TRY(mle_eval_device(CFR(d_a), n, h_u, k, d_out, scratch, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, d_out, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+int zkb_fr_partial_me(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                      size_t cur_dim, size_t window, zkb_fr_t* d_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k > 31) return fail(ZKB_ERR_LIMIT, "partial_me: too many variables");
+    if (cur_dim <= (((size_t)1 << k) >> 1)) return fail(ZKB_ERR_DIM, "cur_dim <= ((1<<u.size()) >> 1)");
+    if (cur_dim > ((size_t)1 << k)) return fail(ZKB_ERR_DIM, "cur_dim > (1<<u.size())");
+    if (window == 0 || n % (cur_dim * window) != 0) return fail(ZKB_ERR_DIM, "t.size % (cur_dim * window_size) != 0");
+    if (k == 0) {   // cur_dim == 1: nothing to fold
+        ZKB_CUDA(cudaMemcpyAsync(d_out, d_a, n * 32, cudaMemcpyDeviceToDevice, s));
+        return ZKB_OK;
+    }
+    Scratch scratch(s);
+    return partial_me_device(CFR(d_a), n, n / (cur_dim * window), cur_dim, window, h_u, k, FR(d_out), scratch, s);
+}
+
+int zkb_fr_partial_me_window(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                             size_t window, zkb_fr_t* d_out, size_t* out_n, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k > 31 || window == 0) return fail(ZKB_ERR_ARG, "partial_me: bad arguments");
+    if (k >= 1 && n <= window * ((size_t)1 << (k - 1))) return fail(ZKB_ERR_DIM, "partial_me: Incompatible dimensions");
+    const size_t J = (size_t)1 << k;
+    const size_t nwin = (n + window - 1) / window;
+    const size_t groups = (nwin + J - 1) / J;
+    if (out_n) *out_n = groups * window;
+    if (k == 0) {
+        ZKB_CUDA(cudaMemcpyAsync(d_out, d_a, n * 32, cudaMemcpyDeviceToDevice, s));
+        if (out_n) *out_n = n;
+        return ZKB_OK;
+    }
+    Scratch scratch(s);
+    // view as [groups, J, window] with everything past n reading as zero
+    return partial_me_device(CFR(d_a), n, groups, J, window, h_u, k, FR(d_out), scratch, s);
+}
+
+int zkb_fr_mle_eval_2d(const zkb_fr_t* d_a, size_t d0, size_t d1,
+                       const zkb_fr_t* h_u0, unsigned k0, const zkb_fr_t* h_u1, unsigned k1,
+                       zkb_fr_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k0 > 31 || k1 > 31) return fail(ZKB_ERR_LIMIT, "multi_dim_me: too many variables");
+    if (d1 <= (((size_t)1 << k1) >> 1)) return fail(ZKB_ERR_DIM, "cur_dim <= ((1<<u.size()) >> 1)");
+    if (d1 > ((size_t)1 << k1)) return fail(ZKB_ERR_DIM, "cur_dim > (1<<u.size())");
+    if (d0 <= (((size_t)1 << k0) / 2) || d0 > ((size_t)1 << k0)) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    Scratch scratch(s);
+    Fr* rowred = scratch.get_n<Fr>(d0 + 1);
+    if (!rowred) return ZKB_ERR_CUDA;
+    if (k1 == 0) {
+        ZKB_CUDA(cudaMemcpyAsync(rowred, d_a, d0 * 32, cudaMemcpyDeviceToDevice, s));
+    } else {
+        ZKB_TRY(partial_me_device(CFR(d_a), d0 * d1, d0, d1, 1, h_u1, k1, rowred, scratch, s));
+    }
+    ZKB_TRY(mle_eval_device(rowred, d0, h_u0, k0, rowred + d0, scratch, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, rowred + d0, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+int zkb_fr_pad_last(const zkb_fr_t* d_a, size_t rows, size_t last, size_t last_padded,
+                    const zkb_fr_t* h_pad_val, zkb_fr_t* d_out, void* stream) {
+    if (last_padded < last) return fail(ZKB_ERR_DIM, "pad: padded extent smaller than extent");
+    const size_t n = rows * last_padded;
+    if (!n) return ZKB_OK;
+    ZKB_LAUNCH(fr_pad_kernel, grid_for(n, kThreads), kThreads, 0, as_stream(stream),
+               CFR(d_a), rows, last, last_padded, host_to_dev(*h_pad_val), FR(d_out));
+    return ZKB_OK;
+}
+int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, void* stream) {
+    if (!M || !N) return ZKB_OK;
+    dim3 grid(div_up(N, 32), div_up(M, 32)), block(32, 8);
+    if (grid.y > 65535) return fail(ZKB_ERR_LIMIT, "transpose: more than 2^21 rows");
+    ZKB_LAUNCH(fr_transpose_kernel, grid, block, 0, as_stream(stream), CFR(d_a), M, N, FR(d_out));
+    return ZKB_OK;
+}
+int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_t M, size_t N, size_t P, void* stream) {
+    if (!M || !P) return ZKB_OK;
+    dim3 grid(div_up(P, kMmTile), div_up(M, kMmTile));
+    if (grid.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^21 rows");
+    ZKB_LAUNCH(fr_matmul_kernel, grid, 256, 0, as_stream(stream), CFR(d_a), CFR(d_b), FR(d_c), M, N, P);
+    return ZKB_OK;
+}
+int zkb_fr_add_bias(zkb_fr_t* d_z, const zkb_fr_t* d_bias, size_t rows, size_t cols, void* stream) {
+    if (!rows || !cols) return ZKB_OK;
+    ZKB_LAUNCH(fr_add_bias_kernel, grid_for(rows * cols, kThreads), kThreads, 0, as_stream(stream),
+               FR(d_z), CFR(d_bias), rows, cols);
+    return ZKB_OK;
+}
+int zkb_fr_gather(const uint32_t* d_indices, const zkb_fr_t* d_vals, zkb_fr_t* d_out, size_t D, void* stream) {
+    if (!D) return ZKB_OK;
+    ZKB_LAUNCH(fr_gather_kernel, grid_for(D, kThreads), kThreads, 0, as_stream(stream), d_indices, CFR(d_vals), FR(d_out), D);
+    return ZKB_OK;
+}
+
+}  // extern "C"

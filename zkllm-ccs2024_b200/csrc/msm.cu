@@ -1,0 +1,387 @@
+// Pedersen/Hyrax row commitment as a bucket-method multi-scalar multiplication.
+//
+// Commitment::commit_int (commitment.cu:31-58) multiplies every (scalar,
+// generator) pair with a 31-step double-and-add, stores all m*n products and
+// tree-sums each row.  Here each row is a Pippenger MSM over the shared
+// generator set:
+//
+//   1. generators are normalised to affine once per call;
+//   2. every scalar is split into signed 7-bit digits d_w in [-64, 63] (adding
+//      0x40 to every 7-bit field makes each digit an independent bit-field
+//      read, no carry chain);  the number of windows follows the largest
+//      |scalar| of the call, so 14-bit fixed-point weights need two windows;
+//   3. per (row, column segment, window) a counting sort in shared memory
+//      groups the non-zero digits by bucket |d|;
+//   4. one warp accumulates bucket b of window w for 32 (row, segment) lists at
+//      a time - lanes walk lists of statistically equal length, so they stay
+//      in step - with mixed Jacobian+affine additions;
+//   5. buckets are combined per row: sum_b b*B_b by running sums over groups
+//      of 8 buckets, then Horner over the windows.
+//
+// The m*n*144-byte product array of the reference is never formed.
+#include "frutil.cuh"
+#include "g1.cuh"
+#include "hostfr.hpp"
+
+#include <vector>
+
+namespace zkb {
+
+static constexpr int kWinBits = 7;
+static constexpr int kBuckets = 64;           // |digit| in 1..64
+static constexpr unsigned kMaxSeg = 16384;    // columns per sorted list (u16 entries: col << 1 | neg)
+static constexpr int kMaxWindows = 37;        // ceil(259 / 7) for full-width scalars
+
+// ---- digits ------------------------------------------------------------------
+// int32 scalar: magnitude + sign; digit w of (|s| + K), K = 0x40 in every field.
+ZKB_DEV int digit_of_u64(unsigned long long biased, int w) {
+    return (int)((biased >> (kWinBits * w)) & 127u) - 64;
+}
+__host__ __device__ constexpr unsigned long long bias_u64() {
+    unsigned long long k = 0;
+    for (int w = 0; w < 9; ++w) k |= 64ull << (kWinBits * w);
+    return k;
+}
+
+// Full-width scalar: 9-limb (a + K), digit read across limb boundaries.
+struct Biased288 { uint32_t l[9]; };
+ZKB_DEV Biased288 bias_fr(const Fr& a) {
+    // K = 0x40 in each of the 37 seven-bit fields = repeating bit pattern
+    Biased288 r;
+    uint32_t carry = 0;
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+        // limb i of K: bits 32i .. 32i+31; field bit 6 of window w sits at 7w + 6
+        uint32_t k = 0;
+#pragma unroll
+        for (int bit = 0; bit < 32; ++bit) {
+            const int pos = 32 * i + bit;
+            if (pos % 7 == 6 && pos / 7 < kMaxWindows) k |= 1u << bit;
+        }
+        const uint32_t ai = i < 8 ? a.v[i] : 0u;
+        const unsigned long long s = (unsigned long long)ai + k + carry;
+        r.l[i] = (uint32_t)s;
+        carry = (uint32_t)(s >> 32);
+    }
+    return r;
+}
+ZKB_DEV int digit_of_288(const Biased288& b, int w) {
+    const int pos = kWinBits * w, limb = pos >> 5, sh = pos & 31;
+    unsigned long long two = b.l[limb];
+    if (limb + 1 < 9) two |= (unsigned long long)b.l[limb + 1] << 32;
+    return (int)((two >> sh) & 127u) - 64;
+}
+
+// ---- kernels -------------------------------------------------------------------
+__global__ void i32_absmax_kernel(const int32_t* __restrict__ s, size_t n, unsigned* __restrict__ out) {
+    unsigned m = 0;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int v = s[i];
+        const unsigned a = v < 0 ? 0u - (unsigned)v : (unsigned)v;
+        m = a > m ? a : m;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned o = __shfl_down_sync(0xffffffffu, m, off);
+        m = o > m ? o : m;
+    }
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+struct MsmShape {
+    size_t m, n;          // rows, generators
+    unsigned nseg, seg;   // column segments per row and their length
+    int W;                // windows
+};
+
+// One CTA per (segment, row): for each window, counting-sort the non-zero
+// digits of the segment by bucket.  ent: u16 lists, offs: 65 offsets per list.
+template <bool FULL>
+__global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ scalars, MsmShape sh,
+                                                        uint16_t* __restrict__ ent, uint16_t* __restrict__ offs) {
+    extern __shared__ uint16_t list[];           // sh.seg entries
+    __shared__ unsigned hist[kBuckets + 1];
+    __shared__ unsigned cursor[kBuckets + 1];
+    const unsigned seg_id = blockIdx.x;
+    const size_t row = blockIdx.y;
+    const size_t col0 = (size_t)seg_id * sh.seg;
+    const size_t ncol = (col0 + sh.seg <= sh.n) ? sh.seg : (sh.n > col0 ? sh.n - col0 : 0);
+    const size_t rs = row * sh.nseg + seg_id;
+    for (int w = 0; w < sh.W; ++w) {
+        if (threadIdx.x <= kBuckets) hist[threadIdx.x] = 0;
+        __syncthreads();
+        for (size_t c = threadIdx.x; c < ncol; c += blockDim.x) {
+            int d;
+            if (FULL) {
+                d = digit_of_288(bias_fr(fr_load(static_cast<const Fr*>(scalars) + row * sh.n + col0 + c)), w);
+            } else {
+                const int v = static_cast<const int32_t*>(scalars)[row * sh.n + col0 + c];
+                const unsigned a = v < 0 ? 0u - (unsigned)v : (unsigned)v;
+                d = digit_of_u64((unsigned long long)a + bias_u64(), w);
+                if (v < 0) d = -d;
+            }
+            if (d) atomicAdd(&hist[d < 0 ? -d : d], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned run = 0;
+            uint16_t* o = offs + (rs * sh.W + w) * (kBuckets + 1);
+            for (int b = 1; b <= kBuckets; ++b) {
+                cursor[b] = run;
+                o[b - 1] = (uint16_t)run;
+                run += hist[b];
+            }
+            o[kBuckets] = (uint16_t)run;
+        }
+        __syncthreads();
+        for (size_t c = threadIdx.x; c < ncol; c += blockDim.x) {
+            int d;
+            if (FULL) {
+                d = digit_of_288(bias_fr(fr_load(static_cast<const Fr*>(scalars) + row * sh.n + col0 + c)), w);
+            } else {
+                const int v = static_cast<const int32_t*>(scalars)[row * sh.n + col0 + c];
+                const unsigned a = v < 0 ? 0u - (unsigned)v : (unsigned)v;
+                d = digit_of_u64((unsigned long long)a + bias_u64(), w);
+                if (v < 0) d = -d;
+            }
+            if (d) {
+                const unsigned pos = atomicAdd(&cursor[d < 0 ? -d : d], 1u);
+                list[pos] = (uint16_t)((c << 1) | (d < 0 ? 1u : 0u));
+            }
+        }
+        __syncthreads();
+        uint16_t* e = ent + (rs * sh.W + w) * (size_t)sh.seg;
+        const unsigned total = cursor[kBuckets];   // end of the last bucket
+        for (unsigned i = threadIdx.x; i < total; i += blockDim.x) e[i] = list[i];
+        __syncthreads();
+    }
+}
+
+// One warp per (32 consecutive lists, window, bucket).  blockIdx.x enumerates
+// (list group, window, bucket) with the bucket fastest.
+static constexpr unsigned kAccWarps = 4;
+__global__ void __launch_bounds__(kAccWarps * 32) msm_accumulate_kernel(const G1Aff* __restrict__ bases, MsmShape sh,
+                                                                         const uint16_t* __restrict__ ent,
+                                                                         const uint16_t* __restrict__ offs,
+                                                                         G1Jac* __restrict__ buckets, size_t n_units) {
+    const size_t unit = (size_t)blockIdx.x * kAccWarps + (threadIdx.x >> 5);
+    if (unit >= n_units) return;
+    const unsigned lane = threadIdx.x & 31;
+    const unsigned b = (unsigned)(unit % kBuckets);           // bucket index 0..63 <-> |digit| = b + 1
+    const unsigned w = (unsigned)((unit / kBuckets) % sh.W);
+    const size_t grp = unit / ((size_t)kBuckets * sh.W);
+    const size_t rs = grp * 32 + lane;
+    const size_t n_rs = sh.m * sh.nseg;
+    if (rs >= n_rs) return;
+    const size_t list_id = rs * sh.W + w;
+    const uint16_t* o = offs + list_id * (kBuckets + 1);
+    const unsigned beg = o[b], end = o[b + 1];
+    const uint16_t* e = ent + list_id * (size_t)sh.seg;
+    const size_t col0 = (rs % sh.nseg) * (size_t)sh.seg;
+    G1Jac acc = g1_identity();
+    for (unsigned i = beg; i < end; ++i) {
+        const unsigned code = e[i];
+        G1Aff p = g1_aff_load(bases + col0 + (code >> 1));
+        if (code & 1u) p = g1_aff_neg(p);
+        acc = g1_add_mixed(acc, p);
+    }
+    g1_store(buckets + list_id * kBuckets + b, acc);
+}
+
+// Thread per (row, window, group of 8 buckets): sums the segment partials of its
+// buckets and forms the group's running sums.
+//   Lg[(row*W + w)*8 + g] = sum_{i=1..8} i * B_{8g+i}      Gg[...] = sum_i B_{8g+i}
+__global__ void __launch_bounds__(128) msm_group_kernel(const G1Jac* __restrict__ buckets, MsmShape sh,
+                                                         G1Jac* __restrict__ Lg, G1Jac* __restrict__ Gg) {
+    const size_t total = sh.m * sh.W * 8;
+    for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        const unsigned g = (unsigned)(t & 7);
+        const unsigned w = (unsigned)((t >> 3) % sh.W);
+        const size_t row = (t >> 3) / sh.W;
+        G1Jac run = g1_identity(), loc = g1_identity();
+        for (int i = 8; i >= 1; --i) {
+            const unsigned b = 8 * g + i - 1;
+            for (unsigned s = 0; s < sh.nseg; ++s) {
+                const size_t list_id = (row * sh.nseg + s) * sh.W + w;
+                run = g1_add(run, g1_load(buckets + list_id * kBuckets + b));
+            }
+            loc = g1_add(loc, run);
+        }
+        g1_store(Lg + t, loc);
+        g1_store(Gg + t, run);
+    }
+}
+
+// Thread per row: window sums from the group results, then Horner over windows.
+__global__ void __launch_bounds__(128) msm_finish_kernel(const G1Jac* __restrict__ Lg, const G1Jac* __restrict__ Gg,
+                                                          MsmShape sh, G1Jac* __restrict__ out) {
+    for (size_t row = blockIdx.x * (size_t)blockDim.x + threadIdx.x; row < sh.m; row += (size_t)gridDim.x * blockDim.x) {
+        G1Jac acc = g1_identity();
+        for (int w = sh.W - 1; w >= 0; --w) {
+            if (w != sh.W - 1) {
+                for (int d = 0; d < kWinBits; ++d) acc = g1_double(acc);
+            }
+            const size_t base = (row * sh.W + w) * 8;
+            // window total = sum_g Lg + 8 * sum_{g>=1} g * Gg
+            G1Jac lsum = g1_identity(), run = g1_identity(), t = g1_identity();
+            for (int g = 7; g >= 0; --g) {
+                lsum = g1_add(lsum, g1_load(Lg + base + g));
+                if (g >= 1) {
+                    run = g1_add(run, g1_load(Gg + base + g));
+                    t = g1_add(t, run);
+                }
+            }
+            t = g1_double(g1_double(g1_double(t)));
+            acc = g1_add(acc, g1_add(lsum, t));
+        }
+        g1_store(out + row, acc);
+    }
+}
+
+__global__ void g1_to_affine_simple_kernel(const G1Jac* __restrict__ a, G1Aff* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const G1Jac p = g1_load(a + i);
+        G1Aff r;
+        if (g1_is_identity(p)) {
+            r.x = fe_zero<FqParams>(); r.y = fe_zero<FqParams>();
+        } else {
+            const Fq zi = mont_inv<FqParams>(p.z);
+            const Fq zi2 = fq_sqr(zi);
+            r.x = fq_mul(p.x, zi2);
+            r.y = fq_mul(p.y, fq_mul(zi2, zi));
+        }
+        g1_aff_store(out + i, r);
+    }
+}
+
+// Shared driver.  `scalars` is int32[m*n] (FULL = false) or Fr[m*n] (FULL = true).
+template <bool FULL>
+static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t m, int W,
+                    G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    if (m == 0) return ZKB_OK;
+    MsmShape sh;
+    sh.m = m; sh.n = n; sh.W = W;
+    // enough (row, segment) lists to fill warps, segments no longer than kMaxSeg
+    size_t nseg = (4096 + m - 1) / m;
+    const size_t min_seg_len = 256;
+    if (nseg > (n + min_seg_len - 1) / min_seg_len) nseg = (n + min_seg_len - 1) / min_seg_len;
+    if (nseg < (n + kMaxSeg - 1) / kMaxSeg) nseg = (n + kMaxSeg - 1) / kMaxSeg;
+    if (nseg < 1) nseg = 1;
+    if (nseg > 65535) return fail(ZKB_ERR_LIMIT, "commit: more than 2^30 generators");
+    if (m > 65535 * 32) return fail(ZKB_ERR_LIMIT, "commit: too many rows");
+    sh.nseg = (unsigned)nseg;
+    sh.seg = (unsigned)((n + nseg - 1) / nseg);
+    const size_t n_rs = m * nseg;
+    const size_t n_lists = n_rs * W;
+
+    G1Aff* bases = scratch.get_n<G1Aff>(n);
+    uint16_t* ent = scratch.get_n<uint16_t>(n_lists * sh.seg);
+    uint16_t* offs = scratch.get_n<uint16_t>(n_lists * (kBuckets + 1));
+    G1Jac* buckets = scratch.get_n<G1Jac>(n_lists * kBuckets);
+    G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
+    G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
+    if (!bases || !ent || !offs || !buckets || !Lg || !Gg) return ZKB_ERR_CUDA;
+
+    ZKB_LAUNCH(g1_to_affine_simple_kernel, grid_for(n, 128), 128, 0, s, d_gens, bases, n);
+    // rows go to gridDim.y in slices of at most 65535
+    for (size_t r0 = 0; r0 < m; r0 += 65535) {
+        const size_t rows = (m - r0 < 65535) ? m - r0 : 65535;
+        MsmShape part = sh;
+        part.m = rows;
+        const void* sc = FULL ? static_cast<const void*>(static_cast<const Fr*>(d_scalars) + r0 * n)
+                              : static_cast<const void*>(static_cast<const int32_t*>(d_scalars) + r0 * n);
+        ZKB_LAUNCH(msm_sort_kernel<FULL>, dim3(sh.nseg, (unsigned)rows), 256, sh.seg * sizeof(uint16_t), s,
+                   sc, part, ent + r0 * nseg * W * sh.seg, offs + r0 * nseg * W * (kBuckets + 1));
+    }
+    const size_t n_groups = (n_rs + 31) / 32;
+    const size_t n_units = n_groups * W * kBuckets;
+    const size_t acc_blocks = (n_units + kAccWarps - 1) / kAccWarps;
+    if (acc_blocks > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
+    ZKB_LAUNCH(msm_accumulate_kernel, (unsigned)acc_blocks, kAccWarps * 32, 0, s, bases, sh, ent, offs, buckets, n_units);
+    ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 128), 128, 0, s, buckets, sh, Lg, Gg);
+    ZKB_LAUNCH(msm_finish_kernel, grid_for(m, 128), 128, 0, s, Lg, Gg, sh, d_out);
+    return ZKB_OK;
+}
+
+// Smallest W such that |s| + K stays below 128^W for every |s| <= max_abs, where
+// K is 0x40 in each of the W fields: max_abs < (63 * 128^W + 64) / 127.
+static int windows_for_max(unsigned long long max_abs) {
+    unsigned long long p = 128;
+    for (int W = 1; W < 9; ++W, p *= 128)
+        if (max_abs * 127 < 63 * p + 64) return W;
+    return 9;
+}
+
+// int32 path: find the largest magnitude (one small D2H), pick the window count.
+static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
+                             G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
+    const size_t m = n_scalars / n_gen;
+    if (m == 0) return ZKB_OK;
+    unsigned* d_max = scratch.get_n<unsigned>(4);
+    if (!d_max) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(d_max, 0, 16, s));
+    ZKB_LAUNCH(i32_absmax_kernel, grid_for(n_scalars, 256 * 8), 256, 0, s, d_scalars, n_scalars, d_max);
+    unsigned h_max = 0;
+    ZKB_CUDA(cudaMemcpyAsync(&h_max, d_max, 4, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return msm_rows<false>(d_gens, n_gen, d_scalars, m, windows_for_max(h_max), d_out, scratch, s);
+}
+
+}  // namespace zkb
+
+using namespace zkb;
+
+extern "C" {
+
+int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
+                   zkb_g1_t* d_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    Scratch scratch(s);
+    return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
+                             reinterpret_cast<G1Jac*>(d_out), scratch, s);
+}
+
+int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
+                   zkb_g1_t* d_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
+    if (n_scalars == 0) return ZKB_OK;
+    Scratch scratch(s);
+    int32_t* ints = scratch.get_n<int32_t>(n_scalars);
+    if (!ints) return ZKB_ERR_CUDA;
+    ZKB_TRY(zkb_fr_to_i32(d_scalars, ints, n_scalars, stream));
+    return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, ints, n_scalars,
+                             reinterpret_cast<G1Jac*>(d_out), scratch, s);
+}
+
+int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_scalars, size_t n_scalars,
+                        zkb_g1_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
+    const size_t m = n_scalars / n_gen;
+    if (m == 0) return ZKB_OK;
+    Scratch scratch(s);
+    G1Jac* d_gens = scratch.get_n<G1Jac>(n_gen);
+    int32_t* d_sc = scratch.get_n<int32_t>(n_scalars);
+    G1Jac* d_out = scratch.get_n<G1Jac>(m);
+    if (!d_gens || !d_sc || !d_out) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemcpyAsync(d_gens, h_gens, n_gen * sizeof(G1Jac), cudaMemcpyHostToDevice, s));
+    ZKB_CUDA(cudaMemcpyAsync(d_sc, h_scalars, n_scalars * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    ZKB_TRY(commit_i32_device(d_gens, n_gen, d_sc, n_scalars, d_out, scratch, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, d_out, m * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
+               zkb_g1_t* d_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit - Incompatible dimensions");
+    if (n_scalars == 0) return ZKB_OK;
+    Scratch scratch(s);
+    return msm_rows<true>(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars / n_gen, kMaxWindows,
+                          reinterpret_cast<G1Jac*>(d_out), scratch, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,737 @@
+// Sumcheck provers: zkip / zkFC::prove, tLookup::prove, multi-Hadamard and the
+// legacy adjacent-pair sumchecks.
+//
+// The reference takes every challenge vector as an argument (or draws it up
+// front), so all rounds of a proof are queued on the stream back to back: each
+// round is ONE kernel that reads the current arrays once, accumulates the
+// round-polynomial sums and writes the folded arrays; the grid-wide sums are
+// finished by the last CTA of the same launch.  The host reads the sums once,
+// after the last round, assembles the polynomials and replays the verifier
+// checks (claim == p(0) + p(1)) that the reference makes between rounds.
+#include "frutil.cuh"
+#include "hostfr.hpp"
+
+#include <vector>
+
+namespace zkb {
+
+int partial_me_device(const Fr* d_a, size_t a_len, size_t other, size_t J, size_t window,
+                      const zkb_fr_t* h_u, unsigned k, Fr* d_out, Scratch& scratch, cudaStream_t stream);
+
+static constexpr unsigned kThreads = 256;
+static constexpr unsigned kEqLoBits = 12;
+
+static inline unsigned clog2(size_t n) {
+    unsigned r = 0;
+    if (n == 0) return 0;
+    --n;
+    while (n) { n >>= 1; ++r; }
+    return r;
+}
+static inline Fr dev_fr(const hfr::H& h) {
+    Fr r;
+    memcpy(r.v, h.l, 32);
+    return r;
+}
+static inline Fr dev_fr_mont(const zkb_fr_t& x) { return dev_fr(hfr::to_mont(hfr::load(x))); }
+
+// eq weights for indices below 2^(kl+kh): lo table over the low kl bits, hi table
+// (may be null) over the rest; both in Montgomery form.
+struct EqTab {
+    const Fr* lo;
+    const Fr* hi;
+    unsigned kl;
+};
+
+// Builds the tables for the first `k` challenges of h_u.
+static int make_eq(const zkb_fr_t* h_u, unsigned k, EqTab* out, Scratch& scratch, cudaStream_t s) {
+    const unsigned kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
+    Fr* lo = scratch.get_n<Fr>((size_t)1 << kl);
+    if (!lo) return ZKB_ERR_CUDA;
+    ZKB_TRY(build_eq_table(h_u, kl, lo, s));
+    Fr* hi = nullptr;
+    if (kh) {
+        hi = scratch.get_n<Fr>((size_t)1 << kh);
+        if (!hi) return ZKB_ERR_CUDA;
+        ZKB_TRY(build_eq_table(h_u + kl, kh, hi, s));
+    }
+    out->lo = lo; out->hi = hi; out->kl = kl;
+    return ZKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// zkip round: pairs (g, g + half); sums of c0, c1, c2; folded outputs.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) zkip_round_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b,
+                                                               size_t n_in, size_t half, Fr v_mont,
+                                                               Fr* __restrict__ na, Fr* __restrict__ nb,
+                                                               Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[3];
+    acc[0] = acc[1] = acc[2] = fr_zero();
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < half; g += (size_t)gridDim.x * blockDim.x) {
+        const Fr a0 = g < n_in ? fr_load(a + g) : fr_zero();
+        const Fr b0 = g < n_in ? fr_load(b + g) : fr_zero();
+        const Fr a1 = g + half < n_in ? fr_load(a + g + half) : fr_zero();
+        const Fr b1 = g + half < n_in ? fr_load(b + g + half) : fr_zero();
+        const Fr da = fr_sub(a1, a0), db = fr_sub(b1, b0);
+        const Fr t0 = fr_mmul(a0, b0), t2 = fr_mmul(da, db);
+        // a0*db + b0*da = a1*b1 - a0*b0 - da*db
+        const Fr t1 = fr_sub(fr_sub(fr_mmul(a1, b1), t0), t2);
+        acc[0] = fr_add(acc[0], t0);
+        acc[1] = fr_add(acc[1], t1);
+        acc[2] = fr_add(acc[2], t2);
+        fr_store(na + g, fr_add(a0, fr_mmul(v_mont, da)));
+        fr_store(nb + g, fr_add(b0, fr_mmul(v_mont, db)));
+    }
+    grid_sum_finish<3>(acc, partial, ticket, out, 0x7u, red);
+}
+
+// Queues all rounds of zkip on `s`.  d_polys receives 3 Fr per round.  The final
+// folded scalars are not needed by the protocol and are dropped.
+static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h_u, unsigned k,
+                       Fr* d_polys, Scratch& scratch, cudaStream_t s) {
+    if (k == 0) return ZKB_OK;
+    const unsigned kn = clog2(n);
+    if (k > kn) return fail(ZKB_ERR_DIM, "zkip: more challenges than variables");
+    size_t half = ((size_t)1 << kn) >> 1;
+    Fr* buf[2][2];
+    for (int i = 0; i < 2; ++i)
+        for (int j = 0; j < 2; ++j) {
+            buf[i][j] = scratch.get_n<Fr>(half >> i ? half >> i : 1);
+            if (!buf[i][j]) return ZKB_ERR_CUDA;
+        }
+    const unsigned max_grid = grid_for(half, kThreads, 4);
+    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    if (!partial || !ticket) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    const Fr* ca = d_a;
+    const Fr* cb = d_b;
+    size_t n_in = n;
+    for (unsigned r = 0; r < k; ++r) {
+        const Fr v = dev_fr_mont(h_u[k - 1 - r]);
+        Fr* oa = buf[r & 1][0];
+        Fr* ob = buf[r & 1][1];
+        ZKB_LAUNCH(zkip_round_kernel, grid_for(half, kThreads, 4), kThreads, 0, s,
+                   ca, cb, n_in, half, v, oa, ob, partial, ticket, d_polys + 3 * r);
+        ca = oa; cb = ob;
+        n_in = half;
+        half >>= 1;
+    }
+    return ZKB_OK;
+}
+
+// Host replay of the verifier checks of zkip (zkfc.cu:140-151).
+static int zkip_verify(const zkb_fr_t* h_claim, const zkb_fr_t* h_u, unsigned k, const zkb_fr_t* polys, zkb_fr_t* h_final) {
+    hfr::H claim = hfr::load(*h_claim);
+    for (unsigned r = 0; r < k; ++r) {
+        hfr::H c[3] = {hfr::load(polys[3 * r]), hfr::load(polys[3 * r + 1]), hfr::load(polys[3 * r + 2])};
+        hfr::H p0 = c[0];
+        hfr::H p1 = hfr::add(hfr::add(c[0], c[1]), c[2]);
+        if (!hfr::eq(claim, hfr::add(p0, p1))) return fail(ZKB_ERR_VERIFY, "claim != p(0) + p(1)");
+        claim = hfr::poly_eval(c, 3, hfr::load(h_u[k - 1 - r]));
+    }
+    *h_final = hfr::store(claim);
+    return ZKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// tLookup rounds
+// ---------------------------------------------------------------------------
+// Phase-1 round on (A, S) of size 2*half (tlookup.cu:74-109, 184-200).
+// sums: [0..2] eq-weighted coefficients of (A0 + A1 t)(S0 + beta + S1 t) (without
+// the alpha factor, applied on the host), [3] sum A0, [4] sum A1.
+__global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S, size_t half,
+                                                              Fr beta, Fr v_mont, EqTab eq,
+                                                              Fr* __restrict__ nA, Fr* __restrict__ nS,
+                                                              Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[5];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) acc[i] = fr_zero();
+    const size_t L = (size_t)1 << eq.kl;
+    const size_t nchunks = (half + L - 1) >> eq.kl;
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        Fr q0 = fr_zero(), q1 = fr_zero(), q2 = fr_zero();
+        const size_t base = c << eq.kl;
+        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
+            const size_t i = base + j;
+            const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
+            const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
+            const Fr e = fr_load(eq.lo + j);
+            const Fr c01 = fr_sub(a1, a0), c10 = fr_add(s0, beta), c11 = fr_sub(s1, s0);
+            const Fr e00 = fr_mmul(a0, e), e01 = fr_mmul(c01, e);
+            const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+            const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+            q0 = fr_add(q0, t0); q1 = fr_add(q1, t1); q2 = fr_add(q2, t2);
+            acc[3] = fr_add(acc[3], a0);
+            acc[4] = fr_add(acc[4], c01);
+            fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
+            fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
+        }
+        if (eq.hi) {
+            const Fr eh = fr_load(eq.hi + c);
+            q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
+        }
+        acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
+    }
+    grid_sum_finish<5>(acc, partial, ticket, out, 0x7u, red);
+}
+
+// Phase-2 round on (A, S, B, T, m) of size 2*half (tlookup.cu:161-279).
+// sums: [0..2] eq-weighted (A,S) coefficients, [3..5] eq-weighted (B,T)
+// coefficients, [6] sum A0, [7] sum A1, [8..10] coefficients of (m0 + m1 t)(B0 + B1 t).
+__global__ void __launch_bounds__(kThreads) tl_phase2_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S,
+                                                              const Fr* __restrict__ Bv, const Fr* __restrict__ T,
+                                                              const Fr* __restrict__ m, size_t half,
+                                                              Fr beta, Fr v_mont, EqTab eq,
+                                                              Fr* __restrict__ nA, Fr* __restrict__ nS, Fr* __restrict__ nB,
+                                                              Fr* __restrict__ nT, Fr* __restrict__ nm,
+                                                              Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[11];
+#pragma unroll
+    for (int i = 0; i < 11; ++i) acc[i] = fr_zero();
+    const size_t L = (size_t)1 << eq.kl;
+    const size_t nchunks = (half + L - 1) >> eq.kl;
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        Fr q[6];
+#pragma unroll
+        for (int i = 0; i < 6; ++i) q[i] = fr_zero();
+        const size_t base = c << eq.kl;
+        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
+            const size_t i = base + j;
+            const Fr e = fr_load(eq.lo + j);
+            {
+                const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
+                const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
+                const Fr c01 = fr_sub(a1, a0), c10 = fr_add(s0, beta), c11 = fr_sub(s1, s0);
+                const Fr e00 = fr_mmul(a0, e), e01 = fr_mmul(c01, e);
+                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+                q[0] = fr_add(q[0], t0); q[1] = fr_add(q[1], t1); q[2] = fr_add(q[2], t2);
+                acc[6] = fr_add(acc[6], a0);
+                acc[7] = fr_add(acc[7], c01);
+                fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
+                fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
+            }
+            {
+                const Fr b0 = fr_load(Bv + i), b1 = fr_load(Bv + i + half);
+                const Fr t0_ = fr_load(T + i), t1_ = fr_load(T + i + half);
+                const Fr m0 = fr_load(m + i), m1f = fr_load(m + i + half);
+                const Fr c01 = fr_sub(b1, b0), c10 = fr_add(t0_, beta), c11 = fr_sub(t1_, t0_);
+                const Fr e00 = fr_mmul(b0, e), e01 = fr_mmul(c01, e);
+                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+                q[3] = fr_add(q[3], t0); q[4] = fr_add(q[4], t1); q[5] = fr_add(q[5], t2);
+                const Fr m1 = fr_sub(m1f, m0);
+                const Fr d0 = fr_mmul(m0, b0), d2 = fr_mmul(m1, c01);
+                const Fr d1 = fr_sub(fr_sub(fr_mmul(m1f, b1), d0), d2);
+                acc[8] = fr_add(acc[8], d0); acc[9] = fr_add(acc[9], d1); acc[10] = fr_add(acc[10], d2);
+                fr_store(nB + i, fr_add(b0, fr_mmul(v_mont, c01)));
+                fr_store(nT + i, fr_add(t0_, fr_mmul(v_mont, c11)));
+                fr_store(nm + i, fr_add(m0, fr_mmul(v_mont, m1)));
+            }
+        }
+        if (eq.hi) {
+            const Fr eh = fr_load(eq.hi + c);
+#pragma unroll
+            for (int t = 0; t < 6; ++t) q[t] = fr_mmul(q[t], eh);
+        }
+#pragma unroll
+        for (int t = 0; t < 6; ++t) acc[t] = fr_add(acc[t], q[t]);
+    }
+    grid_sum_finish<11>(acc, partial, ticket, out, 0x73Fu, red);
+}
+
+// out[0] = sum a[i]*b[i].  fix = 1 when both operands are standard-form tensor
+// values, 0 when b is a Montgomery-form table.
+__global__ void __launch_bounds__(kThreads) fr_dot_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n,
+                                                           Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out,
+                                                           unsigned fix) {
+    __shared__ Fr red[32];
+    Fr acc[1];
+    acc[0] = fr_zero();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        acc[0] = fr_add(acc[0], fr_mmul(fr_load(a + i), fr_load(b + i)));
+    grid_sum_finish<1>(acc, partial, ticket, out, fix, red);
+}
+
+__global__ void tl_count_kernel(const uint32_t* __restrict__ idx, size_t D, size_t N, uint32_t* __restrict__ counts) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < D; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t k = idx[i];
+        if (k < N) atomicAdd(counts + k, 1u);
+    }
+}
+__global__ void tl_counts_to_fr_kernel(const uint32_t* __restrict__ counts, size_t N, Fr* __restrict__ m) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < N; i += (size_t)gridDim.x * blockDim.x)
+        fr_store(m + i, fr_from_u64(counts[i]));
+}
+__global__ void tl_range_indices_kernel(const Fr* __restrict__ vals, Fr low, uint32_t* __restrict__ idx, size_t D) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < D; i += (size_t)gridDim.x * blockDim.x)
+        idx[i] = fr_sub(fr_load(vals + i), low).v[0];
+}
+__global__ void tl_range_table_kernel(int low, size_t len, size_t size, Fr* __restrict__ table) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < size; i += (size_t)gridDim.x * blockDim.x) {
+        const int val = (i < len) ? static_cast<int>(i) + low : static_cast<int>(len) + low - 1;
+        fr_store(table + i, fr_from_i64(val));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// multi-Hadamard round (proof.cu:172-241): K arrays of size 2*half.
+// sums: K+1 eq-weighted coefficients of prod_k (X0_k + X1_k t).
+// ---------------------------------------------------------------------------
+static constexpr int kMaxHadamard = 6;
+struct HadamardPtrs {
+    const Fr* in[kMaxHadamard];
+    Fr* out[kMaxHadamard];
+};
+template <int K>
+__global__ void __launch_bounds__(kThreads) hadamard_round_kernel(HadamardPtrs p, size_t half, Fr v_mont, EqTab eq,
+                                                                   Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[K + 1];
+#pragma unroll
+    for (int i = 0; i <= K; ++i) acc[i] = fr_zero();
+    const size_t L = (size_t)1 << eq.kl;
+    const size_t nchunks = (half + L - 1) >> eq.kl;
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        Fr q[K + 1];
+#pragma unroll
+        for (int i = 0; i <= K; ++i) q[i] = fr_zero();
+        const size_t base = c << eq.kl;
+        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
+            const size_t i = base + j;
+            // Running product polynomial.  It starts as e*R (Montgomery form); the
+            // first multiplication by a standard-form value gives e*x exactly and
+            // every further one adds a factor 1/R, removed after the grid sum.
+            Fr poly[K + 1];
+            poly[0] = fr_load(eq.lo + j);
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const Fr x0 = fr_load(p.in[k] + i), x1f = fr_load(p.in[k] + i + half);
+                const Fr x1 = fr_sub(x1f, x0);
+                fr_store(p.out[k] + i, fr_add(x0, fr_mmul(v_mont, x1)));
+                // poly *= (x0 + x1 t)
+                poly[k + 1] = fr_mmul(poly[k], x1);
+#pragma unroll
+                for (int d = k; d >= 1; --d) poly[d] = fr_add(fr_mmul(poly[d], x0), fr_mmul(poly[d - 1], x1));
+                poly[0] = fr_mmul(poly[0], x0);
+            }
+#pragma unroll
+            for (int d = 0; d <= K; ++d) q[d] = fr_add(q[d], poly[d]);
+        }
+        if (eq.hi) {
+            const Fr eh = fr_load(eq.hi + c);
+#pragma unroll
+            for (int d = 0; d <= K; ++d) q[d] = fr_mmul(q[d], eh);
+        }
+#pragma unroll
+        for (int d = 0; d <= K; ++d) acc[d] = fr_add(acc[d], q[d]);
+    }
+    // every coefficient is e * (product of K standard values) / R^(K-1)
+    grid_sum_finish<K + 1>(acc, partial, ticket, out, (1u << (K + 1)) - 1u, red, K - 1);
+}
+
+// ---------------------------------------------------------------------------
+// legacy adjacent-pair rounds (proof.cu:12-160).  Pairs (2g, 2g+1); the product
+// terms keep the factor 1/R that the reference leaves on them.
+// MODE 0: inner product (plain sums)   MODE 1: Hadamard (eq-weighted)   MODE 2: binary
+// ---------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) legacy_round_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b,
+                                                                 size_t n_in, size_t n_out, Fr v_mont, EqTab eq,
+                                                                 Fr* __restrict__ na, Fr* __restrict__ nb,
+                                                                 Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[3];
+    acc[0] = acc[1] = acc[2] = fr_zero();
+    const size_t L = (size_t)1 << eq.kl;
+    const size_t nchunks = (n_out + L - 1) >> eq.kl;
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        Fr q0 = fr_zero(), q1 = fr_zero(), q2 = fr_zero();
+        const size_t base = c << eq.kl;
+        for (size_t j = threadIdx.x; j < L && base + j < n_out; j += blockDim.x) {
+            const size_t g = base + j;
+            const Fr a0 = fr_load(a + 2 * g);
+            const Fr a1 = (2 * g + 1 < n_in) ? fr_load(a + 2 * g + 1) : fr_zero();
+            const Fr da = fr_sub(a1, a0);
+            Fr t0, t1, t2;
+            if (MODE == 2) {
+                t0 = fr_sub(fr_mmul(a0, a0), a0);
+                t1 = fr_sub(fr_mmul(fr_add(a0, a0), da), da);
+                t2 = fr_mmul(da, da);
+            } else {
+                const Fr b0 = fr_load(b + 2 * g);
+                const Fr b1 = (2 * g + 1 < n_in) ? fr_load(b + 2 * g + 1) : fr_zero();
+                const Fr db = fr_sub(b1, b0);
+                t0 = fr_mmul(a0, b0);
+                t1 = fr_add(fr_mmul(a0, db), fr_mmul(b0, da));
+                t2 = fr_mmul(da, db);
+                fr_store(nb + g, fr_add(b0, fr_mmul(v_mont, db)));
+            }
+            fr_store(na + g, fr_add(a0, fr_mmul(v_mont, da)));
+            if (MODE != 0) {
+                const Fr e = fr_load(eq.lo + j);
+                t0 = fr_mmul(t0, e); t1 = fr_mmul(t1, e); t2 = fr_mmul(t2, e);
+            }
+            q0 = fr_add(q0, t0); q1 = fr_add(q1, t1); q2 = fr_add(q2, t2);
+        }
+        if (MODE != 0 && eq.hi) {
+            const Fr eh = fr_load(eq.hi + c);
+            q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
+        }
+        acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
+    }
+    grid_sum_finish<3>(acc, partial, ticket, out, 0u, red);
+}
+
+template <int MODE>
+static int legacy_sumcheck(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                           unsigned k, zkb_fr_t* h_proof, cudaStream_t s) {
+    if (k > 32) return fail(ZKB_ERR_LIMIT, "sumcheck: more than 32 variables");
+    const size_t full = (size_t)1 << k;
+    if (n == 0 || n <= full / 2 || n > full) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    Scratch scratch(s);
+    const size_t half0 = (n + 1) / 2;
+    Fr* buf[2][2];
+    for (int i = 0; i < 2; ++i)
+        for (int j = 0; j < 2; ++j) {
+            buf[i][j] = scratch.get_n<Fr>(half0);
+            if (!buf[i][j]) return ZKB_ERR_CUDA;
+        }
+    const unsigned max_grid = grid_for((half0 + 4095) / 4096, 1, 4);
+    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    const size_t n_out_vals = 3 * (size_t)k + 2;
+    Fr* d_proof = scratch.get_n<Fr>(n_out_vals);
+    if (!partial || !ticket || !d_proof) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    const Fr* ca = d_a;
+    const Fr* cb = d_b;
+    size_t n_in = n;
+    for (unsigned r = 0; r < k; ++r) {
+        const size_t n_out = (n_in + 1) / 2;
+        EqTab eq = {nullptr, nullptr, 0};
+        if (MODE != 0) {
+            // u_ = u[r+1 .. k): k-1-r variables; the reference requires the
+            // half-size arrays to fit them exactly
+            const unsigned kk = k - 1 - r;
+            const size_t f = (size_t)1 << kk;
+            if (n_out <= f / 2 || n_out > f) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+            ZKB_TRY(make_eq(h_u + r + 1, kk, &eq, scratch, s));
+        } else {
+            eq.kl = kEqLoBits;
+        }
+        const Fr v = dev_fr_mont(MODE == 0 ? h_u[r] : h_v[r]);
+        const size_t nchunks = (n_out + ((size_t)1 << eq.kl) - 1) >> eq.kl;
+        ZKB_LAUNCH(legacy_round_kernel<MODE>, grid_for(nchunks, 1, 4), kThreads, 0, s,
+                   ca, cb, n_in, n_out, v, eq, buf[r & 1][0], buf[r & 1][1], partial, ticket, d_proof + 3 * r);
+        ca = buf[r & 1][0];
+        cb = buf[r & 1][1];
+        n_in = n_out;
+    }
+    // trailing a(0) [, b(0)]
+    ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k, ca, 32, cudaMemcpyDeviceToDevice, s));
+    if (MODE != 2) ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k + 1, cb, 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_proof, d_proof, 32 * (MODE == 2 ? 3 * (size_t)k + 1 : n_out_vals), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+}  // namespace zkb
+
+using namespace zkb;
+#define FR(p) reinterpret_cast<Fr*>(p)
+#define CFR(p) reinterpret_cast<const Fr*>(p)
+
+extern "C" {
+
+int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+             const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k == 0) { *h_final = *h_claim; return ZKB_OK; }
+    if (n == 0) return fail(ZKB_ERR_DIM, "zkip: empty input");
+    Scratch scratch(s);
+    Fr* d_polys = scratch.get_n<Fr>(3 * (size_t)k);
+    if (!d_polys) return ZKB_ERR_CUDA;
+    ZKB_TRY(zkip_device(CFR(d_a), CFR(d_b), n, h_u, k, d_polys, scratch, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_polys, d_polys, 96 * (size_t)k, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return zkip_verify(h_claim, h_u, k, h_polys, h_final);
+}
+
+int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y,
+                   size_t B, size_t I, size_t O,
+                   const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
+                   zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (!B || !I || !O) return fail(ZKB_ERR_DIM, "zkFC::prove: empty dimension");
+    const unsigned kB = clog2(B), kI = clog2(I), kO = clog2(O);
+    Scratch scratch(s);
+    // results gathered on the device: [claim, claim_X, claim_W, polys...]
+    Fr* d_res = scratch.get_n<Fr>(3 + 3 * (size_t)kI);
+    Fr* y_rows = scratch.get_n<Fr>(B);
+    Fr* x_red = scratch.get_n<Fr>(I);
+    Fr* w_red = scratch.get_n<Fr>(I);
+    Fr* E_b = scratch.get_n<Fr>((size_t)1 << kB);
+    Fr* E_in = scratch.get_n<Fr>((size_t)1 << kI);
+    if (!d_res || !y_rows || !x_red || !w_red || !E_b || !E_in) return ZKB_ERR_CUDA;
+    ZKB_TRY(build_eq_table(h_u_batch, kB, E_b, s));
+    ZKB_TRY(build_eq_table(h_u_input, kI, E_in, s));
+    // claim = Y(u_batch, u_output): row dots with eq(u_output), then eq(u_batch)
+    if (kO) ZKB_TRY(partial_me_device(CFR(d_Y), B * O, B, O, 1, h_u_output, kO, y_rows, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(y_rows, d_Y, B * 32, cudaMemcpyDeviceToDevice, s));
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    Fr* partial = scratch.get_n<Fr>((size_t)sm_count() * 4);
+    if (!ticket || !partial) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(B, kThreads, 4), kThreads, 0, s, y_rows, E_b, B, partial, ticket, d_res + 0, 0u);
+    // X_red = eq(u_batch)^T X ; W_red = W eq(u_output)
+    if (kB) ZKB_TRY(partial_me_device(CFR(d_X), B * I, 1, B, I, h_u_batch, kB, x_red, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(x_red, d_X, I * 32, cudaMemcpyDeviceToDevice, s));
+    if (kO) ZKB_TRY(partial_me_device(CFR(d_W), I * O, I, O, 1, h_u_output, kO, w_red, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(w_red, d_W, I * 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_TRY(zkip_device(x_red, w_red, I, h_u_input, kI, d_res + 3, scratch, s));
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, x_red, E_in, I, partial, ticket, d_res + 1, 0u);
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, w_red, E_in, I, partial, ticket, d_res + 2, 0u);
+    std::vector<zkb_fr_t> res(3 + 3 * (size_t)kI);
+    ZKB_CUDA(cudaMemcpyAsync(res.data(), d_res, res.size() * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    for (size_t i = 0; i < 3 * (size_t)kI; ++i) h_polys[i] = res[3 + i];
+    h_claims[0] = res[0];
+    h_claims[2] = res[1];
+    h_claims[3] = res[2];
+    ZKB_TRY(zkip_verify(&res[0], h_u_input, kI, h_polys, &h_claims[1]));
+    const hfr::H prod = hfr::mul(hfr::load(res[1]), hfr::load(res[2]));
+    if (!hfr::eq(prod, hfr::load(h_claims[1]))) return fail(ZKB_ERR_VERIFY, "Claim does not match");
+    return ZKB_OK;
+}
+
+int zkb_tlookup_prep(const uint32_t* d_indices, size_t D, size_t N, zkb_fr_t* d_m, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (!N) return ZKB_OK;
+    Scratch scratch(s);
+    uint32_t* counts = scratch.get_n<uint32_t>(N);
+    if (!counts) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(counts, 0, N * 4, s));
+    if (D) ZKB_LAUNCH(tl_count_kernel, grid_for(D, kThreads), kThreads, 0, s, d_indices, D, N, counts);
+    ZKB_LAUNCH(tl_counts_to_fr_kernel, grid_for(N, kThreads), kThreads, 0, s, counts, N, FR(d_m));
+    return ZKB_OK;
+}
+int zkb_tlookup_range_indices(const zkb_fr_t* d_vals, int32_t low, uint32_t* d_indices, size_t D, void* stream) {
+    if (!D) return ZKB_OK;
+    hfr::H l = low >= 0 ? hfr::from_u64((uint64_t)low) : hfr::neg(hfr::from_u64((uint64_t)(-(int64_t)low)));
+    ZKB_LAUNCH(tl_range_indices_kernel, grid_for(D, kThreads), kThreads, 0, as_stream(stream), CFR(d_vals), dev_fr(l), d_indices, D);
+    return ZKB_OK;
+}
+int zkb_tlookup_range_table(int32_t low, size_t len, size_t table_size, zkb_fr_t* d_table, void* stream) {
+    if (!table_size) return ZKB_OK;
+    ZKB_LAUNCH(tl_range_table_kernel, grid_for(table_size, kThreads), kThreads, 0, as_stream(stream), (int)low, len, table_size, FR(d_table));
+    return ZKB_OK;
+}
+
+int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
+                      size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                      const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                      zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
+        return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
+    const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN;
+    if (kD > 32) return fail(ZKB_ERR_LIMIT, "tLookup: D above 2^32");
+    Scratch scratch(s);
+    // working arrays: A (D), then ping-pong halves
+    Fr* A = scratch.get_n<Fr>(D);
+    Fr* Bv = scratch.get_n<Fr>(N);
+    if (!A || !Bv) return ZKB_ERR_CUDA;
+    ZKB_TRY(zkb_fr_inv_shifted(d_S, h_beta, reinterpret_cast<zkb_fr_t*>(A), D, stream));
+    ZKB_TRY(zkb_fr_inv_shifted(d_table, h_beta, reinterpret_cast<zkb_fr_t*>(Bv), N, stream));
+    const size_t half0 = D > 1 ? D / 2 : 1;
+    Fr* pp[2][5];
+    for (int i = 0; i < 2; ++i)
+        for (int j = 0; j < 5; ++j) {
+            // A,S halves shrink from D/2; B,T,m from N/2
+            const size_t sz = j < 2 ? (half0 >> i ? half0 >> i : 1) : ((N / 2) >> i ? (N / 2) >> i : 1);
+            pp[i][j] = scratch.get_n<Fr>(sz);
+            if (!pp[i][j]) return ZKB_ERR_CUDA;
+        }
+    const unsigned max_grid = (unsigned)sm_count() * 4;
+    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 11);
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    Fr* d_sums = scratch.get_n<Fr>(1 + 11 * (size_t)kD);
+    if (!partial || !ticket || !d_sums) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    // sum B*m
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(N, kThreads, 4), kThreads, 0, s, Bv, CFR(d_m), N, partial, ticket, d_sums, 1u);
+    const Fr beta = dev_fr(hfr::load(*h_beta));
+    const Fr* cA = A;
+    const Fr* cS = CFR(d_S);
+    const Fr* cB = Bv;
+    const Fr* cT = CFR(d_table);
+    const Fr* cm = CFR(d_m);
+    size_t M = D;
+    unsigned nu = kD;   // challenges of u still unbound
+    for (unsigned r = 0; r < kD; ++r) {
+        const size_t half = M / 2;
+        EqTab eq;
+        ZKB_TRY(make_eq(h_u, nu - 1, &eq, scratch, s));
+        const size_t nchunks = (half + ((size_t)1 << eq.kl) - 1) >> eq.kl;
+        const unsigned grid = grid_for(nchunks, 1, 4);
+        Fr* out = d_sums + 1 + 11 * (size_t)r;
+        const int pb = r & 1;
+        if (r < k1) {
+            const Fr v = dev_fr_mont(h_v[k1 - 1 - r]);
+            ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq,
+                       pp[pb][0], pp[pb][1], partial, ticket, out);
+            cA = pp[pb][0]; cS = pp[pb][1];
+        } else {
+            const Fr v = dev_fr_mont(h_v[kD - 1 - (r - k1)]);
+            const int qb = (r - k1) & 1;   // B, T, m start shrinking at the first phase-2 round
+            ZKB_LAUNCH(tl_phase2_kernel, grid, kThreads, 0, s, cA, cS, cB, cT, cm, half, beta, v, eq,
+                       pp[pb][0], pp[pb][1], pp[qb][2], pp[qb][3], pp[qb][4], partial, ticket, out);
+            cA = pp[pb][0]; cS = pp[pb][1]; cB = pp[qb][2]; cT = pp[qb][3]; cm = pp[qb][4];
+        }
+        M = half;
+        --nu;
+    }
+    std::vector<zkb_fr_t> sums(1 + 11 * (size_t)kD);
+    ZKB_CUDA(cudaMemcpyAsync(sums.data(), d_sums, sums.size() * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+
+    // ---- host: assemble the round polynomials and replay the checks -------------
+    using hfr::H;
+    const H alpha0 = hfr::load(*h_alpha);
+    const H two_inv = hfr::inv(hfr::from_u64(2));
+    H alpha = alpha0;
+    H alpha_sq = hfr::mul(alpha0, alpha0);
+    H C = hfr::sub(alpha_sq, hfr::load(sums[0]));
+    H claim = hfr::add(alpha0, alpha_sq);
+    const H inv_ratio = hfr::mul(hfr::from_u64(N), hfr::inv(hfr::from_u64(D)));
+    nu = kD;
+    for (unsigned r = 0; r < kD; ++r) {
+        const zkb_fr_t* q = &sums[1 + 11 * (size_t)r];
+        const H ub = hfr::load(h_u[nu - 1]);
+        const H e0 = hfr::sub(hfr::from_u64(1), ub);                 // eq(u)(t) = e0 + e1 t
+        const H e1 = hfr::sub(hfr::add(ub, ub), hfr::from_u64(1));
+        H p0[3], p[4];
+        H vb;
+        if (r < k1) {
+            for (int i = 0; i < 3; ++i) p0[i] = hfr::mul(alpha, hfr::load(q[i]));
+            vb = hfr::load(h_v[k1 - 1 - r]);
+        } else {
+            const H coefB = hfr::mul(inv_ratio, alpha_sq);
+            for (int i = 0; i < 3; ++i)
+                p0[i] = hfr::add(hfr::mul(alpha, hfr::load(q[i])), hfr::mul(coefB, hfr::load(q[3 + i])));
+            vb = hfr::load(h_v[kD - 1 - (r - k1)]);
+        }
+        // p0 * eq
+        p[0] = hfr::mul(p0[0], e0);
+        p[1] = hfr::add(hfr::mul(p0[1], e0), hfr::mul(p0[0], e1));
+        p[2] = hfr::add(hfr::mul(p0[2], e0), hfr::mul(p0[1], e1));
+        p[3] = hfr::mul(p0[2], e1);
+        if (r < k1) {
+            p[0] = hfr::add(hfr::add(p[0], hfr::load(q[3])), hfr::mul(C, two_inv));
+            p[1] = hfr::add(p[1], hfr::load(q[4]));
+        } else {
+            p[0] = hfr::sub(hfr::add(p[0], hfr::load(q[6])), hfr::mul(hfr::load(q[8]), inv_ratio));
+            p[1] = hfr::sub(hfr::add(p[1], hfr::load(q[7])), hfr::mul(hfr::load(q[9]), inv_ratio));
+            p[2] = hfr::sub(p[2], hfr::mul(hfr::load(q[10]), inv_ratio));
+        }
+        for (int i = 0; i < 4; ++i) h_polys[4 * (size_t)r + i] = hfr::store(p[i]);
+        const H at1 = hfr::add(hfr::add(p[0], p[1]), hfr::add(p[2], p[3]));
+        if (!hfr::eq(claim, hfr::add(p[0], at1)))
+            return fail(ZKB_ERR_VERIFY, r < k1 ? "tLookup_phase1: claim != p(0) + p(1)" : "tLookup_phase2: claim != p(0) + p(1)");
+        claim = hfr::poly_eval(p, 4, vb);
+        const H e = hfr::eq_eval(ub, vb);
+        alpha = hfr::mul(alpha, e);
+        if (r < k1) C = hfr::mul(C, two_inv);
+        else alpha_sq = hfr::mul(alpha_sq, e);
+        --nu;
+    }
+    *h_final = hfr::store(claim);
+    return ZKB_OK;
+}
+
+int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,
+                       const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                       zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (K < 1 || K > (unsigned)kMaxHadamard) return fail(ZKB_ERR_LIMIT, "multi_hadamard: between 1 and 6 tensors");
+    if (N == 1) { *h_final = *h_claim; return ZKB_OK; }
+    if (N == 0 || (N & (N - 1))) return fail(ZKB_ERR_DIM, "N is not a power of 2");
+    const unsigned kN = clog2(N);
+    Scratch scratch(s);
+    Fr* bufs[2][kMaxHadamard];
+    for (int i = 0; i < 2; ++i)
+        for (unsigned j = 0; j < K; ++j) {
+            bufs[i][j] = scratch.get_n<Fr>((N / 2) >> i ? (N / 2) >> i : 1);
+            if (!bufs[i][j]) return ZKB_ERR_CUDA;
+        }
+    const unsigned max_grid = (unsigned)sm_count() * 4;
+    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * (K + 1));
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    Fr* d_sums = scratch.get_n<Fr>((size_t)kN * (K + 1));
+    if (!partial || !ticket || !d_sums) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    HadamardPtrs ptrs;
+    for (unsigned j = 0; j < K; ++j) ptrs.in[j] = CFR(h_d_Xs[j]);
+    size_t M = N;
+    for (unsigned r = 0; r < kN; ++r) {
+        const size_t half = M / 2;
+        EqTab eq;
+        ZKB_TRY(make_eq(h_u, kN - 1 - r, &eq, scratch, s));
+        for (unsigned j = 0; j < K; ++j) ptrs.out[j] = bufs[r & 1][j];
+        const Fr v = dev_fr_mont(h_v[kN - 1 - r]);
+        const size_t nchunks = (half + ((size_t)1 << eq.kl) - 1) >> eq.kl;
+        const unsigned grid = grid_for(nchunks, 1, 4);
+        Fr* out = d_sums + (size_t)r * (K + 1);
+        switch (K) {
+            case 1: ZKB_LAUNCH(hadamard_round_kernel<1>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            case 2: ZKB_LAUNCH(hadamard_round_kernel<2>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            case 3: ZKB_LAUNCH(hadamard_round_kernel<3>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            case 4: ZKB_LAUNCH(hadamard_round_kernel<4>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            case 5: ZKB_LAUNCH(hadamard_round_kernel<5>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            default: ZKB_LAUNCH(hadamard_round_kernel<6>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+        }
+        for (unsigned j = 0; j < K; ++j) ptrs.in[j] = bufs[r & 1][j];
+        M = half;
+    }
+    ZKB_CUDA(cudaMemcpyAsync(h_polys, d_sums, (size_t)kN * (K + 1) * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    using hfr::H;
+    H claim = hfr::load(*h_claim);
+    std::vector<H> c(K + 1);
+    for (unsigned r = 0; r < kN; ++r) {
+        for (unsigned i = 0; i <= K; ++i) c[i] = hfr::load(h_polys[(size_t)r * (K + 1) + i]);
+        const H ub = hfr::load(h_u[kN - 1 - r]);
+        const H e0 = hfr::sub(hfr::from_u64(1), ub);
+        const H e1 = hfr::sub(hfr::add(ub, ub), hfr::from_u64(1));
+        // (c * eq)(0) + (c * eq)(1) = c(0) e0 + c(1) (e0 + e1)
+        H c_at1 = hfr::zero();
+        for (unsigned i = 0; i <= K; ++i) c_at1 = hfr::add(c_at1, c[i]);
+        const H lhs = hfr::add(hfr::mul(c[0], e0), hfr::mul(c_at1, hfr::add(e0, e1)));
+        if (!hfr::eq(claim, lhs)) return fail(ZKB_ERR_VERIFY, "multi_hadamard_sumchecks: claim != p(0) + p(1)");
+        claim = hfr::poly_eval(c.data(), (int)K + 1, hfr::load(h_v[kN - 1 - r]));
+    }
+    *h_final = hfr::store(claim);
+    return ZKB_OK;
+}
+
+int zkb_hadamard_product_sumcheck(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+                                  const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned k,
+                                  zkb_fr_t* h_proof, void* stream) {
+    return legacy_sumcheck<1>(CFR(d_a), CFR(d_b), n, h_u, h_v, k, h_proof, as_stream(stream));
+}
+int zkb_inner_product_sumcheck(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
+                               const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_proof, void* stream) {
+    return legacy_sumcheck<0>(CFR(d_a), CFR(d_b), n, h_u, nullptr, k, h_proof, as_stream(stream));
+}
+int zkb_binary_sumcheck(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                        unsigned k, zkb_fr_t* h_proof, void* stream) {
+    return legacy_sumcheck<2>(CFR(d_a), CFR(d_a), n, h_u, h_v, k, h_proof, as_stream(stream));
+}
+
+}  // extern "C"
