@@ -56,10 +56,14 @@ def _p(x):
     if x is None:
         return ctypes.c_void_p(0)
     if isinstance(x, DeviceBuffer):
-        return ctypes.c_void_p(x.ptr)
+        c = ctypes.c_void_p(x.ptr)
+        c._keep = x          # the buffer must outlive the call even when passed as a temporary
+        return c
     if isinstance(x, np.ndarray):
         assert x.flags["C_CONTIGUOUS"]
-        return x.ctypes.data_as(ctypes.c_void_p)
+        c = x.ctypes.data_as(ctypes.c_void_p)
+        c._keep = x
+        return c
     if isinstance(x, int):
         return ctypes.c_void_p(x)
     raise TypeError(type(x))
