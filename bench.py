@@ -1,0 +1,329 @@
+"""Benchmark: Pedersen/Hyrax row commitment of a 4096 x 11008 fixed-point weight
+matrix over 11008 G1 generators (one 11008-point MSM per row), the configuration
+the G1-MSM throughput metric is quoted on.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference            # the reference's own build, same inputs
+
+One JSON line on stdout (rank 0).  `value` is device-timed throughput with inputs
+resident in HBM; `e2e` goes through the host-buffer C-ABI call with the copies
+inside the timed region.  Inputs are synthetic: int32 weights round(N(0,0.02)*2^16)
+from numpy PCG64, generators s_j*G with seeded s_j.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+R_MOD = 0x73EDA753299D7D483339D80809A1D80553BDA402FFFE5BFEFFFFFFFF00000001
+SEED = 0x5EED0000 + 2 * 16
+FQ_MULS_PER_MIXED_ADD = 11
+MADS_PER_FQ_MUL = 576          # 4 * 12^2 32-bit multiply-add instructions (product + Montgomery reduction)
+
+
+def weights(m: int, n: int, seed: int) -> np.ndarray:
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return np.rint(rng.standard_normal(m * n) * 0.02 * 65536).astype(np.int32)
+
+
+def generator_scalars(n: int) -> np.ndarray:
+    """(n, 8) uint32 standard-form Fr values below r (62-bit words, top word reduced)"""
+    rng = np.random.Generator(np.random.PCG64(SEED + 1))
+    vals = rng.integers(0, 1 << 32, size=(n, 8), dtype=np.uint64).astype(np.uint32)
+    vals[:, 7] %= np.uint32(R_MOD >> 224)
+    return vals
+
+
+class ClockSampler(threading.Thread):
+    """samples SM clocks and throttle reasons with nvidia-smi while the timed region runs"""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.rows = index, threading.Event(), []
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([t.strip() for t in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self) -> dict:
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for k, nm in enumerate(names) if any(len(r) > 2 + k and r[2 + k] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def g1_equal(z_norm_a: np.ndarray, z_norm_b: np.ndarray) -> bool:
+    return bool(np.array_equal(z_norm_a, z_norm_b))
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    z = load_package()
+    m, n = args.rows, args.cols
+    stream = torch.cuda.current_stream().cuda_stream
+    sp = z._p(stream)
+
+    # ---- inputs, resident in HBM -------------------------------------------------------
+    h_sc = torch.from_numpy(weights(m, n, SEED + 2 + 7 * rank)).pin_memory()
+    d_sc = h_sc.cuda(non_blocking=True)
+    gs = generator_scalars(n)
+    d_gs = torch.from_numpy(gs.view(np.int32)).cuda()
+    gen1 = np.zeros((1, 36), dtype=np.uint32)   # the G1 generator, Montgomery form, Z = R mod p
+    gx = 0x120177419E0BFB75EDCE6ECC21DBF440F0AE6ACDF3D0E747154F95C7143BA1C17817FC679976FFF55CB38790FD530C16
+    gy = 0x0BBC3EFC5008A26A0E1C8C3FAD0059C051AC582950405194DD595F13570725CE8C22631A7918FD8EBAAC93D50CE72271
+    gz = 0x15F65EC3FA80E4935C071A97A256EC6D77CE5853705257455F48985753C758BAEBF4000BC40C0002760900000002FFFD
+    for k, v in enumerate((gx, gy, gz)):
+        for i in range(12):
+            gen1[0, 12 * k + i] = (v >> (32 * i)) & 0xFFFFFFFF
+    d_gen1 = torch.from_numpy(gen1.view(np.int32)).cuda()
+    d_gens = torch.empty(n * 36, dtype=torch.int32, device="cuda")
+    z.call("zkb_g1_mul", z._p(d_gen1.data_ptr()), z.sz(1), z._p(d_gs.data_ptr()), z.sz(n), z._p(d_gens.data_ptr()), sp)
+    d_out = torch.empty(m * 36, dtype=torch.int32, device="cuda")
+    gathered = [torch.empty_like(d_out) for _ in range(world)] if world > 1 else None
+    torch.cuda.synchronize()
+
+    def step():
+        z.call("zkb_commit_i32", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_sc.data_ptr()), z.sz(m * n), z._p(d_out.data_ptr()), sp)
+        if world > 1:
+            dist.all_gather(gathered, d_out)     # the exchange step of a row-sharded commitment: m points per rank
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- device-timed region --------------------------------------------------------------
+    sampler = ClockSampler(local)
+    sampler.start()
+    z.call("zkb_profile_reset")
+    z.call("zkb_profile_enable", ctypes.c_int(1))
+    launches0 = z.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = z.launch_count() - launches0
+    z.call("zkb_profile_enable", ctypes.c_int(0))
+    buf = ctypes.create_string_buffer(1 << 16)
+    z.call("zkb_profile_read", buf, z.sz(len(buf)))
+    sampler.stop_flag.set()
+    sampler.join()
+    kernels = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split(",")
+        kernels[name] = (int(cnt), float(ms))
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * m * n / (ms_step * 1e-3) / 1e6
+
+    # ---- end to end through the host-buffer call -------------------------------------------
+    h_gens = torch.empty(n * 36, dtype=torch.int32).pin_memory()
+    h_gens.copy_(d_gens)
+    h_out = torch.empty(m * 36, dtype=torch.int32).pin_memory()
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        z.call("zkb_commit_i32_host", z._p(h_gens.data_ptr()), z.sz(n), z._p(h_sc.data_ptr()), z.sz(m * n), z._p(h_out.data_ptr()), sp)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_s = f0.elapsed_time(f1) * 1e-3 / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * m * n / e2e_s / 1e6, "unit": "Mpts/s", "h2d_bytes_per_step": int(n * 144 + m * n * 4),
+           "d2h_bytes_per_step": int(m * 144)}
+
+    result = None
+    if rank == 0:
+        # ---- correctness on a sample of rows (checker: CPU restatement) -------------------
+        from oracle import cpporacle as C
+        sample = sorted(set([0, 1, m // 2, m - 1]))
+        got = d_out.cpu().numpy().view(np.uint32).reshape(m, 36)
+        exp = C.commit_int(h_gens.numpy().view(np.uint32).reshape(n, 36), h_sc.numpy().reshape(m, n)[sample], "pippenger")
+        parity = g1_equal(C.g1_normalise(got[sample]), C.g1_normalise(exp))
+        e2e_ok = g1_equal(C.g1_normalise(h_out.numpy().view(np.uint32).reshape(m, 36)[sample]), C.g1_normalise(exp))
+
+        # ---- CPU baseline: same algorithm on the host cores, bounded sample ---------------
+        cores = C.threads()
+        rows_cpu = min(m, max(cores * 8, 64))
+        t0 = time.perf_counter()
+        C.commit_int(h_gens.numpy().view(np.uint32).reshape(n, 36), h_sc.numpy().reshape(m, n)[:rows_cpu], "pippenger")
+        cpu_s = time.perf_counter() - t0
+        cpu_baseline = {"value": rows_cpu * n / cpu_s / 1e6, "unit": "Mpts/s", "cores": cores, "kind": "port",
+                        "sample": f"first {rows_cpu} of {m} rows, signed-digit bucket MSM in C++ (oracle/zkoracle.cpp), OpenMP"}
+
+        # ---- roofline of the dominant kernel ------------------------------------------------
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        hbm_peak, peak_src = 6650.0, "fallback"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+            hbm_peak, peak_src = float(peaks.get("hbm_gbs", hbm_peak)), "measured"
+        imad = {}
+        for mode, nm in ((0, "mad_lo_u32"), (1, "mad_wide_u32"), (2, "madc_chain")):
+            g = ctypes.c_double(0.0)
+            z.call("zkb_bench_imad", ctypes.c_int(mode), ctypes.c_uint(4096), ctypes.byref(g), sp)
+            imad[nm] = g.value
+        dom_name = max(kernels, key=lambda k: kernels[k][1]) if kernels else None
+        dom_cnt, dom_ms = kernels.get(dom_name, (0, 0.0))
+        dom_launch_ms = dom_ms / max(dom_cnt, 1)
+        windows = 2 if int(np.abs(h_sc.numpy()).max()) < 8128 else 3
+        algo_bytes = m * n * 4 + n * 96 + m * windows * 64 * 144     # scalars + affine bases in, bucket sums out
+        achieved = algo_bytes / (dom_launch_ms * 1e-3) / 1e9 if dom_launch_ms else 0.0
+        algo_mads = m * n * windows * FQ_MULS_PER_MIXED_ADD * MADS_PER_FQ_MUL
+        ach_gmad = algo_mads / (dom_launch_ms * 1e-3) / 1e9 if dom_launch_ms else 0.0
+        roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
+                    "note": "kernel is bound by 32-bit multiply-add issue, not HBM: see int_pipe"}
+        int_pipe = {"kernel": dom_name, "achieved": ach_gmad, "peak": imad["madc_chain"], "unit": "G mad/s",
+                    "frac": ach_gmad / imad["madc_chain"] if imad["madc_chain"] else None,
+                    "peaks_measured": imad, "algorithmic_mads_per_point": windows * FQ_MULS_PER_MIXED_ADD * MADS_PER_FQ_MUL,
+                    "launch_ms": dom_launch_ms}
+        shares = {k: round(v[1] / sum(x[1] for x in kernels.values()), 4) for k, v in kernels.items()} if kernels else {}
+        result = {
+            "metric": "G1 MSM throughput (Pedersen/Hyrax row commitment)", "value": value, "unit": "Mpts/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": f"commit_int {m}x{n} int32 fixed-point weights over {n} G1 generators (BLS12-381), "
+                                   f"{windows} signed 7-bit windows", "rows_per_gpu": m, "generators": n,
+                       "l2": "inputs (172 MB of scalars per step) larger than L2, no flush needed"},
+            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
+            "roofline": roofline, "int_pipe": int_pipe, "cpu_baseline": cpu_baseline,
+            "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok),
+        }
+        if not (parity and e2e_ok):
+            result["error"] = "sampled rows differ from the CPU oracle"
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+def run_reference(args) -> dict:
+    """The reference's own build (oracle/_ref/ref_harness: its unmodified CUDA
+    sources, device-LTO) on the same inputs; without it, the reference's algorithm
+    restated on the host cores (oracle/zkoracle.cpp)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import cpporacle as C
+    m, n = args.rows, args.cols
+    sc = weights(m, n, SEED + 2)
+    gs = generator_scalars(n)
+    gen1 = np.zeros((n, 36), dtype=np.uint32)
+    gx = 0x120177419E0BFB75EDCE6ECC21DBF440F0AE6ACDF3D0E747154F95C7143BA1C17817FC679976FFF55CB38790FD530C16
+    gy = 0x0BBC3EFC5008A26A0E1C8C3FAD0059C051AC582950405194DD595F13570725CE8C22631A7918FD8EBAAC93D50CE72271
+    gz = 0x15F65EC3FA80E4935C071A97A256EC6D77CE5853705257455F48985753C758BAEBF4000BC40C0002760900000002FFFD
+    for k, v in enumerate((gx, gy, gz)):
+        for i in range(12):
+            gen1[:, 12 * k + i] = (v >> (32 * i)) & 0xFFFFFFFF
+    gens = C.g1_mul(gen1, gs)
+    harness = ROOT / "oracle" / "_ref" / "ref_harness"
+    base = {"metric": "G1 MSM throughput (Pedersen/Hyrax row commitment)", "unit": "Mpts/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic", "impl": "reference"}
+    have_gpu = subprocess.run(["nvidia-smi", "-L"], capture_output=True).returncode == 0
+    if harness.exists() and have_gpu:
+        with tempfile.TemporaryDirectory() as tmp:
+            gp, ip, op = Path(tmp) / "pp.bin", Path(tmp) / "w-int.bin", Path(tmp) / "com.bin"
+            gens.tofile(gp)
+            sc.tofile(ip)
+            res = subprocess.run([str(harness), "bench-commit", str(gp), str(ip), str(args.steps), str(args.warmup), str(op)],
+                                 capture_output=True, text=True, timeout=3000)
+            if res.returncode != 0:
+                return {**base, "unavailable": f"reference harness failed rc={res.returncode}: {res.stderr[-200:]!r}"}
+            times = [float(l.split()[1]) for l in res.stdout.splitlines() if l.startswith("step_s")]
+        s = sum(times) / len(times)
+        v = m * n / s / 1e6
+        return {**base, "value": v, "ms_per_step": s * 1e3,
+                "config": {"workload": f"commit_int {m}x{n} (reference Commitment::commit_int, its own CUDA kernels, sm_100 build)"},
+                "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": 0, "kind": "reference",
+                                 "sample": "full workload, reference CUDA build on the same GPU (the reference has no CPU path)"},
+                "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    cores = C.threads()
+    rows = min(m, max(cores, 16))
+    best = None
+    for _ in range(max(1, min(args.steps, 2))):
+        t0 = time.perf_counter()
+        C.commit_int(gens, sc.reshape(m, n)[:rows], "ref")
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    v = rows * n / best / 1e6
+    return {**base, "value": v, "ms_per_step": best * 1e3 * m / rows,
+            "config": {"workload": f"commit_int {m}x{n}: the reference's double-and-add algorithm on host cores, {rows}-row sample"},
+            "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": cores, "kind": "port",
+                             "sample": f"first {rows} of {m} rows (per-point 31-step double-and-add + row sum, commitment.cu:31-58)"},
+            "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=4096)
+    ap.add_argument("--cols", type=int, default=11008)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,19 @@ int zkb_version(void);
 /* Number of kernels this library has launched in the calling process. */
 unsigned long long zkb_launch_count(void);
 
+/* Per-kernel timing for benchmarks (no counterpart in the reference).  While
+ * enabled, every kernel launch of the library is bracketed by CUDA events on its
+ * stream.  zkb_profile_read synchronises the device and writes one line per
+ * kernel, "name,launches,total_ms\n", into buf. */
+int zkb_profile_enable(int on);
+int zkb_profile_reset(void);
+int zkb_profile_read(char* buf, size_t cap);
+
+/* Integer-pipe micro-benchmark (no counterpart in the reference): issue rate, in
+ * 10^9 instructions per second, of mode 0 = mad.lo.u32, 1 = mad.wide.u32,
+ * 2 = the mad.lo.cc/madc.hi.cc carry chains of the field multiplier. */
+int zkb_bench_imad(int mode, unsigned iters, double* h_gops, void* stream);
+
 /* ---- device memory (FrTensor/G1Tensor ctors, dtors, copies:
  *      fr-tensor.cu:158-179, g1-tensor.cu:40-60,123-152) ------------------------- */
 int zkb_malloc(void** d_ptr, size_t bytes);

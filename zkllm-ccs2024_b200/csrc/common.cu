@@ -3,6 +3,9 @@
 
 #include <atomic>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <vector>
 
 namespace zkb {
 
@@ -19,6 +22,27 @@ int fail(int code, const std::string& msg) {
 int cuda_fail(cudaError_t e, const char* what) {
     g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
     return ZKB_ERR_CUDA;
+}
+
+// ---- per-kernel timing ------------------------------------------------------------
+bool g_profile_on = false;
+namespace {
+struct ProfRec { std::string name; cudaEvent_t e0, e1; };
+std::vector<ProfRec> g_prof;
+std::mutex g_prof_mu;
+}  // namespace
+
+void profile_begin(const char* name, cudaStream_t s) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    ProfRec r;
+    r.name = name;
+    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+    cudaEventRecord(r.e0, s);
+    g_prof.push_back(r);
+}
+void profile_end(cudaStream_t s) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    if (!g_prof.empty()) cudaEventRecord(g_prof.back().e1, s);
 }
 
 int sm_count() {
@@ -62,6 +86,40 @@ extern "C" {
 const char* zkb_last_error(void) { return g_last_error.c_str(); }
 int zkb_version(void) { return 100; }
 unsigned long long zkb_launch_count(void) { return g_launches.load(); }
+
+int zkb_profile_enable(int on) {
+    g_profile_on = on != 0;
+    return ZKB_OK;
+}
+int zkb_profile_reset(void) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    g_prof.clear();
+    return ZKB_OK;
+}
+int zkb_profile_read(char* buf, size_t cap) {
+    if (!buf || cap == 0) return fail(ZKB_ERR_ARG, "zkb_profile_read: no buffer");
+    ZKB_CUDA(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    std::map<std::string, std::pair<unsigned long long, double>> agg;
+    for (auto& r : g_prof) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
+            auto& a = agg[r.name];
+            a.first += 1;
+            a.second += ms;
+        }
+    }
+    std::string out;
+    for (auto& kv : agg) {
+        char line[256];
+        snprintf(line, sizeof(line), "%s,%llu,%.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        out += line;
+    }
+    if (out.size() + 1 > cap) return fail(ZKB_ERR_LIMIT, "zkb_profile_read: buffer too small");
+    memcpy(buf, out.c_str(), out.size() + 1);
+    return ZKB_OK;
+}
 
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");

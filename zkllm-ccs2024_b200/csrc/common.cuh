@@ -37,10 +37,18 @@ int cuda_fail(cudaError_t e, const char* what);
 // Count of kernels launched by this library in this process (zkb_launch_count()).
 extern std::atomic<unsigned long long> g_launches;
 
+// Optional per-kernel timing (zkb_profile_*): when enabled every launch is
+// bracketed by two events on its stream.
+extern bool g_profile_on;
+void profile_begin(const char* name, cudaStream_t s);
+void profile_end(cudaStream_t s);
+
 // Launch + count + check.  Usage: ZKB_LAUNCH(kernel, grid, block, smem, stream, args...)
 #define ZKB_LAUNCH(kernel, grid, block, smem, stream, ...)                \
     do {                                                                  \
+        if (::zkb::g_profile_on) ::zkb::profile_begin(#kernel, (stream)); \
         kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);       \
+        if (::zkb::g_profile_on) ::zkb::profile_end((stream));            \
         ::zkb::g_launches.fetch_add(1, std::memory_order_relaxed);        \
         ZKB_LAUNCH_CHECK(#kernel);                                        \
     } while (0)
