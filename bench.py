@@ -113,13 +113,15 @@ def run_ours(args) -> dict:
     d_gens = torch.empty(n * 36, dtype=torch.int32, device="cuda")
     z.call("zkb_g1_mul", z._p(d_gen1.data_ptr()), z.sz(1), z._p(d_gs.data_ptr()), z.sz(n), z._p(d_gens.data_ptr()), sp)
     d_out = torch.empty(m * 36, dtype=torch.int32, device="cuda")
-    gathered = [torch.empty_like(d_out) for _ in range(world)] if world > 1 else None
+    if world > 1:
+        from zkllm_ccs2024_b200 import sharding
     torch.cuda.synchronize()
 
     def step():
         z.call("zkb_commit_i32", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_sc.data_ptr()), z.sz(m * n), z._p(d_out.data_ptr()), sp)
         if world > 1:
-            dist.all_gather(gathered, d_out)     # the exchange step of a row-sharded commitment: m points per rank
+            # the exchange step of a row-sharded commitment: every rank ends with all world*m points
+            sharding.all_gather_rows(d_out, world * m, 36)
 
     def barrier():
         if world > 1:

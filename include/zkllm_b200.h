@@ -124,9 +124,11 @@ int zkb_fr_mle_eval_2d(const zkb_fr_t* d_a, size_t d0, size_t d1,
                        zkb_fr_t* h_out, void* stream);
 
 /* ---- layout (fr-tensor.cu:800-828, 885-900) -------------------------------------- */
-/* one level of FrTensor::pad: [rows, last] -> [rows, last_padded] filled with pad_val */
+/* one level of FrTensor::pad (fr-tensor.cu:800-828): [rows, last] -> [rows, last_padded]
+ * filled with pad_val */
 int zkb_fr_pad_last(const zkb_fr_t* d_a, size_t rows, size_t last, size_t last_padded,
                     const zkb_fr_t* h_pad_val, zkb_fr_t* d_out, void* stream);
+/* FrTensor::transpose (fr-tensor.cu:885-900): [M, N] -> [N, M] */
 int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, void* stream);
 /* FrTensor::matmul / zkFC::operator() (fr-tensor.cu:831-881, zkfc.cu:44-58):
  * C[M,P] = A[M,N] * B[N,P] over Fr */
@@ -203,15 +205,16 @@ int zkb_softmax_shift(const zkb_fr_t* d_A, zkb_fr_t* d_shift, zkb_fr_t* d_out, s
 int zkb_softmax_decompose(const zkb_fr_t* d_X, const uint32_t* h_bs, unsigned K, zkb_fr_t* d_out,
                           size_t N, void* stream);
 
-/* ---- G1 tensors (g1-tensor.cu) ----------------------------------------------------- */
+/* ---- G1 tensors: fills, negation, elementwise and broadcast add/sub, affine lift
+ *      (g1-tensor.cu:61-375) -------------------------------------------------------------- */
 int zkb_g1_fill(zkb_g1_t* d_out, const zkb_g1_t* h_val, size_t n, void* stream);
 int zkb_g1_neg(const zkb_g1_t* d_a, zkb_g1_t* d_out, size_t n, void* stream);
 int zkb_g1_add(const zkb_g1_t* d_a, const zkb_g1_t* d_b, zkb_g1_t* d_out, size_t n, void* stream);
 int zkb_g1_sub(const zkb_g1_t* d_a, const zkb_g1_t* d_b, zkb_g1_t* d_out, size_t n, void* stream);
 int zkb_g1_add_scalar(const zkb_g1_t* d_a, const zkb_g1_t* h_x, zkb_g1_t* d_out, size_t n, void* stream);
 int zkb_g1_from_affine(const zkb_g1_affine_t* d_a, zkb_g1_t* d_out, size_t n, void* stream);
-/* Jacobian -> affine (X/Z^2, Y/Z^3), identity -> (0,0).  Not in the reference:
- * this is the normal form on which G1 results are compared. */
+/* Jacobian -> affine (X/Z^2, Y/Z^3), identity -> (0,0).  It has no counterpart in the
+ * reference: this is the normal form on which G1 results are compared. */
 int zkb_g1_to_affine(const zkb_g1_t* d_a, zkb_g1_affine_t* d_out, size_t n, void* stream);
 /* G1TensorJacobian::operator*(FrTensor) (g1-tensor.cu:445-480): out[i] = scalars[i] * g[i mod n_g] */
 int zkb_g1_mul(const zkb_g1_t* d_g, size_t n_g, const zkb_fr_t* d_scalars, size_t n, zkb_g1_t* d_out, void* stream);
@@ -229,11 +232,12 @@ int zkb_g1_mle_eval(const zkb_g1_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned
 int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
                    zkb_g1_t* d_out, void* stream);
 /* Same with the scalars given directly as int32 (the weight .bin format,
- * fileio_utils.py:4-12): skips the 8x larger Fr encoding. */
+ * fileio_utils.py:4-12; read by FrTensor::from_int_bin, fr-tensor.cu:226-236): skips the
+ * 8x larger Fr encoding. */
 int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
                    zkb_g1_t* d_out, void* stream);
-/* Host-buffer form of the same call: copies generators and int32 scalars in,
- * commits, copies the m Jacobian results out. */
+/* Host-buffer form of the same call - what commit-param.cu:12-28 does through files:
+ * copies generators and int32 scalars in, commits, copies the m Jacobian results out. */
 int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_scalars, size_t n_scalars,
                         zkb_g1_t* h_out, void* stream);
 /* Commitment::commit (commitment.cu:22-29): full-width scalars */

@@ -14,7 +14,8 @@ from pathlib import Path
 import numpy as np
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "lib" / "libzkllm_b200.so"
+# ZKLLM_B200_LIB selects another build of the same library (e.g. a tuning variant)
+LIB_PATH = Path(os.environ["ZKLLM_B200_LIB"]) if os.environ.get("ZKLLM_B200_LIB") else _HERE / "lib" / "libzkllm_b200.so"
 
 OK, ERR_CUDA, ERR_DIM, ERR_VERIFY, ERR_ARG, ERR_LIMIT = 0, -1, -2, -3, -4, -5
 

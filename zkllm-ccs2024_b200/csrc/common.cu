@@ -57,6 +57,21 @@ int sm_count() {
     return cached[dev];
 }
 
+// Keep freed scratch blocks cached in the device's stream-ordered pool: with the
+// default release threshold (0) the pool returns memory to the driver at every
+// synchronisation and the next call pays for mapping it again.
+static void ensure_pool_keeps_memory() {
+    static bool done[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+        unsigned long long thresh = ~0ull;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh);
+    }
+    done[dev] = true;
+}
+
 Scratch::~Scratch() {
     for (int i = 0; i < n_; ++i) cudaFreeAsync(blocks_[i], stream_);
 }
@@ -67,6 +82,7 @@ void* Scratch::get(size_t bytes) {
         return nullptr;
     }
     if (bytes == 0) bytes = 16;
+    ensure_pool_keeps_memory();
     void* p = nullptr;
     cudaError_t e = cudaMallocAsync(&p, bytes, stream_);
     if (e != cudaSuccess) {
@@ -123,18 +139,6 @@ int zkb_profile_read(char* buf, size_t cap) {
 
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");
-    static bool pool_ready = false;
-    if (!pool_ready) {
-        // keep freed scratch blocks cached in the stream-ordered pool instead of
-        // returning them to the driver at every synchronisation
-        int dev = 0;
-        cudaMemPool_t pool;
-        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
-            unsigned long long thresh = ~0ull;
-            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh);
-        }
-        pool_ready = true;
-    }
     ZKB_CUDA(cudaMalloc(d_ptr, bytes ? bytes : 16));
     return ZKB_OK;
 }

@@ -15,8 +15,12 @@ namespace zkb {
 struct __align__(16) G1Jac { Fq x, y, z; };   // 144 bytes
 struct __align__(16) G1Aff { Fq x, y; };      //  96 bytes; (0,0) encodes the identity
 
+#ifdef ZKB_FQ_NOINLINE
+__device__ __noinline__ static Fq fq_mul(const Fq& a, const Fq& b) { return mont_mul<FqParams>(a, b); }
+#else
 ZKB_DEV Fq fq_mul(const Fq& a, const Fq& b) { return mont_mul<FqParams>(a, b); }
-ZKB_DEV Fq fq_sqr(const Fq& a) { return mont_mul<FqParams>(a, a); }
+#endif
+ZKB_DEV Fq fq_sqr(const Fq& a) { return fq_mul(a, a); }
 ZKB_DEV Fq fq_add(const Fq& a, const Fq& b) { return fe_add<FqParams>(a, b); }
 ZKB_DEV Fq fq_sub(const Fq& a, const Fq& b) { return fe_sub<FqParams>(a, b); }
 ZKB_DEV Fq fq_dbl(const Fq& a) { return fe_add<FqParams>(a, a); }

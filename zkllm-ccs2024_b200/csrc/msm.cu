@@ -13,8 +13,8 @@
 //   3. per (row, column segment, window) a counting sort in shared memory
 //      groups the non-zero digits by bucket |d|;
 //   4. one warp accumulates bucket b of window w for 32 (row, segment) lists at
-//      a time - lanes walk lists of statistically equal length, so they stay
-//      in step - with mixed Jacobian+affine additions;
+//      a time with mixed Jacobian+affine additions; the lists of a bucket are
+//      ordered by length first, so the lanes of a warp stay in step;
 //   5. buckets are combined per row: sum_b b*B_b by running sums over groups
 //      of 8 buckets, then Horner over the windows.
 //
@@ -157,12 +157,48 @@ __global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ 
     }
 }
 
-// One warp per (32 consecutive lists, window, bucket).  blockIdx.x enumerates
-// (list group, window, bucket) with the bucket fastest.
+// One CTA per (window, bucket): orders the (row, segment) lists of that bucket by
+// decreasing length (in bins of 4 entries), so that the 32 lists a warp walks
+// in lockstep have nearly the same length and the longest lists start first.
+static constexpr unsigned kLenBins = kMaxSeg / 4 + 2;
+__global__ void __launch_bounds__(256) msm_schedule_kernel(const uint16_t* __restrict__ offs, MsmShape sh, size_t n_rs,
+                                                            uint32_t* __restrict__ perm) {
+    __shared__ unsigned hist[kLenBins];
+    const unsigned w = blockIdx.x / kBuckets, b = blockIdx.x % kBuckets;
+    for (unsigned i = threadIdx.x; i < kLenBins; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (size_t rs = threadIdx.x; rs < n_rs; rs += blockDim.x) {
+        const uint16_t* o = offs + (rs * sh.W + w) * (kBuckets + 1);
+        atomicAdd(&hist[(unsigned)(o[b + 1] - o[b]) >> 2], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {   // exclusive prefix from the longest bin down
+        unsigned run = 0;
+        for (int i = (int)kLenBins - 1; i >= 0; --i) {
+            const unsigned c = hist[i];
+            hist[i] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    uint32_t* out = perm + (size_t)blockIdx.x * n_rs;
+    for (size_t rs = threadIdx.x; rs < n_rs; rs += blockDim.x) {
+        const uint16_t* o = offs + (rs * sh.W + w) * (kBuckets + 1);
+        const unsigned pos = atomicAdd(&hist[(unsigned)(o[b + 1] - o[b]) >> 2], 1u);
+        out[pos] = (uint32_t)rs;
+    }
+}
+
+// One warp per (32 lists of similar length, window, bucket).  blockIdx.x
+// enumerates (list group, window, bucket) with the bucket fastest.
 static constexpr unsigned kAccWarps = 4;
-__global__ void __launch_bounds__(kAccWarps * 32) msm_accumulate_kernel(const G1Aff* __restrict__ bases, MsmShape sh,
+#ifndef ZKB_ACC_MINBLOCKS
+#define ZKB_ACC_MINBLOCKS 3
+#endif
+__global__ void __launch_bounds__(kAccWarps * 32, ZKB_ACC_MINBLOCKS) msm_accumulate_kernel(const G1Aff* __restrict__ bases, MsmShape sh,
                                                                          const uint16_t* __restrict__ ent,
                                                                          const uint16_t* __restrict__ offs,
+                                                                         const uint32_t* __restrict__ perm,
                                                                          G1Jac* __restrict__ buckets, size_t n_units) {
     const size_t unit = (size_t)blockIdx.x * kAccWarps + (threadIdx.x >> 5);
     if (unit >= n_units) return;
@@ -170,9 +206,9 @@ __global__ void __launch_bounds__(kAccWarps * 32) msm_accumulate_kernel(const G1
     const unsigned b = (unsigned)(unit % kBuckets);           // bucket index 0..63 <-> |digit| = b + 1
     const unsigned w = (unsigned)((unit / kBuckets) % sh.W);
     const size_t grp = unit / ((size_t)kBuckets * sh.W);
-    const size_t rs = grp * 32 + lane;
     const size_t n_rs = sh.m * sh.nseg;
-    if (rs >= n_rs) return;
+    if (grp * 32 + lane >= n_rs) return;
+    const size_t rs = perm[((size_t)w * kBuckets + b) * n_rs + grp * 32 + lane];
     const size_t list_id = rs * sh.W + w;
     const uint16_t* o = offs + list_id * (kBuckets + 1);
     const unsigned beg = o[b], end = o[b + 1];
@@ -280,7 +316,9 @@ static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t
     G1Jac* buckets = scratch.get_n<G1Jac>(n_lists * kBuckets);
     G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
     G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
-    if (!bases || !ent || !offs || !buckets || !Lg || !Gg) return ZKB_ERR_CUDA;
+    uint32_t* perm = scratch.get_n<uint32_t>((size_t)W * kBuckets * n_rs);
+    if (!bases || !ent || !offs || !buckets || !Lg || !Gg || !perm) return ZKB_ERR_CUDA;
+    if (n_rs > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
 
     ZKB_LAUNCH(g1_to_affine_simple_kernel, grid_for(n, 128), 128, 0, s, d_gens, bases, n);
     // rows go to gridDim.y in slices of at most 65535
@@ -297,7 +335,8 @@ static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t
     const size_t n_units = n_groups * W * kBuckets;
     const size_t acc_blocks = (n_units + kAccWarps - 1) / kAccWarps;
     if (acc_blocks > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
-    ZKB_LAUNCH(msm_accumulate_kernel, (unsigned)acc_blocks, kAccWarps * 32, 0, s, bases, sh, ent, offs, buckets, n_units);
+    ZKB_LAUNCH(msm_schedule_kernel, (unsigned)(W * kBuckets), 256, 0, s, offs, sh, n_rs, perm);
+    ZKB_LAUNCH(msm_accumulate_kernel, (unsigned)acc_blocks, kAccWarps * 32, 0, s, bases, sh, ent, offs, perm, buckets, n_units);
     ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 128), 128, 0, s, buckets, sh, Lg, Gg);
     ZKB_LAUNCH(msm_finish_kernel, grid_for(m, 128), 128, 0, s, Lg, Gg, sh, d_out);
     return ZKB_OK;
