@@ -128,6 +128,10 @@ int zkb_fr_mle_eval_2d(const zkb_fr_t* d_a, size_t d0, size_t d1,
  * filled with pad_val */
 int zkb_fr_pad_last(const zkb_fr_t* d_a, size_t rows, size_t last, size_t last_padded,
                     const zkb_fr_t* h_pad_val, zkb_fr_t* d_out, void* stream);
+/* FrTensor::split (fr-tensor.cu:562-585): windows 0,2,4,.. go to d_out0 and 1,3,5,.. to
+ * d_out1 (out_n elements each, zero past the end of the input) */
+int zkb_fr_split_window(const zkb_fr_t* d_a, size_t n, size_t window, zkb_fr_t* d_out0, zkb_fr_t* d_out1,
+                        size_t out_n, void* stream);
 /* FrTensor::transpose (fr-tensor.cu:885-900): [M, N] -> [N, M] */
 int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, void* stream);
 /* FrTensor::matmul / zkFC::operator() (fr-tensor.cu:831-881, zkfc.cu:44-58):

@@ -63,5 +63,72 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+HOST = HERE / "host"
+HOST_SOURCES = ["ioutils", "fr-tensor", "polynomial", "g1-tensor", "commitment", "proof", "zkfc", "tlookup", "rescaling", "zksoftmax"]
+HOST_LIB = HERE / "lib" / "libzkllm_host.so"
+BIN = HERE / "bin"
+STAGES = ["ppgen", "commit-param", "rmsnorm", "self-attn", "ffn", "skip-connection"]
+HOST_CXX = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
+
+
+def _run(cmd):
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"{' '.join(map(str, cmd))} failed:\n{res.stdout}\n{res.stderr}")
+
+
+def build_host(force: bool = False) -> Path:
+    """The C++ classes with the reference's names (host/), as libzkllm_host.so, and
+    the stage driver bin/zkllm-driver with one symlink per stage name."""
+    out = BUILD / "host"
+    out.mkdir(parents=True, exist_ok=True)
+    BIN.mkdir(exist_ok=True)
+    newest_hdr = max(p.stat().st_mtime for p in list(HOST.glob("*.cuh")) + list(HOST.glob("*.hpp")) + [CSRC / "hostfr.hpp"])
+
+    def one(name):
+        src, obj = HOST / f"{name}.cpp", out / f"{name}.o"
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_hdr):
+            _run([HOST_CXX, "-std=c++17", "-O2", "-fPIC", "-Wall", "-c", str(src), "-o", str(obj)])
+        return str(obj)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(one, HOST_SOURCES))
+        drv = one("drivers")
+    _run([HOST_CXX, "-shared", "-o", str(HOST_LIB), *objs, f"-L{LIB.parent}", "-lzkllm_b200", "-Wl,-rpath,$ORIGIN"])
+    exe = BIN / "zkllm-driver"
+    _run([HOST_CXX, "-o", str(exe), drv, f"-L{LIB.parent}", "-lzkllm_host", "-lzkllm_b200", "-Wl,-rpath,$ORIGIN/../lib"])
+    for st in STAGES:
+        link = BIN / st
+        if link.is_symlink() or link.exists():
+            link.unlink()
+        link.symlink_to("zkllm-driver")
+    print(f"linked: {HOST_LIB} and {exe}")
+    return HOST_LIB
+
+
+def build_reference_drivers(ref_dir: Path) -> bool:
+    """Drop-in check: the reference's six driver sources, unmodified, compiled against
+    host/ and linked with the two libraries, into bin/ref-drivers/.  Each source is
+    compiled from a scratch copy, because a quoted #include looks beside the
+    including file first and would find the reference's own headers there."""
+    import shutil
+    import tempfile
+    if not all((ref_dir / f"{st}.cu").exists() for st in STAGES):
+        return False
+    dst = BIN / "ref-drivers"
+    dst.mkdir(parents=True, exist_ok=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        for st in STAGES:
+            shutil.copy(ref_dir / f"{st}.cu", Path(tmp) / f"{st}.cu")
+            obj = Path(tmp) / f"{st}.o"
+            _run([HOST_CXX, "-x", "c++", "-std=c++17", "-O1", f"-I{HOST}", "-c", str(Path(tmp) / f"{st}.cu"), "-o", str(obj)])
+            _run([HOST_CXX, "-o", str(dst / st), str(obj), f"-L{LIB.parent}", "-lzkllm_host", "-lzkllm_b200",
+                  "-Wl,-rpath,$ORIGIN/../../lib"])
+    print(f"reference drivers built unmodified against host/: {dst}")
+    return True
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="--verbose-ptxas" in sys.argv)
+    build_host(force="--force" in sys.argv)
+    build_reference_drivers(Path(os.environ.get("ZKLLM_REFERENCE_DIR", "/root/reference")))

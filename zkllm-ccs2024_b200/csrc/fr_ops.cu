@@ -291,6 +291,16 @@ __global__ void fr_transpose_kernel(const Fr* __restrict__ a, size_t M, size_t N
         if (row < N && col < M) fr_store(out + row * M + col, tile[threadIdx.x][r]);
     }
 }
+// Fr_split_by_window (fr-tensor.cu:562-573): even and odd windows to two arrays
+__global__ void fr_split_window_kernel(const Fr* __restrict__ a, size_t n, size_t window, Fr* __restrict__ o0, Fr* __restrict__ o1,
+                                       size_t out_n) {
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < out_n; g += (size_t)gridDim.x * blockDim.x) {
+        const size_t w = g / window, k = g % window;
+        const size_t i0 = 2 * w * window + k, i1 = (2 * w + 1) * window + k;
+        fr_store(o0 + g, i0 < n ? fr_load(a + i0) : fr_zero());
+        fr_store(o1 + g, i1 < n ? fr_load(a + i1) : fr_zero());
+    }
+}
 __global__ void fr_add_bias_kernel(Fr* __restrict__ z, const Fr* __restrict__ bias, size_t rows, size_t cols) {
     const size_t n = rows * cols;
     for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < n; g += (size_t)gridDim.x * blockDim.x)
@@ -623,6 +633,13 @@ int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_
     dim3 grid(div_up(P, kMmTile), div_up(M, kMmTile));
     if (grid.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^21 rows");
     ZKB_LAUNCH(fr_matmul_kernel, grid, 256, 0, as_stream(stream), CFR(d_a), CFR(d_b), FR(d_c), M, N, P);
+    return ZKB_OK;
+}
+int zkb_fr_split_window(const zkb_fr_t* d_a, size_t n, size_t window, zkb_fr_t* d_out0, zkb_fr_t* d_out1, size_t out_n, void* stream) {
+    if (!out_n) return ZKB_OK;
+    if (!window) return fail(ZKB_ERR_ARG, "Invalid window size.");
+    ZKB_LAUNCH(fr_split_window_kernel, grid_for(out_n, kThreads), kThreads, 0, as_stream(stream),
+               CFR(d_a), n, window, FR(d_out0), FR(d_out1), out_n);
     return ZKB_OK;
 }
 int zkb_fr_add_bias(zkb_fr_t* d_z, const zkb_fr_t* d_bias, size_t rows, size_t cols, void* stream) {

@@ -1,0 +1,220 @@
+// Per-layer stage drivers with the reference's command lines and .bin hand-off
+// files (reference: ppgen.cu, commit-param.cu, rmsnorm.cu, self-attn.cu, ffn.cu,
+// skip-connection.cu).  One executable; the stage is the first argument, or the
+// name the program was invoked under (a symlink called `ffn` runs the ffn stage):
+//
+//   zkllm-driver ppgen <size> <out-pp.bin>
+//   zkllm-driver commit-param <pp.bin> <int.bin> <out-commitment.bin> <in_dim> <out_dim>
+//   zkllm-driver rmsnorm <input|post_attention> <in.bin> <seq> <embed> <workdir> <layer-prefix> <out.bin>
+//   zkllm-driver self-attn <linear|attn> <in.bin> <seq> <embed> <workdir> <layer-prefix> <out.bin>
+//   zkllm-driver ffn <in.bin> <seq> <embed> <hidden> <workdir> <layer-prefix> <out.bin>
+//   zkllm-driver skip-connection <x.bin> <y.bin> <out.bin>
+//
+// Each stage computes its fixed-point outputs in the field, proves them and
+// throws if a verifier equation fails, printing the reference's progress lines.
+#include <cstring>
+#include <functional>
+#include <map>
+#include <string>
+
+#include "commitment.cuh"
+#include "fr-tensor.cuh"
+#include "proof.cuh"
+#include "rescaling.cuh"
+#include "zkfc.cuh"
+#include "zksoftmax.cuh"
+
+namespace {
+
+typedef std::vector<std::string> Args;
+
+// generator, int weights and commitment of one parameter of one layer
+Weight load_param(const std::string& workdir, const std::string& prefix, const std::string& name, uint in_dim, uint out_dim) {
+    return create_weight(workdir + "/" + name + "-pp.bin", workdir + "/" + prefix + "-" + name + "-int.bin",
+                         workdir + "/" + prefix + "-" + name + "-commitment.bin", in_dim, out_dim);
+}
+
+// forward + rescale + both proofs of one linear layer; returns the rescaled output
+struct Linear {
+    Weight w;
+    zkFC fc;
+    Rescaling rs;
+    Linear(const Weight& weight, uint in_dim, uint out_dim, uint scale) : w(weight), fc(in_dim, out_dim, w.weight), rs(scale) {}
+};
+
+int run_ppgen(const Args& a) {
+    const uint size = std::stoi(a.at(0));
+    Commitment::random(1u << ceilLog2(size)).save(a.at(1));
+    return 0;
+}
+
+int run_commit_param(const Args& a) {
+    Commitment generator(a.at(0));
+    if (generator.size != (1u << ceilLog2(generator.size))) throw std::runtime_error("Generator size has to be a power of 2");
+    const uint in_dim = std::stoi(a.at(3)), out_dim = std::stoi(a.at(4));
+    FrTensor param = FrTensor::from_int_bin(a.at(1));
+    cout << "Param size: " << param.size << endl << "In dim: " << in_dim << endl << "Out dim: " << out_dim << endl;
+    auto padded = param.pad({in_dim, out_dim});
+    auto com = generator.commit_int(padded);
+    cout << "Generator size: " << generator.size << endl << "Unpadded param size: " << param.size << endl;
+    cout << "Padded param size: " << padded.size << endl << "Commitment size: " << com.size << endl;
+    com.save(a.at(2));
+    return 0;
+}
+
+int run_rmsnorm(const Args& a) {
+    const std::string which = a.at(0);
+    const uint seq = std::stoi(a.at(2)), embed = std::stoi(a.at(3));
+    auto weight = load_param(a.at(4), a.at(5), which + "_layernorm.weight", 1, embed);
+    FrTensor X = FrTensor::from_int_bin(a.at(1));
+    FrTensor rms_inv = FrTensor::from_int_bin("rms_inv_temp.bin");   // written by the Python side, one value per row
+    Rescaling rs_gain(1 << 16), rs_out(1 << 16);
+    zkFC gain(1, embed, weight.weight);
+    auto g_rms = gain(rms_inv);                 // outer product [seq, embed]
+    auto g_rms_ = rs_gain(g_rms);
+    auto Y = g_rms_ * X;
+    auto Y_ = rs_out(Y);
+    rs_out.prove(Y, Y_);
+    Y_.save_int(a.at(6));
+    hadamard_product_sumcheck(g_rms_, X, random_vec(ceilLog2(Y.size)), random_vec(ceilLog2(Y.size)));
+    rs_gain.prove(g_rms, g_rms_);
+    verifyWeightClaim(weight, gain.prove(rms_inv, g_rms)[0]);
+    (void)seq;
+    return 0;
+}
+
+int run_self_attn(const Args& a) {
+    const std::string mode = a.at(0);
+    const uint seq = std::stoi(a.at(2)), embed = std::stoi(a.at(3));
+    if (mode == "linear") {
+        FrTensor input = FrTensor::from_int_bin(a.at(1));
+        const char* names[3] = {"q", "k", "v"};
+        std::vector<Linear*> layers;
+        std::vector<FrTensor> raw, scaled;
+        for (const char* nm : names) {
+            layers.push_back(new Linear(load_param(a.at(4), a.at(5), std::string("self_attn.") + nm + "_proj.weight", embed, embed),
+                                        embed, embed, 1 << 16));
+            raw.push_back(layers.back()->fc(input));
+            scaled.push_back(layers.back()->rs(raw.back()));
+        }
+        for (int i = 0; i < 3; ++i) layers[i]->rs.prove(raw[i], scaled[i]);
+        // the reference opens k first, then q, then v
+        for (int i : {1, 0, 2}) verifyWeightClaim(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]);
+        scaled[0].save_int("temp_Q.bin");
+        scaled[1].save_int("temp_K.bin");
+        scaled[2].save_int("temp_V.bin");
+        for (auto* l : layers) delete l;
+        cout << "QKV linear proof successfully verified!" << endl;
+        return 0;
+    }
+    if (mode == "attn") {
+        auto Q = FrTensor::from_int_bin("temp_Q.bin");
+        auto K = FrTensor::from_int_bin("temp_K.bin");
+        auto V = FrTensor::from_int_bin("temp_V.bin");
+        const uint d = Q.size / seq;   // all heads together, as the reference does
+        auto X = FrTensor::matmul(Q, K.transpose(seq, d), seq, d, seq);
+        zkSoftmax softmax({1 << 8, 1 << 20, 1 << 20}, 1, 0, 1UL << 32, {1 << 18, 1 << 22}, seq, seq, d, 1);
+        Rescaling rs1(1 << 20), rs2(1 << 20);
+        FrTensor shift(seq), X_shifted(seq * seq);
+        vector<FrTensor> X_segments, Y_segments, m_segments;
+        FrTensor Y = softmax.compute(X, shift, X_shifted, X_segments, Y_segments, m_segments);
+        Y.save_long("temp_head_Y.bin");
+        auto out = FrTensor::matmul(Y, V, seq, seq, d);
+        auto out_ = rs2(out);
+        auto out__ = rs1(out_);
+        out__.save_int("temp_head_out.bin");
+        rs1.prove(out_, out__);
+        rs2.prove(out, out_);
+        auto temp_rand = random_vec(3);
+        vector<Polynomial> proof;
+        auto u1 = random_vec(ceilLog2(seq));
+        auto u2 = random_vec(ceilLog2(d));
+        auto ud = random_vec(ceilLog2(seq));
+        auto claim = out.multi_dim_me({u1, u2}, {seq, d});
+        zkip(claim, Y.partial_me(u1, seq, seq), V.partial_me(u2, d, 1), ud, proof);
+        auto u_sm = random_vec(ceilLog2(Y.size));
+        auto v_sm = random_vec(ceilLog2(Y.size));
+        softmax.prove(Y, X, shift, X_shifted, X_segments, Y_segments, m_segments, u_sm, v_sm, temp_rand[0], temp_rand[1], temp_rand[2],
+                      proof);
+        auto u1_ = random_vec(ceilLog2(seq));
+        auto u2_ = random_vec(ceilLog2(seq));
+        auto ud_ = random_vec(ceilLog2(d));
+        auto claim_ = X.multi_dim_me({u1_, u2_}, {seq, seq});
+        zkip(claim_, Q.partial_me(u1_, seq, d), K.partial_me(u2_, seq, d), ud_, proof);
+        cout << "Self attention proof successfully verified!" << endl;
+        return 0;
+    }
+    return 0;
+}
+
+int run_ffn(const Args& a) {
+    const uint seq = std::stoi(a.at(1)), embed = std::stoi(a.at(2)), hidden = std::stoi(a.at(3));
+    const std::string workdir = a.at(4), prefix = a.at(5);
+    Linear up(load_param(workdir, prefix, "mlp.up_proj.weight", embed, hidden), embed, hidden, 1 << 16);
+    Linear gate(load_param(workdir, prefix, "mlp.gate_proj.weight", embed, hidden), embed, hidden, 1 << 20);
+    Linear down(load_param(workdir, prefix, "mlp.down_proj.weight", hidden, embed), hidden, embed, 1 << 16);
+    Rescaling hidden_rescale(1 << 16);
+    FrTensor swiglu_values = FrTensor::from_int_bin("swiglu-table.bin");   // written by the Python side
+    tLookupRangeMapping swiglu(-(1 << 21), 1 << 22, swiglu_values);
+
+    FrTensor input = FrTensor::from_int_bin(a.at(0));
+    auto up_out = up.fc(input);
+    auto up_out_ = up.rs(up_out);
+    auto gate_out = gate.fc(input);
+    auto gate_out_ = gate.rs(gate_out);
+    auto act = swiglu(gate_out_);   // (activations, multiplicities)
+    auto temp_rand = random_vec(3);
+    auto swiglu_u = random_vec(ceilLog2(seq * hidden));
+    auto swiglu_v = random_vec(ceilLog2(seq * hidden));
+    vector<Polynomial> swiglu_proof;
+    auto down_in = act.first * up_out_;
+    auto down_in_ = hidden_rescale(down_in);
+    auto down_out = down.fc(down_in_);
+    auto down_out_ = down.rs(down_out);
+    down_out.save_int(a.at(6));   // the reference saves the value before the last rescaling
+
+    down.rs.prove(down_out, down_out_);
+    verifyWeightClaim(down.w, down.fc.prove(down_in_, down_out)[0]);
+    hidden_rescale.prove(down_in, down_in_);
+    swiglu.prove(gate_out_, act.first, act.second, temp_rand[0], temp_rand[1], temp_rand[2], swiglu_u, swiglu_v, swiglu_proof);
+    cout << "SwiGLU proof complete." << endl;
+    gate.rs.prove(gate_out, gate_out_);
+    verifyWeightClaim(gate.w, gate.fc.prove(input, gate_out)[0]);
+    up.rs.prove(up_out, up_out_);
+    verifyWeightClaim(up.w, up.fc.prove(input, up_out)[0]);
+    return 0;
+}
+
+int run_skip(const Args& a) {
+    FrTensor x = FrTensor::from_int_bin(a.at(0));
+    FrTensor y = FrTensor::from_int_bin(a.at(1));
+    (x + y).save_int(a.at(2));
+    return 0;
+}
+
+}  // namespace
+
+int main(int argc, char* argv[]) {
+    const std::map<std::string, std::pair<std::function<int(const Args&)>, size_t>> stages = {
+        {"ppgen", {run_ppgen, 2}},         {"commit-param", {run_commit_param, 5}}, {"rmsnorm", {run_rmsnorm, 7}},
+        {"self-attn", {run_self_attn, 7}}, {"ffn", {run_ffn, 7}},                   {"skip-connection", {run_skip, 3}}};
+    std::string self = argv[0];
+    const size_t slash = self.find_last_of('/');
+    if (slash != std::string::npos) self = self.substr(slash + 1);
+    int first = 1;
+    std::string stage = self;
+    if (!stages.count(stage)) {
+        if (argc < 2 || !stages.count(argv[1])) {
+            cerr << "usage: " << self << " <ppgen|commit-param|rmsnorm|self-attn|ffn|skip-connection> <stage arguments>" << endl;
+            return 2;
+        }
+        stage = argv[1];
+        first = 2;
+    }
+    Args args(argv + first, argv + argc);
+    if (args.size() < stages.at(stage).second) {
+        cerr << stage << ": expected " << stages.at(stage).second << " arguments" << endl;
+        return 2;
+    }
+    return stages.at(stage).first(args);
+}
