@@ -77,6 +77,148 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.rows)}
 
 
+def ints_to_fr_limbs(v: np.ndarray) -> np.ndarray:
+    """int64 array -> (n, 8) uint32 standard-form Fr encodings (negatives as r - |v|), on the host"""
+    v = np.ascontiguousarray(v, dtype=np.int64).reshape(-1)
+    a = np.abs(v).astype(np.uint64)
+    r64 = [(R_MOD >> (64 * i)) & 0xFFFFFFFFFFFFFFFF for i in range(4)]
+    out = np.zeros((v.size, 4), dtype=np.uint64)
+    neg = v < 0
+    out[~neg, 0] = a[~neg]
+    an = a[neg]
+    lo = (np.uint64(r64[0]) - an)                         # wraps modulo 2^64
+    borrow = (an > np.uint64(r64[0])).astype(np.uint64)
+    out[neg, 0] = lo
+    out[neg, 1] = np.uint64(r64[1]) - borrow              # r64[1] > 0: no further borrow
+    out[neg, 2] = np.uint64(r64[2])
+    out[neg, 3] = np.uint64(r64[3])
+    return out.view(np.uint32).reshape(v.size, 8)
+
+
+def random_fr(rng, k: int) -> np.ndarray:
+    vals = rng.integers(0, 1 << 32, size=(max(k, 1), 8), dtype=np.uint64).astype(np.uint32)
+    vals[:, 7] %= np.uint32(R_MOD >> 224)
+    return vals[:k] if k else vals[:0]
+
+
+ZKFC_SHAPE = (128, 4096, 4096)                 # batch, in, out: X 128x4096, W 4096x4096
+ZKFC_BYTES = 32 * (128 * 4096 + 4096 * 4096 + 128 * 4096)
+TL_D, TL_N, TL_LOW = 1 << 23, 1 << 16, -(1 << 15)
+TL_BYTES = 64 * TL_D + 192 * (TL_D - TL_N) + 480 * TL_N
+
+
+def zkfc_inputs():
+    B, I, O = ZKFC_SHAPE
+    rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 16))
+    X = np.rint(rng.standard_normal((B, I)) * 0.02 * 65536).astype(np.int64)
+    W = np.rint(rng.standard_normal((I, O)) * 0.02 * 65536).astype(np.int64)
+    Y = (X.astype(np.float64) @ W.astype(np.float64)).astype(np.int64)    # |sum| < 2^53: exact in float64
+    ch = np.random.Generator(np.random.PCG64(0x5EED0000 + 17))
+    return X, W, Y, random_fr(ch, 7), random_fr(ch, 12), random_fr(ch, 12)
+
+
+def tlookup_inputs():
+    rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 48))
+    S = rng.integers(TL_LOW, TL_LOW + TL_N, size=TL_D, dtype=np.int64).astype(np.int32)
+    ch = np.random.Generator(np.random.PCG64(0x5EED0000 + 49))
+    return S, random_fr(ch, 1), random_fr(ch, 1), random_fr(ch, 23), random_fr(ch, 23)
+
+
+def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
+    """zkFC::prove body (128x4096 . 4096x4096) and tLookupRange prep + prove (2^23 in 2^16):
+    seconds per proof and algorithmic GB/s (bytes each live array is read/written once per round)"""
+    sp = z._p(torch.cuda.current_stream().cuda_stream)
+    out = {}
+    B, I, O = ZKFC_SHAPE
+    X, W, Y, ub, ui, uo = zkfc_inputs()
+    dev = {}
+    for nm, arr in (("X", X), ("W", W), ("Y", Y)):
+        t = torch.from_numpy(arr.reshape(-1)).cuda()
+        fr = torch.empty(arr.size * 8, dtype=torch.int32, device="cuda")
+        z.call("zkb_fr_from_i64", z._p(t.data_ptr()), z._p(fr.data_ptr()), z.sz(arr.size), sp)
+        dev[nm] = fr
+    polys, claims = np.zeros((36, 8), dtype=np.uint32), np.zeros((4, 8), dtype=np.uint32)
+
+    def zk():
+        z.call("zkb_zkfc_prove", z._p(dev["X"].data_ptr()), z._p(dev["W"].data_ptr()), z._p(dev["Y"].data_ptr()), z.sz(B), z.sz(I),
+               z.sz(O), z._p(ub), z._p(ui), z._p(uo), z._p(polys), z._p(claims), sp)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / steps
+
+    s = timed(zk)
+    out["zkfc_prove"] = {"workload": "zkFC::prove body, X 128x4096, W 4096x4096", "seconds": s, "algorithmic_bytes": ZKFC_BYTES,
+                         "gb_per_s": ZKFC_BYTES / s / 1e9, "frac_of_hbm_peak": ZKFC_BYTES / s / 1e9 / hbm_peak,
+                         "final_claim": bytes(claims[1]).hex()}
+    del dev
+    S, alpha, beta, u, v = tlookup_inputs()
+    d_S_int = torch.from_numpy(S).cuda()
+    d_S = torch.empty(TL_D * 8, dtype=torch.int32, device="cuda")
+    z.call("zkb_fr_from_i32", z._p(d_S_int.data_ptr()), z._p(d_S.data_ptr()), z.sz(TL_D), sp)
+    d_T = torch.empty(TL_N * 8, dtype=torch.int32, device="cuda")
+    z.call("zkb_tlookup_range_table", z.i32(TL_LOW), z.sz(TL_N), z.sz(TL_N), z._p(d_T.data_ptr()), sp)
+    d_idx = torch.empty(TL_D, dtype=torch.int32, device="cuda")
+    d_m = torch.empty(TL_N * 8, dtype=torch.int32, device="cuda")
+    tpolys, tfinal = np.zeros((4 * 23, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+
+    def tl():
+        z.call("zkb_tlookup_range_indices", z._p(d_S.data_ptr()), z.i32(TL_LOW), z._p(d_idx.data_ptr()), z.sz(TL_D), sp)
+        z.call("zkb_tlookup_prep", z._p(d_idx.data_ptr()), z.sz(TL_D), z.sz(TL_N), z._p(d_m.data_ptr()), sp)
+        z.call("zkb_tlookup_prove", z._p(d_S.data_ptr()), z._p(d_T.data_ptr()), z._p(d_m.data_ptr()), z.sz(TL_D), z.sz(TL_N),
+               z._p(alpha), z._p(beta), z._p(u), z._p(v), z._p(tpolys), z._p(tfinal), sp)
+
+    s = timed(tl)
+    out["tlookup_prove"] = {"workload": "tLookupRange(-32768, 65536) prep + prove, 2^23 values", "seconds": s,
+                            "algorithmic_bytes": TL_BYTES, "gb_per_s": TL_BYTES / s / 1e9,
+                            "frac_of_hbm_peak": TL_BYTES / s / 1e9 / hbm_peak, "final_claim": bytes(tfinal[0]).hex()}
+    return out
+
+
+def sumcheck_reference(harness: Path, steps: int) -> dict:
+    """the same two proofs through the reference's own build (oracle/_ref/ref_harness)"""
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        t = Path(tmp)
+        X, W, Y, ub, ui, uo = zkfc_inputs()
+        for nm, arr in (("X", X), ("W", W), ("Y", Y)):
+            ints_to_fr_limbs(arr).tofile(t / f"{nm}.bin")
+        for nm, arr in (("ub", ub), ("ui", ui), ("uo", uo)):
+            arr.tofile(t / f"{nm}.bin")
+        B, I, O = ZKFC_SHAPE
+        res = subprocess.run([str(harness), "bench-zkfc", t / "X.bin", t / "W.bin", t / "Y.bin", str(B), str(I), str(O), t / "ub.bin",
+                              t / "ui.bin", t / "uo.bin", str(steps), "1"], capture_output=True, text=True, timeout=3000)
+        if res.returncode == 0:
+            times = [float(l.split()[1]) for l in res.stdout.splitlines() if l.startswith("step_s")]
+            fin = [l.split()[1] for l in res.stdout.splitlines() if l.startswith("final")]
+            s = sum(times) / len(times)
+            out["zkfc_prove"] = {"seconds": s, "gb_per_s": ZKFC_BYTES / s / 1e9, "final_claim_hex_be": fin[0] if fin else None}
+        else:
+            out["zkfc_prove"] = {"unavailable": res.stderr[-200:]}
+        S, alpha, beta, u, v = tlookup_inputs()
+        S.tofile(t / "S.bin")
+        for nm, arr in (("alpha", alpha), ("beta", beta), ("u", u), ("v", v)):
+            arr.tofile(t / f"{nm}.bin")
+        res = subprocess.run([str(harness), "bench-tlookup", t / "S.bin", str(TL_LOW), str(TL_N), t / "alpha.bin", t / "beta.bin",
+                              t / "u.bin", t / "v.bin", str(steps), "1"], capture_output=True, text=True, timeout=3000)
+        if res.returncode == 0:
+            times = [float(l.split()[1]) for l in res.stdout.splitlines() if l.startswith("step_s")]
+            fin = [l.split()[1] for l in res.stdout.splitlines() if l.startswith("final")]
+            s = sum(times) / len(times)
+            out["tlookup_prove"] = {"seconds": s, "gb_per_s": TL_BYTES / s / 1e9, "final_claim_hex_be": fin[0] if fin else None}
+        else:
+            out["tlookup_prove"] = {"unavailable": res.stderr[-200:]}
+    return out
+
+
 def g1_equal(z_norm_a: np.ndarray, z_norm_b: np.ndarray) -> bool:
     return bool(np.array_equal(z_norm_a, z_norm_b))
 
@@ -235,6 +377,11 @@ def run_ours(args) -> dict:
                     "peaks_measured": imad, "algorithmic_mads_per_point": windows * FQ_MULS_PER_MIXED_ADD * MADS_PER_FQ_MUL,
                     "launch_ms": dom_launch_ms}
         shares = {k: round(v[1] / sum(x[1] for x in kernels.values()), 4) for k, v in kernels.items()} if kernels else {}
+        sumcheck = None
+        if not args.no_sumcheck:
+            del d_sc, d_out
+            torch.cuda.empty_cache()
+            sumcheck = sumcheck_ours(z, torch, max(2, min(args.steps, 5)), hbm_peak)
         result = {
             "metric": "G1 MSM throughput (Pedersen/Hyrax row commitment)", "value": value, "unit": "Mpts/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -244,7 +391,7 @@ def run_ours(args) -> dict:
                        "l2": "inputs (172 MB of scalars per step) larger than L2, no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
             "roofline": roofline, "int_pipe": int_pipe, "cpu_baseline": cpu_baseline,
-            "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok),
+            "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "sumcheck": sumcheck,
         }
         if not (parity and e2e_ok):
             result["error"] = "sampled rows differ from the CPU oracle"
@@ -290,7 +437,8 @@ def run_reference(args) -> dict:
             times = [float(l.split()[1]) for l in res.stdout.splitlines() if l.startswith("step_s")]
         s = sum(times) / len(times)
         v = m * n / s / 1e6
-        return {**base, "value": v, "ms_per_step": s * 1e3,
+        sumcheck = None if args.no_sumcheck else sumcheck_reference(harness, max(1, min(args.steps, 2)))
+        return {**base, "value": v, "ms_per_step": s * 1e3, "sumcheck": sumcheck,
                 "config": {"workload": f"commit_int {m}x{n} (reference Commitment::commit_int, its own CUDA kernels, sm_100 build)"},
                 "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": 0, "kind": "reference",
                                  "sample": "full workload, reference CUDA build on the same GPU (the reference has no CPU path)"},
@@ -319,6 +467,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=11008)
+    ap.add_argument("--no-sumcheck", action="store_true", help="skip the zkFC / tLookup proof timings reported under 'sumcheck'")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -290,6 +290,42 @@ int main(int argc, char** argv) {
                 cout << "step_s " << (now_s() - t0) << endl;
                 if (i == steps - 1) c.save(arg(6));
             }
+        } else if (cmd == "bench-zkfc") {           // X W Y B I O ub ui uo steps warmup : body of zkFC::prove
+            FrTensor X(arg(2)), W(arg(3)), Y(arg(4));
+            uint B = stoul(arg(5)), I = stoul(arg(6)), O = stoul(arg(7));
+            auto ub = load_vec(arg(8)), ui = load_vec(arg(9)), uo = load_vec(arg(10));
+            int steps = stoi(arg(11)), warm = stoi(arg(12));
+            for (int i = 0; i < warm + steps; ++i) {
+                cudaDeviceSynchronize();
+                double t0 = now_s();
+                auto claim = Y.multi_dim_me({ub, uo}, {B, O});
+                auto X_red = X.partial_me(ub, B, I);
+                auto W_red = W.partial_me(uo, O, 1);
+                vector<Polynomial> proof;
+                auto final_claim = zkip(claim, X_red, W_red, ui, proof);
+                auto claim_X = X.multi_dim_me({ub, ui}, {B, I});
+                auto claim_W = W.multi_dim_me({ui, uo}, {I, O});
+                bool ok = (claim_X * claim_W == final_claim);
+                cudaDeviceSynchronize();
+                if (i >= warm) cout << "step_s " << (now_s() - t0) << endl;
+                if (i == warm + steps - 1) cout << "final " << final_claim << endl << "ok " << ok << endl;
+            }
+        } else if (cmd == "bench-tlookup") {        // S(int.bin) low len alpha beta u v steps warmup : prep + prove
+            FrTensor S = FrTensor::from_int_bin(arg(2));
+            tLookupRange tl(stoi(arg(3)), stoul(arg(4)));
+            Fr_t alpha = load_vec(arg(5))[0], beta = load_vec(arg(6))[0];
+            auto u = load_vec(arg(7)), v = load_vec(arg(8));
+            int steps = stoi(arg(9)), warm = stoi(arg(10));
+            for (int i = 0; i < warm + steps; ++i) {
+                cudaDeviceSynchronize();
+                double t0 = now_s();
+                auto m = tl.prep(S);
+                vector<Polynomial> proof;
+                Fr_t fc = tl.prove(S, m, alpha, beta, u, v, proof);
+                cudaDeviceSynchronize();
+                if (i >= warm) cout << "step_s " << (now_s() - t0) << endl;
+                if (i == warm + steps - 1) cout << "final " << fc << endl;
+            }
         } else {
             cerr << "unknown command " << cmd << endl;
             return 2;
