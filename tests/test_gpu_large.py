@@ -1,0 +1,150 @@
+"""GPU parity at sizes the Python oracle cannot reach: against the C++ oracle, and
+through size-independent properties (linearity of the commitment, the provers'
+own verifier equations) at larger sizes."""
+import ctypes
+import random
+
+import numpy as np
+import pytest
+
+from oracle import cpporacle as C
+from oracle import pyref as R
+from tests.util import Dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev(zkb):
+    return Dev(zkb)
+
+
+def gpu_generators(dev, n, seed):
+    """n generators s_i * G made on the device (checked against the oracle in test_gpu_g1)"""
+    z = dev.z
+    rng = np.random.Generator(np.random.PCG64(seed))
+    s = rng.integers(0, 1 << 32, size=(n, 8), dtype=np.uint64).astype(np.uint32)
+    s[:, 7] %= np.uint32(R.R_MOD >> 224)
+    out = z.DeviceBuffer(144 * n)
+    g1 = z.DeviceBuffer.from_host(R.g1_pack([R.G1_GEN]))
+    dev.call("zkb_g1_mul", z._p(g1), z.sz(1), z._p(z.DeviceBuffer.from_host(s)), z.sz(n), z._p(out), z._p(0))
+    return out, out.to_host(np.uint32, (n, 36))
+
+
+def normalised(dev, buf, n):
+    return C.g1_normalise(buf.to_host(np.uint32, (n, 36)))
+
+
+@pytest.mark.parametrize("m,n,bits", [(64, 3000, 14), (3, 40000, 14), (17, 1000, 31), (5, 300, 20), (1, 70000, 13)])
+def test_commit_against_cpp_oracle(dev, m, n, bits):
+    z = dev.z
+    d_g, h_g = gpu_generators(dev, n, 1000 + n)
+    rng = np.random.Generator(np.random.PCG64(m * n))
+    sc = rng.integers(-(1 << bits), 1 << bits, size=m * n, dtype=np.int64).astype(np.int32)
+    out = z.DeviceBuffer(144 * m)
+    dev.call("zkb_commit_i32", z._p(d_g), z.sz(n), z._p(z.DeviceBuffer.from_host(sc)), z.sz(m * n), z._p(out), z._p(0))
+    exp = C.commit_int(h_g, sc, "pippenger")
+    assert np.array_equal(normalised(dev, out, m), C.g1_normalise(exp))
+
+
+def test_commit_is_linear_in_the_scalars(dev):
+    """commit(a + b) = commit(a) + commit(b), 512 rows x 11008 generators (benchmark row length)"""
+    z = dev.z
+    m, n = 512, 11008
+    d_g, _ = gpu_generators(dev, n, 7)
+    rng = np.random.Generator(np.random.PCG64(99))
+    a = np.rint(rng.standard_normal(m * n) * 0.02 * 65536).astype(np.int32)
+    b = np.rint(rng.standard_normal(m * n) * 0.02 * 65536).astype(np.int32)
+    outs = []
+    for s in (a, b, a + b):
+        o = z.DeviceBuffer(144 * m)
+        dev.call("zkb_commit_i32", z._p(d_g), z.sz(n), z._p(z.DeviceBuffer.from_host(s)), z.sz(m * n), z._p(o), z._p(0))
+        outs.append(o)
+    summed = z.DeviceBuffer(144 * m)
+    dev.call("zkb_g1_add", z._p(outs[0]), z._p(outs[1]), z._p(summed), z.sz(m), z._p(0))
+    assert np.array_equal(normalised(dev, summed, m), normalised(dev, outs[2], m))
+    # and a sample of rows against the oracle
+    _, h_g = gpu_generators(dev, n, 7)
+    rows = [0, 255, 511]
+    exp = C.commit_int(h_g, a.reshape(m, n)[rows], "pippenger")
+    assert np.array_equal(normalised(dev, outs[0], m)[rows], C.g1_normalise(exp))
+
+
+def _rand_fr(rng, k):
+    v = rng.integers(0, 1 << 32, size=(max(k, 1), 8), dtype=np.uint64).astype(np.uint32)
+    v[:, 7] %= np.uint32(R.R_MOD >> 224)
+    return v[:k] if k else np.zeros((0, 8), dtype=np.uint32)
+
+
+@pytest.mark.parametrize("B,I,O", [(64, 512, 768), (100, 300, 1000), (2048, 64, 128)])
+def test_zkfc_against_cpp_oracle(dev, B, I, O):
+    z = dev.z
+    rng = np.random.Generator(np.random.PCG64(B + I + O))
+    X = rng.integers(-70000, 70000, size=(B, I), dtype=np.int64)
+    W = rng.integers(-5000, 5000, size=(I, O), dtype=np.int64)
+    Y = X @ W
+    fr = lambda a: R.fr_pack([int(v) for v in a.reshape(-1)])
+    hX, hW, hY = fr(X), fr(W), fr(Y)
+    ub, ui, uo = _rand_fr(rng, R.ceil_log2(B)), _rand_fr(rng, R.ceil_log2(I)), _rand_fr(rng, R.ceil_log2(O))
+    rc, epolys, eclaims = C.zkfc_prove(hX, hW, hY, B, I, O, ub, ui, uo)
+    assert rc == 0
+    kI = ui.shape[0]
+    polys = np.zeros((max(3 * kI, 1), 8), dtype=np.uint32)
+    claims = np.zeros((4, 8), dtype=np.uint32)
+    dev.call("zkb_zkfc_prove", z._p(z.fr_buffer(hX)), z._p(z.fr_buffer(hW)), z._p(z.fr_buffer(hY)), z.sz(B), z.sz(I), z.sz(O),
+             z._p(z.fr_host(ub)), z._p(z.fr_host(ui)), z._p(z.fr_host(uo)), z._p(polys), z._p(claims), z._p(0))
+    assert np.array_equal(polys[:3 * kI], epolys) and np.array_equal(claims, eclaims)
+    # forward pass
+    dY = z.DeviceBuffer(32 * B * O)
+    dev.call("zkb_fr_matmul", z._p(z.fr_buffer(hX)), z._p(z.fr_buffer(hW)), z._p(dY), z.sz(B), z.sz(I), z.sz(O), z._p(0))
+    assert np.array_equal(dY.to_host(np.uint32, (B * O, 8)), hY)
+
+
+@pytest.mark.parametrize("logD,logN", [(16, 10), (18, 16), (14, 14)])
+def test_tlookup_against_cpp_oracle(dev, logD, logN):
+    z = dev.z
+    D, N, low = 1 << logD, 1 << logN, -(1 << (logN - 1))
+    rng = np.random.Generator(np.random.PCG64(logD * 100 + logN))
+    S_int = rng.integers(low, low + N, size=D, dtype=np.int64).astype(np.int32)
+    dS = z.DeviceBuffer(32 * D)
+    dev.call("zkb_fr_from_i32", z._p(z.DeviceBuffer.from_host(S_int)), z._p(dS), z.sz(D), z._p(0))
+    dT, dI, dM = z.DeviceBuffer(32 * N), z.DeviceBuffer(4 * D), z.DeviceBuffer(32 * N)
+    dev.call("zkb_tlookup_range_table", z.i32(low), z.sz(N), z.sz(N), z._p(dT), z._p(0))
+    dev.call("zkb_tlookup_range_indices", z._p(dS), z.i32(low), z._p(dI), z.sz(D), z._p(0))
+    dev.call("zkb_tlookup_prep", z._p(dI), z.sz(D), z.sz(N), z._p(dM), z._p(0))
+    hS, hT, hM = dS.to_host(np.uint32, (D, 8)), dT.to_host(np.uint32, (N, 8)), dM.to_host(np.uint32, (N, 8))
+    assert np.array_equal(hM[:, 0], np.bincount(S_int.astype(np.int64) - low, minlength=N).astype(np.uint32))
+    alpha, beta, u, v = _rand_fr(rng, 1), _rand_fr(rng, 1), _rand_fr(rng, logD), _rand_fr(rng, logD)
+    rc, epolys, efinal = C.tlookup_prove(hS, hT, hM, alpha, beta, u, v)
+    assert rc == 0
+    polys = np.zeros((4 * logD, 8), dtype=np.uint32)
+    final = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(dM), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u), z._p(v),
+             z._p(polys), z._p(final), z._p(0))
+    assert np.array_equal(polys, epolys) and np.array_equal(final, efinal)
+
+
+def test_tlookup_full_size_verifies(dev):
+    """2^23 lookups in a 2^16 table (the lookup benchmark size): all 23 round checks pass"""
+    z = dev.z
+    D, N, low = 1 << 23, 1 << 16, -(1 << 15)
+    rng = np.random.Generator(np.random.PCG64(5))
+    S_int = rng.integers(low, low + N, size=D, dtype=np.int64).astype(np.int32)
+    dS = z.DeviceBuffer(32 * D)
+    dev.call("zkb_fr_from_i32", z._p(z.DeviceBuffer.from_host(S_int)), z._p(dS), z.sz(D), z._p(0))
+    dT, dI, dM = z.DeviceBuffer(32 * N), z.DeviceBuffer(4 * D), z.DeviceBuffer(32 * N)
+    dev.call("zkb_tlookup_range_table", z.i32(low), z.sz(N), z.sz(N), z._p(dT), z._p(0))
+    dev.call("zkb_tlookup_range_indices", z._p(dS), z.i32(low), z._p(dI), z.sz(D), z._p(0))
+    dev.call("zkb_tlookup_prep", z._p(dI), z.sz(D), z.sz(N), z._p(dM), z._p(0))
+    alpha, beta, u, v = _rand_fr(rng, 1), _rand_fr(rng, 1), _rand_fr(rng, 23), _rand_fr(rng, 23)
+    polys = np.zeros((4 * 23, 8), dtype=np.uint32)
+    final = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(dM), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u), z._p(v),
+             z._p(polys), z._p(final), z._p(0))
+    # a corrupted multiplicity must be caught
+    bad = dM.to_host(np.uint32, (N, 8))
+    bad[3, 0] += 1
+    with pytest.raises(z.ZkbError) as e:
+        dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(z.DeviceBuffer.from_host(bad)), z.sz(D), z.sz(N), z._p(alpha),
+                 z._p(beta), z._p(u), z._p(v), z._p(polys), z._p(final), z._p(0))
+    assert e.value.code == z.ERR_VERIFY
