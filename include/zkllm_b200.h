@@ -107,6 +107,18 @@ int zkb_fr_sum(const zkb_fr_t* d_a, size_t n, zkb_fr_t* h_out, void* stream);
  * binding the least-significant index bit; needs 2^(k-1) < n <= 2^k. */
 int zkb_fr_mle_eval(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
                     zkb_fr_t* h_out, void* stream);
+/* Same evaluation for callers that cannot allocate device memory - for example a
+ * process that gave the whole GPU to its own memory manager at start-up, or a
+ * latency-critical loop that must stay clear of the allocator.  It has no
+ * counterpart in the reference.  All working memory is one fixed device array
+ * inside the library (288 KiB on every GPU that loads the library, held until
+ * exit); the call performs no cudaMalloc/cudaFree and uses no memory pool.
+ * Limit: n <= 2^24 elements (k <= 24), larger sizes return ZKB_ERR_LIMIT.
+ * The first call on a device looks up the array's address; make that first
+ * call before any stream capture.  All calls share the array, so two calls
+ * that overlap on the GPU (different streams or threads) race: serialise them. */
+int zkb_fr_mle_eval_noalloc(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
+                            zkb_fr_t* h_out, void* stream);
 /* FrTensor::partial_me(u, cur_dim, window_size) (fr-tensor.cu:518-560): the tensor
  * is [n/(cur_dim*window), cur_dim, window]; the middle axis is folded away with u.
  * d_out receives n/cur_dim elements. */

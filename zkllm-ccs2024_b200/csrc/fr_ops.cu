@@ -655,3 +655,78 @@ int zkb_fr_gather(const uint32_t* d_indices, const zkb_fr_t* d_vals, zkb_fr_t* d
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// zkb_fr_mle_eval_noalloc: the same evaluation as zkb_fr_mle_eval for callers
+// that must not allocate device memory.  Examples: a host process that handed
+// the whole GPU to its own memory manager at start-up and cannot let a library
+// take memory behind its back, or a latency-critical loop that cannot afford the
+// allocator's locks.  The eq-tables, the per-CTA partial sums and the result
+// slot live in one file-scope device array of fixed size instead of pool
+// blocks; nothing here calls cudaMalloc, cudaFree, the stream-ordered pool or
+// any other allocating routine.
+// ---------------------------------------------------------------------------
+static constexpr unsigned kNoAllocMaxVars = 24;                       // n <= 2^24 elements
+static constexpr unsigned kNoAllocGrid = 1024;                        // at most this many partial sums
+static constexpr size_t kNoAllocLo = (size_t)1 << kEqLoBits;          // 4096-entry low table
+static constexpr size_t kNoAllocHi = (size_t)1 << (kNoAllocMaxVars - kEqLoBits);
+static constexpr size_t kNoAllocElems = kNoAllocLo + kNoAllocHi + kNoAllocGrid + 1;   // 9217 Fr = 288 KiB per GPU
+static __device__ __align__(256) zkb::Fr g_noalloc_scratch[kNoAllocElems];
+
+// The array's name is a host-side stand-in in host code, not a device address:
+// the address the kernels need is looked up once per device.
+static zkb::Fr* g_noalloc_addr[64];
+
+static int noalloc_scratch(zkb::Fr** out) {
+    int dev = 0;
+    ZKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ZKB_ERR_LIMIT, "zkb_fr_mle_eval_noalloc: device index above 63");
+    if (!g_noalloc_addr[dev]) {
+        void* p = nullptr;
+        ZKB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_addr[dev] = static_cast<zkb::Fr*>(p);
+    }
+    *out = g_noalloc_addr[dev];
+    return ZKB_OK;
+}
+
+#define ZKB_LAUNCH_NOALLOC(kernel, grid, block, stream, ...)              \
+    do {                                                                  \
+        kernel<<<(grid), (block), 0, (stream)>>>(__VA_ARGS__);            \
+        ::zkb::g_launches.fetch_add(1, std::memory_order_relaxed);        \
+        ZKB_LAUNCH_CHECK(#kernel);                                        \
+    } while (0)
+
+extern "C" int zkb_fr_mle_eval_noalloc(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (k > kNoAllocMaxVars || n > ((size_t)1 << kNoAllocMaxVars))
+        return fail(ZKB_ERR_LIMIT, "zkb_fr_mle_eval_noalloc: at most 2^24 elements (24 variables); use zkb_fr_mle_eval for larger tensors");
+    if (n == 0) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    const size_t full = (size_t)1 << k;
+    if (n <= full / 2 || n > full) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+    Fr* base = nullptr;
+    ZKB_TRY(noalloc_scratch(&base));
+    Fr* lo = base;
+    Fr* hi = base + kNoAllocLo;
+    Fr* partial = hi + kNoAllocHi;
+    Fr* result = partial + kNoAllocGrid;
+    const unsigned kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
+    Challenges ch;
+    memset(&ch, 0, sizeof(ch));
+    for (unsigned j = 0; j < kl; ++j) memcpy(ch.u[j].v, h_u[j].val, 32);
+    ZKB_LAUNCH_NOALLOC(eq_table_kernel, grid_for((size_t)1 << kl, kThreads), kThreads, s, ch, kl, lo);
+    if (kh) {
+        memset(&ch, 0, sizeof(ch));
+        for (unsigned j = 0; j < kh; ++j) memcpy(ch.u[j].v, h_u[kl + j].val, 32);
+        ZKB_LAUNCH_NOALLOC(eq_table_kernel, grid_for((size_t)1 << kh, kThreads), kThreads, s, ch, kh, hi);
+    }
+    const size_t nchunks = (n + ((size_t)1 << kl) - 1) >> kl;
+    unsigned grid = grid_for(nchunks, 1, 4);
+    if (grid > kNoAllocGrid) grid = kNoAllocGrid;
+    // every slot that is read below is written first by this call: nothing has to start at zero
+    ZKB_LAUNCH_NOALLOC(fr_mle_kernel, grid, kThreads, s, CFR(d_a), n, lo, kl, kh ? hi : nullptr, partial);
+    ZKB_LAUNCH_NOALLOC(fr_final_sum_kernel, 1, kThreads, s, partial, (size_t)grid, result);
+    ZKB_CUDA(cudaMemcpyAsync(h_out, result, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
