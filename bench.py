@@ -339,6 +339,8 @@ def run_ours(args) -> dict:
         exp = C.commit_int(h_gens.numpy().view(np.uint32).reshape(n, 36), h_sc.numpy().reshape(m, n)[sample], "pippenger")
         parity = g1_equal(C.g1_normalise(got[sample]), C.g1_normalise(exp))
         e2e_ok = g1_equal(C.g1_normalise(h_out.numpy().view(np.uint32).reshape(m, 36)[sample]), C.g1_normalise(exp))
+        import hashlib
+        commit_sha = hashlib.sha256(C.g1_normalise(got).tobytes()).hexdigest()   # all m points, affine-normalised
 
         # ---- CPU baseline: same algorithm on the host cores, bounded sample ---------------
         cores = C.threads()
@@ -391,7 +393,8 @@ def run_ours(args) -> dict:
                        "l2": "inputs (172 MB of scalars per step) larger than L2, no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
             "roofline": roofline, "int_pipe": int_pipe, "cpu_baseline": cpu_baseline,
-            "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "sumcheck": sumcheck,
+            "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "commit_sha256": commit_sha,
+            "sumcheck": sumcheck,
         }
         if not (parity and e2e_ok):
             result["error"] = "sampled rows differ from the CPU oracle"
@@ -435,10 +438,12 @@ def run_reference(args) -> dict:
             if res.returncode != 0:
                 return {**base, "unavailable": f"reference harness failed rc={res.returncode}: {res.stderr[-200:]!r}"}
             times = [float(l.split()[1]) for l in res.stdout.splitlines() if l.startswith("step_s")]
+            import hashlib
+            commit_sha = hashlib.sha256(C.g1_normalise(np.fromfile(op, dtype=np.uint32).reshape(m, 36)).tobytes()).hexdigest()
         s = sum(times) / len(times)
         v = m * n / s / 1e6
         sumcheck = None if args.no_sumcheck else sumcheck_reference(harness, max(1, min(args.steps, 2)))
-        return {**base, "value": v, "ms_per_step": s * 1e3, "sumcheck": sumcheck,
+        return {**base, "value": v, "ms_per_step": s * 1e3, "sumcheck": sumcheck, "commit_sha256": commit_sha,
                 "config": {"workload": f"commit_int {m}x{n} (reference Commitment::commit_int, its own CUDA kernels, sm_100 build)"},
                 "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": 0, "kind": "reference",
                                  "sample": "full workload, reference CUDA build on the same GPU (the reference has no CPU path)"},

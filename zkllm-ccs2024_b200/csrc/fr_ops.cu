@@ -426,6 +426,69 @@ __global__ void __launch_bounds__(kThreads) fr_inv_shifted_kernel(const Fr* __re
     }
 }
 
+
+// Same result with a long run per thread: prefix products are parked in `out`
+// (which therefore must not alias `a`) instead of registers, so one inversion
+// serves kInvLong * 256 elements and the kernel needs few registers, which lets
+// several CTAs share an SM and hide the single-thread inversion of each other.
+static constexpr int kInvLong = 32;
+__global__ void __launch_bounds__(kThreads) fr_inv_shifted_long_kernel(const Fr* __restrict__ a, Fr beta, Fr* __restrict__ out, size_t n) {
+    __shared__ Fr pre[kThreads];
+    __shared__ Fr suf[kThreads];
+    __shared__ Fr inv_total;
+    const size_t tile = (size_t)kThreads * kInvLong;
+    Fr one = fr_zero();
+    one.v[0] = 1;
+    for (size_t base = blockIdx.x * tile; base < n; base += (size_t)gridDim.x * tile) {
+        Fr run = one;
+#pragma unroll 1
+        for (int e = 0; e < kInvLong; ++e) {
+            const size_t i = base + (size_t)e * kThreads + threadIdx.x;
+            if (i < n) {
+                Fr v = fr_add(fr_load(a + i), beta);
+                if (fe_is_zero(v)) v = one;
+                run = fr_mmul(run, v);          // the run starts from the integer 1, i.e. the Montgomery form of 1/R
+                fr_store(out + i, run);
+            }
+        }
+        pre[threadIdx.x] = run;
+        suf[threadIdx.x] = run;
+        __syncthreads();
+        for (int off = 1; off < (int)kThreads; off <<= 1) {
+            Fr np = pre[threadIdx.x], ns = suf[threadIdx.x];
+            if ((int)threadIdx.x >= off) np = fr_mmul(np, pre[threadIdx.x - off]);
+            if (threadIdx.x + off < kThreads) ns = fr_mmul(ns, suf[threadIdx.x + off]);
+            __syncthreads();
+            pre[threadIdx.x] = np;
+            suf[threadIdx.x] = ns;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            Fr t = mont_inv<FrP>(pre[kThreads - 1]);
+            inv_total = fr_mmul(fr_mmul(t, one), one);   // * R^-2: every inverse below comes out in standard form
+        }
+        __syncthreads();
+        // Montgomery-domain inverse of this thread's run product
+        Fr r = inv_total;
+        if (threadIdx.x > 0) r = fr_mmul(r, pre[threadIdx.x - 1]);
+        if (threadIdx.x + 1 < kThreads) r = fr_mmul(r, suf[threadIdx.x + 1]);
+#pragma unroll 1
+        for (int e = kInvLong - 1; e >= 0; --e) {
+            const size_t i = base + (size_t)e * kThreads + threadIdx.x;
+            if (i >= n) continue;
+            Fr v = fr_add(fr_load(a + i), beta);
+            const bool was_zero = fe_is_zero(v);
+            if (was_zero) v = one;
+            // r = 1/(run_e) in the Montgomery domain; run_(e-1) is parked one stride back
+            Fr prev = e ? fr_load(out + i - kThreads) : one;
+            Fr inv_e = fr_mmul(r, prev);
+            r = fr_mmul(r, v);
+            fr_store(out + i, was_zero ? fr_zero() : inv_e);
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace zkb
 
 using namespace zkb;
@@ -523,6 +586,11 @@ int zkb_fr_unmont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream) 
 }
 int zkb_fr_inv_shifted(const zkb_fr_t* d_a, const zkb_fr_t* h_beta, zkb_fr_t* d_out, size_t n, void* stream) {
     if (!n) return ZKB_OK;
+    if (static_cast<const void*>(d_a) != static_cast<const void*>(d_out) && n >= (size_t)kThreads * kInvLong) {
+        ZKB_LAUNCH(fr_inv_shifted_long_kernel, grid_for(n, kThreads * kInvLong, 8), kThreads, 0, as_stream(stream),
+                   CFR(d_a), host_to_dev(*h_beta), FR(d_out), n);
+        return ZKB_OK;
+    }
     ZKB_LAUNCH(fr_inv_shifted_kernel, grid_for(n, kThreads * kInvPerThread, 4), kThreads, 0, as_stream(stream),
                CFR(d_a), host_to_dev(*h_beta), FR(d_out), n);
     return ZKB_OK;

@@ -59,6 +59,21 @@ static int make_eq(const zkb_fr_t* h_u, unsigned k, EqTab* out, Scratch& scratch
     return ZKB_OK;
 }
 
+// Work split of the eq-weighted round kernels: a CTA walks "pieces" of
+// blockDim.x * R consecutive indices (R a power of two, at most 16, so a piece
+// never straddles a 4096-entry chunk of the low table and the high-table
+// factor is applied once per piece).  R shrinks for small arrays so that
+// there are enough pieces to occupy the GPU.
+static void pieces_for(size_t count, unsigned* R, unsigned* grid) {
+    unsigned r = 16;
+    const size_t want = (size_t)sm_count() * 2;
+    while (r > 1 && (count + (size_t)kThreads * r - 1) / ((size_t)kThreads * r) < want) r >>= 1;
+    const size_t npieces = (count + (size_t)kThreads * r - 1) / ((size_t)kThreads * r);
+    const size_t cap = (size_t)sm_count() * 4;
+    *R = r;
+    *grid = (unsigned)(npieces < 1 ? 1 : (npieces < cap ? npieces : cap));
+}
+
 // ---------------------------------------------------------------------------
 // zkip round: pairs (g, g + half); sums of c0, c1, c2; folded outputs.
 // ---------------------------------------------------------------------------
@@ -143,20 +158,22 @@ static int zkip_verify(const zkb_fr_t* h_claim, const zkb_fr_t* h_u, unsigned k,
 // sums: [0..2] eq-weighted coefficients of (A0 + A1 t)(S0 + beta + S1 t) (without
 // the alpha factor, applied on the host), [3] sum A0, [4] sum A1.
 __global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S, size_t half,
-                                                              Fr beta, Fr v_mont, EqTab eq,
+                                                              Fr beta, Fr v_mont, EqTab eq, unsigned R,
                                                               Fr* __restrict__ nA, Fr* __restrict__ nS,
                                                               Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
     __shared__ Fr red[32];
     Fr acc[5];
 #pragma unroll
     for (int i = 0; i < 5; ++i) acc[i] = fr_zero();
-    const size_t L = (size_t)1 << eq.kl;
-    const size_t nchunks = (half + L - 1) >> eq.kl;
-    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    const size_t piece = (size_t)blockDim.x * R;          // never straddles a chunk of the low table
+    const size_t npieces = (half + piece - 1) / piece;
+    for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
         Fr q0 = fr_zero(), q1 = fr_zero(), q2 = fr_zero();
-        const size_t base = c << eq.kl;
-        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
-            const size_t i = base + j;
+        const size_t base = c * piece;
+        for (size_t jj = threadIdx.x; jj < piece && base + jj < half; jj += blockDim.x) {
+            const size_t j = (base + jj) & lmask;
+            const size_t i = base + jj;
             const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
             const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
             const Fr e = fr_load(eq.lo + j);
@@ -171,7 +188,7 @@ __global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restric
             fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
         }
         if (eq.hi) {
-            const Fr eh = fr_load(eq.hi + c);
+            const Fr eh = fr_load(eq.hi + (base >> eq.kl));
             q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
         }
         acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
@@ -185,7 +202,7 @@ __global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restric
 __global__ void __launch_bounds__(kThreads) tl_phase2_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S,
                                                               const Fr* __restrict__ Bv, const Fr* __restrict__ T,
                                                               const Fr* __restrict__ m, size_t half,
-                                                              Fr beta, Fr v_mont, EqTab eq,
+                                                              Fr beta, Fr v_mont, EqTab eq, unsigned R,
                                                               Fr* __restrict__ nA, Fr* __restrict__ nS, Fr* __restrict__ nB,
                                                               Fr* __restrict__ nT, Fr* __restrict__ nm,
                                                               Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
@@ -193,15 +210,17 @@ __global__ void __launch_bounds__(kThreads) tl_phase2_kernel(const Fr* __restric
     Fr acc[11];
 #pragma unroll
     for (int i = 0; i < 11; ++i) acc[i] = fr_zero();
-    const size_t L = (size_t)1 << eq.kl;
-    const size_t nchunks = (half + L - 1) >> eq.kl;
-    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    const size_t piece = (size_t)blockDim.x * R;          // never straddles a chunk of the low table
+    const size_t npieces = (half + piece - 1) / piece;
+    for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
         Fr q[6];
 #pragma unroll
         for (int i = 0; i < 6; ++i) q[i] = fr_zero();
-        const size_t base = c << eq.kl;
-        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
-            const size_t i = base + j;
+        const size_t base = c * piece;
+        for (size_t jj = threadIdx.x; jj < piece && base + jj < half; jj += blockDim.x) {
+            const size_t j = (base + jj) & lmask;
+            const size_t i = base + jj;
             const Fr e = fr_load(eq.lo + j);
             {
                 const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
@@ -235,7 +254,7 @@ __global__ void __launch_bounds__(kThreads) tl_phase2_kernel(const Fr* __restric
             }
         }
         if (eq.hi) {
-            const Fr eh = fr_load(eq.hi + c);
+            const Fr eh = fr_load(eq.hi + (base >> eq.kl));
 #pragma unroll
             for (int t = 0; t < 6; ++t) q[t] = fr_mmul(q[t], eh);
         }
@@ -289,21 +308,23 @@ struct HadamardPtrs {
     Fr* out[kMaxHadamard];
 };
 template <int K>
-__global__ void __launch_bounds__(kThreads) hadamard_round_kernel(HadamardPtrs p, size_t half, Fr v_mont, EqTab eq,
+__global__ void __launch_bounds__(kThreads) hadamard_round_kernel(HadamardPtrs p, size_t half, Fr v_mont, EqTab eq, unsigned R,
                                                                    Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
     __shared__ Fr red[32];
     Fr acc[K + 1];
 #pragma unroll
     for (int i = 0; i <= K; ++i) acc[i] = fr_zero();
-    const size_t L = (size_t)1 << eq.kl;
-    const size_t nchunks = (half + L - 1) >> eq.kl;
-    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    const size_t piece = (size_t)blockDim.x * R;          // never straddles a chunk of the low table
+    const size_t npieces = (half + piece - 1) / piece;
+    for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
         Fr q[K + 1];
 #pragma unroll
         for (int i = 0; i <= K; ++i) q[i] = fr_zero();
-        const size_t base = c << eq.kl;
-        for (size_t j = threadIdx.x; j < L && base + j < half; j += blockDim.x) {
-            const size_t i = base + j;
+        const size_t base = c * piece;
+        for (size_t jj = threadIdx.x; jj < piece && base + jj < half; jj += blockDim.x) {
+            const size_t j = (base + jj) & lmask;
+            const size_t i = base + jj;
             // Running product polynomial.  It starts as e*R (Montgomery form); the
             // first multiplication by a standard-form value gives e*x exactly and
             // every further one adds a factor 1/R, removed after the grid sum.
@@ -324,7 +345,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_round_kernel(HadamardPtrs p
             for (int d = 0; d <= K; ++d) q[d] = fr_add(q[d], poly[d]);
         }
         if (eq.hi) {
-            const Fr eh = fr_load(eq.hi + c);
+            const Fr eh = fr_load(eq.hi + (base >> eq.kl));
 #pragma unroll
             for (int d = 0; d <= K; ++d) q[d] = fr_mmul(q[d], eh);
         }
@@ -342,19 +363,21 @@ __global__ void __launch_bounds__(kThreads) hadamard_round_kernel(HadamardPtrs p
 // ---------------------------------------------------------------------------
 template <int MODE>
 __global__ void __launch_bounds__(kThreads) legacy_round_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b,
-                                                                 size_t n_in, size_t n_out, Fr v_mont, EqTab eq,
+                                                                 size_t n_in, size_t n_out, Fr v_mont, EqTab eq, unsigned R,
                                                                  Fr* __restrict__ na, Fr* __restrict__ nb,
                                                                  Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
     __shared__ Fr red[32];
     Fr acc[3];
     acc[0] = acc[1] = acc[2] = fr_zero();
-    const size_t L = (size_t)1 << eq.kl;
-    const size_t nchunks = (n_out + L - 1) >> eq.kl;
-    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    const size_t piece = (size_t)blockDim.x * R;          // never straddles a chunk of the low table
+    const size_t npieces = (n_out + piece - 1) / piece;
+    for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
         Fr q0 = fr_zero(), q1 = fr_zero(), q2 = fr_zero();
-        const size_t base = c << eq.kl;
-        for (size_t j = threadIdx.x; j < L && base + j < n_out; j += blockDim.x) {
-            const size_t g = base + j;
+        const size_t base = c * piece;
+        for (size_t jj = threadIdx.x; jj < piece && base + jj < n_out; jj += blockDim.x) {
+            const size_t j = (base + jj) & lmask;
+            const size_t g = base + jj;
             const Fr a0 = fr_load(a + 2 * g);
             const Fr a1 = (2 * g + 1 < n_in) ? fr_load(a + 2 * g + 1) : fr_zero();
             const Fr da = fr_sub(a1, a0);
@@ -380,7 +403,7 @@ __global__ void __launch_bounds__(kThreads) legacy_round_kernel(const Fr* __rest
             q0 = fr_add(q0, t0); q1 = fr_add(q1, t1); q2 = fr_add(q2, t2);
         }
         if (MODE != 0 && eq.hi) {
-            const Fr eh = fr_load(eq.hi + c);
+            const Fr eh = fr_load(eq.hi + (base >> eq.kl));
             q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
         }
         acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
@@ -402,7 +425,7 @@ static int legacy_sumcheck(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_
             buf[i][j] = scratch.get_n<Fr>(half0);
             if (!buf[i][j]) return ZKB_ERR_CUDA;
         }
-    const unsigned max_grid = grid_for((half0 + 4095) / 4096, 1, 4);
+    const unsigned max_grid = (unsigned)sm_count() * 4;
     Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
     unsigned* ticket = scratch.get_n<unsigned>(4);
     const size_t n_out_vals = 3 * (size_t)k + 2;
@@ -426,9 +449,10 @@ static int legacy_sumcheck(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_
             eq.kl = kEqLoBits;
         }
         const Fr v = dev_fr_mont(MODE == 0 ? h_u[r] : h_v[r]);
-        const size_t nchunks = (n_out + ((size_t)1 << eq.kl) - 1) >> eq.kl;
-        ZKB_LAUNCH(legacy_round_kernel<MODE>, grid_for(nchunks, 1, 4), kThreads, 0, s,
-                   ca, cb, n_in, n_out, v, eq, buf[r & 1][0], buf[r & 1][1], partial, ticket, d_proof + 3 * r);
+        unsigned R, grid;
+        pieces_for(n_out, &R, &grid);
+        ZKB_LAUNCH(legacy_round_kernel<MODE>, grid, kThreads, 0, s,
+                   ca, cb, n_in, n_out, v, eq, R, buf[r & 1][0], buf[r & 1][1], partial, ticket, d_proof + 3 * r);
         ca = buf[r & 1][0];
         cb = buf[r & 1][1];
         n_in = n_out;
@@ -578,19 +602,19 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
         const size_t half = M / 2;
         EqTab eq;
         ZKB_TRY(make_eq(h_u, nu - 1, &eq, scratch, s));
-        const size_t nchunks = (half + ((size_t)1 << eq.kl) - 1) >> eq.kl;
-        const unsigned grid = grid_for(nchunks, 1, 4);
+        unsigned R, grid;
+        pieces_for(half, &R, &grid);
         Fr* out = d_sums + 1 + 11 * (size_t)r;
         const int pb = r & 1;
         if (r < k1) {
             const Fr v = dev_fr_mont(h_v[k1 - 1 - r]);
-            ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq,
+            ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq, R,
                        pp[pb][0], pp[pb][1], partial, ticket, out);
             cA = pp[pb][0]; cS = pp[pb][1];
         } else {
             const Fr v = dev_fr_mont(h_v[kD - 1 - (r - k1)]);
             const int qb = (r - k1) & 1;   // B, T, m start shrinking at the first phase-2 round
-            ZKB_LAUNCH(tl_phase2_kernel, grid, kThreads, 0, s, cA, cS, cB, cT, cm, half, beta, v, eq,
+            ZKB_LAUNCH(tl_phase2_kernel, grid, kThreads, 0, s, cA, cS, cB, cT, cm, half, beta, v, eq, R,
                        pp[pb][0], pp[pb][1], pp[qb][2], pp[qb][3], pp[qb][4], partial, ticket, out);
             cA = pp[pb][0]; cS = pp[pb][1]; cB = pp[qb][2]; cT = pp[qb][3]; cm = pp[qb][4];
         }
@@ -685,16 +709,16 @@ int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, u
         ZKB_TRY(make_eq(h_u, kN - 1 - r, &eq, scratch, s));
         for (unsigned j = 0; j < K; ++j) ptrs.out[j] = bufs[r & 1][j];
         const Fr v = dev_fr_mont(h_v[kN - 1 - r]);
-        const size_t nchunks = (half + ((size_t)1 << eq.kl) - 1) >> eq.kl;
-        const unsigned grid = grid_for(nchunks, 1, 4);
+        unsigned R, grid;
+        pieces_for(half, &R, &grid);
         Fr* out = d_sums + (size_t)r * (K + 1);
         switch (K) {
-            case 1: ZKB_LAUNCH(hadamard_round_kernel<1>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
-            case 2: ZKB_LAUNCH(hadamard_round_kernel<2>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
-            case 3: ZKB_LAUNCH(hadamard_round_kernel<3>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
-            case 4: ZKB_LAUNCH(hadamard_round_kernel<4>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
-            case 5: ZKB_LAUNCH(hadamard_round_kernel<5>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
-            default: ZKB_LAUNCH(hadamard_round_kernel<6>, grid, kThreads, 0, s, ptrs, half, v, eq, partial, ticket, out); break;
+            case 1: ZKB_LAUNCH(hadamard_round_kernel<1>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            case 2: ZKB_LAUNCH(hadamard_round_kernel<2>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            case 3: ZKB_LAUNCH(hadamard_round_kernel<3>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            case 4: ZKB_LAUNCH(hadamard_round_kernel<4>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            case 5: ZKB_LAUNCH(hadamard_round_kernel<5>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            default: ZKB_LAUNCH(hadamard_round_kernel<6>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
         }
         for (unsigned j = 0; j < K; ++j) ptrs.in[j] = bufs[r & 1][j];
         M = half;
