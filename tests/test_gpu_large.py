@@ -148,3 +148,40 @@ def test_tlookup_full_size_verifies(dev):
         dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(z.DeviceBuffer.from_host(bad)), z.sz(D), z.sz(N), z._p(alpha),
                  z._p(beta), z._p(u), z._p(v), z._p(polys), z._p(final), z._p(0))
     assert e.value.code == z.ERR_VERIFY
+
+
+def _fr_of_ints(a):
+    import bench
+    return bench.ints_to_fr_limbs(np.asarray(a, dtype=np.int64))
+
+
+@pytest.mark.parametrize("M,N,P,amax,bmax", [(128, 256, 128, 1 << 20, 3000), (100, 300, 150, (1 << 31) - 1, (1 << 31) - 1),
+                                             (257, 129, 131, 70000, 70000), (64, 1024, 64, 1 << 31, 1 << 31)])
+def test_matmul_integer_path_and_its_fallbacks(dev, M, N, P, amax, bmax):
+    """large products of int32-encodings take the exact int64 kernel; products whose sum could pass 2^62 and
+    operands that are not small integers take the field kernel; all agree with exact integer arithmetic"""
+    z = dev.z
+    rng = np.random.Generator(np.random.PCG64(M * N + P))
+    A = rng.integers(-amax, amax, size=(M, N), dtype=np.int64)
+    B = rng.integers(-bmax, bmax, size=(N, P), dtype=np.int64)
+    A[0, 0], B[0, 0] = -amax, -bmax                       # includes -2^31 in the last case
+    exp = [int(v) % R.R_MOD for v in (A.astype(object) @ B.astype(object)).reshape(-1)]
+    dC = z.DeviceBuffer(32 * M * P)
+    dev.call("zkb_fr_matmul", z._p(z.fr_buffer(_fr_of_ints(A))), z._p(z.fr_buffer(_fr_of_ints(B))), z._p(dC), z.sz(M), z.sz(N),
+             z.sz(P), z._p(0))
+    assert R.fr_unpack(dC.to_host(np.uint32, (M * P, 8))) == exp
+
+
+def test_matmul_with_general_field_elements_uses_the_field_kernel(dev):
+    z = dev.z
+    M, N, P = 96, 512, 96
+    rng = np.random.Generator(np.random.PCG64(3))
+    A = rng.integers(-1000, 1000, size=(M, N), dtype=np.int64)
+    hA = _fr_of_ints(A)
+    hB = _rand_fr(rng, N * P)
+    dC = z.DeviceBuffer(32 * M * P)
+    dev.call("zkb_fr_matmul", z._p(z.fr_buffer(hA)), z._p(z.fr_buffer(hB)), z._p(dC), z.sz(M), z.sz(N), z.sz(P), z._p(0))
+    Bv = R.fr_unpack(hB)
+    got = R.fr_unpack(dC.to_host(np.uint32, (M * P, 8)))
+    for (i, j) in ((0, 0), (5, 7), (95, 95), (40, 3)):
+        assert got[i * P + j] == sum(int(A[i, k]) * Bv[k * P + j] for k in range(N)) % R.R_MOD

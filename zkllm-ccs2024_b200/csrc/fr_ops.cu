@@ -489,6 +489,86 @@ __global__ void __launch_bounds__(kThreads) fr_inv_shifted_long_kernel(const Fr*
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Exact integer fast path of the matmul.  Fixed-point activations and weights
+// are field encodings of small signed integers; when every entry of both
+// operands is such an encoding of an int32 and |a|max * |b|max * N < 2^62, the
+// product is computed in int64 (32x32->64 multiply-adds) and encoded back,
+// which gives the same field elements as the Montgomery path at a fraction of
+// the multiply-adds.
+// ---------------------------------------------------------------------------
+// flags[0] = 1 if some entry is not an int32 encoding, flags[1] = max |value|
+__global__ void fr_to_small_kernel(const Fr* __restrict__ a, size_t n, int32_t* __restrict__ out, unsigned* __restrict__ flags) {
+    unsigned mx = 0, bad = 0;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const Fr x = fr_load(a + i);
+        const uint32_t hi = x.v[1] | x.v[2] | x.v[3] | x.v[4] | x.v[5] | x.v[6] | x.v[7];
+        int32_t v = 0;
+        if (!hi && !(x.v[0] >> 31)) {
+            v = (int32_t)x.v[0];
+            mx = max(mx, x.v[0]);
+        } else {
+            const Fr m = fr_neg(x);
+            const uint32_t mhi = m.v[1] | m.v[2] | m.v[3] | m.v[4] | m.v[5] | m.v[6] | m.v[7];
+            if (!mhi && m.v[0] <= 0x80000000u && m.v[0] != 0) {
+                v = (int32_t)(0u - m.v[0]);
+                mx = max(mx, m.v[0]);
+            } else {
+                bad = 1;
+            }
+        }
+        out[i] = v;
+    }
+    if (bad) atomicOr(flags, 1u);
+    if (mx) atomicMax(flags + 1, mx);
+}
+
+static constexpr int kImTile = 64, kImK = 16;
+__global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restrict__ A, const int32_t* __restrict__ B,
+                                                          Fr* __restrict__ C, size_t M, size_t N, size_t P) {
+    __shared__ int32_t As[kImK][kImTile + 1];   // [k][row]
+    __shared__ int32_t Bs[kImK][kImTile];       // [k][col]
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const size_t row0 = (size_t)blockIdx.y * kImTile, col0 = (size_t)blockIdx.x * kImTile;
+    long long acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0;
+    for (size_t k0 = 0; k0 < N; k0 += kImK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int l = threadIdx.x + e * 256;          // 1024 elements per tile
+            const int ar = l >> 4, ak = l & 15;           // A tile: 64 rows x 16 k, k fastest (coalesced along k)
+            const size_t gr = row0 + ar, gk = k0 + ak;
+            As[ak][ar] = (gr < M && gk < N) ? A[gr * N + gk] : 0;
+            const int bk = l >> 6, bc = l & 63;           // B tile: 16 k x 64 cols
+            const size_t gk2 = k0 + bk, gc = col0 + bc;
+            Bs[bk][bc] = (gk2 < N && gc < P) ? B[gk2 * P + gc] : 0;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kImK; ++kk) {
+            int a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty + 16 * i]; b[i] = Bs[kk][tx + 16 * i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += (long long)a[i] * (long long)b[j];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const size_t r = row0 + ty + 16 * i, c = col0 + tx + 16 * j;
+            if (r < M && c < P) fr_store(C + r * P + c, fr_from_i64(acc[i][j]));
+        }
+}
+
 }  // namespace zkb
 
 using namespace zkb;
@@ -698,9 +778,32 @@ int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, v
 }
 int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_t M, size_t N, size_t P, void* stream) {
     if (!M || !P) return ZKB_OK;
+    cudaStream_t s = as_stream(stream);
+    if (N && M * N * P >= ((size_t)1 << 22)) {
+        // try the exact int64 path (worth a small device-to-host read only for large products)
+        Scratch scratch(s);
+        int32_t* ia = scratch.get_n<int32_t>(M * N);
+        int32_t* ib = scratch.get_n<int32_t>(N * P);
+        unsigned* flags = scratch.get_n<unsigned>(4);
+        if (!ia || !ib || !flags) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemsetAsync(flags, 0, 16, s));
+        ZKB_LAUNCH(fr_to_small_kernel, grid_for(M * N, kThreads), kThreads, 0, s, CFR(d_a), M * N, ia, flags);
+        ZKB_LAUNCH(fr_to_small_kernel, grid_for(N * P, kThreads), kThreads, 0, s, CFR(d_b), N * P, ib, flags + 2);
+        unsigned h[4];
+        ZKB_CUDA(cudaMemcpyAsync(h, flags, 16, cudaMemcpyDeviceToHost, s));
+        ZKB_CUDA(cudaStreamSynchronize(s));
+        // |sum| <= N * maxA * maxB must stay below 2^62
+        const unsigned __int128 bound = (unsigned __int128)h[1] * h[3] * N;
+        if (!h[0] && !h[2] && bound < ((unsigned __int128)1 << 62)) {
+            dim3 gi(div_up(P, kImTile), div_up(M, kImTile));
+            if (gi.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^22 rows");
+            ZKB_LAUNCH(i32_matmul_kernel, gi, 256, 0, s, ia, ib, FR(d_c), M, N, P);
+            return ZKB_OK;
+        }
+    }
     dim3 grid(div_up(P, kMmTile), div_up(M, kMmTile));
     if (grid.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^21 rows");
-    ZKB_LAUNCH(fr_matmul_kernel, grid, 256, 0, as_stream(stream), CFR(d_a), CFR(d_b), FR(d_c), M, N, P);
+    ZKB_LAUNCH(fr_matmul_kernel, grid, 256, 0, s, CFR(d_a), CFR(d_b), FR(d_c), M, N, P);
     return ZKB_OK;
 }
 int zkb_fr_split_window(const zkb_fr_t* d_a, size_t n, size_t window, zkb_fr_t* d_out0, zkb_fr_t* d_out1, size_t out_n, void* stream) {
