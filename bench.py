@@ -464,6 +464,68 @@ def run_reference(args) -> dict:
             "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
+def run_layer(args) -> dict:
+    """One Llama-2-7B-shape decoder layer (seq 2048, hidden 4096, FFN 11008, random-init fixed-point weights) through the
+    stage drivers with the reference's command lines and files: parameter commitment, then rmsnorm, self-attn (linear +
+    attn), skip-connection, rmsnorm, ffn, skip-connection.  Wall seconds per stage process (each includes start-up and file
+    I/O).  --impl reference runs the reference's own driver executables (oracle/_ref/drivers, device-LTO build)."""
+    seq, embed, hidden = args.seq, args.embed, args.hidden
+    bindir = (ROOT / "oracle" / "_ref" / "drivers") if args.impl == "reference" else (ROOT / "zkllm-ccs2024_b200" / "bin")
+    if not (bindir / "ffn").exists():
+        return {"impl": args.impl, "workload": "layer", "unavailable": f"{bindir} has no driver executables"}
+    env = dict(os.environ, ZKLLM_CHALLENGE_SEED="2024")
+    stages = {}
+
+    def run(stage, argv, cwd, label=None):
+        t0 = time.perf_counter()
+        res = subprocess.run([str(bindir / stage), *[str(a) for a in argv]], cwd=cwd, env=env, capture_output=True, text=True)
+        dt = time.perf_counter() - t0
+        if res.returncode != 0:
+            raise RuntimeError(f"{stage} failed: {res.stdout[-500:]} {res.stderr[-500:]}")
+        stages[label or stage] = stages.get(label or stage, 0.0) + dt
+
+    with tempfile.TemporaryDirectory(dir=args.tmpdir) as tmp:
+        w = Path(tmp)
+        rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 64))
+        params = [("input_layernorm.weight", 1, embed, embed), ("post_attention_layernorm.weight", 1, embed, embed),
+                  ("self_attn.q_proj.weight", embed, embed, embed << 5), ("self_attn.k_proj.weight", embed, embed, embed << 5),
+                  ("self_attn.v_proj.weight", embed, embed, embed << 5), ("mlp.up_proj.weight", embed, hidden, hidden << 5),
+                  ("mlp.gate_proj.weight", embed, hidden, hidden << 5), ("mlp.down_proj.weight", hidden, embed, embed << 5)]
+        for name, in_dim, out_dim, pp_size in params:
+            if in_dim == 1:
+                wi = np.rint((1.0 + 0.1 * rng.standard_normal(out_dim)) * 65536).astype(np.int32)
+            else:
+                wi = np.rint(rng.standard_normal(in_dim * out_dim) * 0.02 * 65536).astype(np.int32)
+            wi.tofile(w / f"layer-0-{name}-int.bin")
+            run("ppgen", [pp_size, w / f"{name}-pp.bin"], w, "ppgen (8 generator sets)")
+            run("commit-param", [w / f"{name}-pp.bin", w / f"layer-0-{name}-int.bin", w / f"layer-0-{name}-commitment.bin",
+                                 in_dim, out_dim], w, "commit-param (8 parameters)")
+        x = np.rint(rng.standard_normal((seq, embed)) * 65536).astype(np.int32)
+        x.tofile(w / "x0.bin")
+        xs = np.arange(-(1 << 21), 1 << 21, dtype=np.float64) / 4096.0
+        np.rint(xs / (1.0 + np.exp(-xs)) * 16).astype(np.int32).tofile(w / "swiglu-table.bin")
+
+        def rms_inv(path):
+            xf = np.fromfile(path, dtype=np.int32).reshape(seq, embed).astype(np.float64) / 65536.0
+            np.rint(65536.0 / np.sqrt((xf ** 2).mean(axis=1) + 1e-5)).astype(np.int32).tofile(w / "rms_inv_temp.bin")
+
+        rms_inv(w / "x0.bin")
+        run("rmsnorm", ["input", "x0.bin", seq, embed, w, "layer-0", "x1.bin"], w, "rmsnorm (input)")
+        run("self-attn", ["linear", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn linear")
+        run("self-attn", ["attn", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn attn")
+        run("skip-connection", ["x0.bin", "temp_head_out.bin", "x2.bin"], w, "skip-connection (x2)")
+        rms_inv(w / "x2.bin")
+        run("rmsnorm", ["post_attention", "x2.bin", seq, embed, w, "layer-0", "x3.bin"], w, "rmsnorm (post_attention)")
+        run("ffn", ["x3.bin", seq, embed, hidden, w, "layer-0", "x4.bin"], w, "ffn")
+        run("skip-connection", ["x2.bin", "x4.bin", "x5.bin"], w, "skip-connection (x2)")
+        import hashlib
+        digest = hashlib.sha256((w / "x4.bin").read_bytes() + (w / "temp_head_out.bin").read_bytes()).hexdigest()
+    prove = sum(v for k, v in stages.items() if not k.startswith(("ppgen", "commit-param")))
+    return {"metric": "Llama-2-7B-shape layer prove time", "unit": "s", "value": prove, "higher_is_better": False,
+            "impl": args.impl, "workload": f"layer seq {seq} hidden {embed} ffn {hidden}", "stages_s": stages,
+            "commit_params_s": stages.get("commit-param (8 parameters)"), "outputs_sha256": digest, "data": "synthetic"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,10 +534,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=11008)
+    ap.add_argument("--workload", default="commit", choices=["commit", "layer"],
+                    help="commit: the headline MSM benchmark; layer: one decoder layer through the stage drivers")
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--embed", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=11008)
+    ap.add_argument("--tmpdir", default=None)
     ap.add_argument("--no-sumcheck", action="store_true", help="skip the zkFC / tLookup proof timings reported under 'sumcheck'")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    if args.workload == "layer":
+        print(json.dumps(run_layer(args)))
+        return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:
         print(json.dumps(out))
