@@ -476,12 +476,33 @@ def run_layer(args) -> dict:
     env = dict(os.environ, ZKLLM_CHALLENGE_SEED="2024")
     stages = {}
 
+    batch = args.layer_mode == "batch" and args.impl == "ours"
+    server = {"proc": None, "log": []}
+
     def run(stage, argv, cwd, label=None):
         t0 = time.perf_counter()
-        res = subprocess.run([str(bindir / stage), *[str(a) for a in argv]], cwd=cwd, env=env, capture_output=True, text=True)
+        if batch:
+            # one resident driver process (zkllm-driver batch -): a command line in, its "[batch] ..." line back
+            if server["proc"] is None:
+                server["proc"] = subprocess.Popen([str(bindir / "zkllm-driver"), "batch", "-"], cwd=cwd, env=env, text=True,
+                                                  stdin=subprocess.PIPE, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE)
+            pr = server["proc"]
+            pr.stdin.write(" ".join([stage, *[str(a) for a in argv]]) + "\n")
+            pr.stdin.flush()
+            seen = []
+            while True:
+                line = pr.stderr.readline()
+                if not line:
+                    raise RuntimeError(f"{stage} failed in batch mode: {''.join(seen)[-800:]}")
+                seen.append(line)
+                server["log"].append(line)
+                if line.startswith("[batch] "):
+                    break
+        else:
+            res = subprocess.run([str(bindir / stage), *[str(a) for a in argv]], cwd=cwd, env=env, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"{stage} failed: {res.stdout[-500:]} {res.stderr[-500:]}")
         dt = time.perf_counter() - t0
-        if res.returncode != 0:
-            raise RuntimeError(f"{stage} failed: {res.stdout[-500:]} {res.stderr[-500:]}")
         stages[label or stage] = stages.get(label or stage, 0.0) + dt
 
     with tempfile.TemporaryDirectory(dir=args.tmpdir) as tmp:
@@ -509,20 +530,40 @@ def run_layer(args) -> dict:
             xf = np.fromfile(path, dtype=np.int32).reshape(seq, embed).astype(np.float64) / 65536.0
             np.rint(65536.0 / np.sqrt((xf ** 2).mean(axis=1) + 1e-5)).astype(np.int32).tofile(w / "rms_inv_temp.bin")
 
-        rms_inv(w / "x0.bin")
-        run("rmsnorm", ["input", "x0.bin", seq, embed, w, "layer-0", "x1.bin"], w, "rmsnorm (input)")
-        run("self-attn", ["linear", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn linear")
-        run("self-attn", ["attn", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn attn")
-        run("skip-connection", ["x0.bin", "temp_head_out.bin", "x2.bin"], w, "skip-connection (x2)")
-        rms_inv(w / "x2.bin")
-        run("rmsnorm", ["post_attention", "x2.bin", seq, embed, w, "layer-0", "x3.bin"], w, "rmsnorm (post_attention)")
-        run("ffn", ["x3.bin", seq, embed, hidden, w, "layer-0", "x4.bin"], w, "ffn")
-        run("skip-connection", ["x2.bin", "x4.bin", "x5.bin"], w, "skip-connection (x2)")
+        def prove_layer():
+            rms_inv(w / "x0.bin")
+            run("rmsnorm", ["input", "x0.bin", seq, embed, w, "layer-0", "x1.bin"], w, "rmsnorm (input)")
+            run("self-attn", ["linear", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn linear")
+            run("self-attn", ["attn", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn attn")
+            run("skip-connection", ["x0.bin", "temp_head_out.bin", "x2.bin"], w, "skip-connection (x2)")
+            rms_inv(w / "x2.bin")
+            run("rmsnorm", ["post_attention", "x2.bin", seq, embed, w, "layer-0", "x3.bin"], w, "rmsnorm (post_attention)")
+            run("ffn", ["x3.bin", seq, embed, hidden, w, "layer-0", "x4.bin"], w, "ffn")
+            run("skip-connection", ["x2.bin", "x4.bin", "x5.bin"], w, "skip-connection (x2)")
+
+        setup = dict(stages)
+        passes = []
+        for _ in range(max(1, args.layer_repeat)):
+            stages.clear()
+            prove_layer()
+            passes.append(dict(stages))
+        stages.clear()
+        stages.update(setup)
+        stages.update(passes[-1])
+        if server["proc"] is not None:
+            server["proc"].stdin.close()
+            server["log"].extend(server["proc"].stderr.readlines())
+            if args.layer_log:
+                Path(args.layer_log).write_text("".join(server["log"]))
+            if server["proc"].wait(timeout=60) != 0:
+                raise RuntimeError("batch driver exited with an error")
         import hashlib
         digest = hashlib.sha256((w / "x4.bin").read_bytes() + (w / "temp_head_out.bin").read_bytes()).hexdigest()
     prove = sum(v for k, v in stages.items() if not k.startswith(("ppgen", "commit-param")))
     return {"metric": "Llama-2-7B-shape layer prove time", "unit": "s", "value": prove, "higher_is_better": False,
             "impl": args.impl, "workload": f"layer seq {seq} hidden {embed} ffn {hidden}", "stages_s": stages,
+            "mode": "one resident driver process" if batch else "one process per stage",
+            "passes_s": [sum(p.values()) for p in passes],
             "commit_params_s": stages.get("commit-param (8 parameters)"), "outputs_sha256": digest, "data": "synthetic"}
 
 
@@ -540,6 +581,13 @@ def main():
     ap.add_argument("--embed", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=11008)
     ap.add_argument("--tmpdir", default=None)
+    ap.add_argument("--layer-repeat", type=int, default=1, help="layer workload: prove the layer this many times (the value "
+                    "reported is the last pass; passes_s lists all)")
+    ap.add_argument("--layer-log", default=None, help="layer workload, batch mode: write the driver's stderr (stage times, and "
+                    "per-kernel times when ZKLLM_PROFILE=1) to this file")
+    ap.add_argument("--layer-mode", default="batch", choices=["batch", "process"],
+                    help="layer workload, our arm: all stages in one resident driver process, or one process per stage as the "
+                         "reference's Python glue does (the reference arm always runs one process per stage)")
     ap.add_argument("--no-sumcheck", action="store_true", help="skip the zkFC / tLookup proof timings reported under 'sumcheck'")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -67,8 +67,15 @@ int zkb_bench_imad(int mode, unsigned iters, double* h_gops, void* stream);
 
 /* ---- device memory (FrTensor/G1Tensor ctors, dtors, copies:
  *      fr-tensor.cu:158-179, g1-tensor.cu:40-60,123-152) ------------------------- */
-int zkb_malloc(void** d_ptr, size_t bytes);
-int zkb_free(void* d_ptr);
+int zkb_malloc(void** d_ptr, size_t bytes);   /* usable at once on any stream */
+int zkb_free(void* d_ptr);                    /* waits for the device first, like cudaFree */
+/* Page-locked host memory and copies that do not wait (no counterpart in the
+ * reference, whose ioutils.cu:3-45 stages files through pageable memory): the host
+ * buffer must stay untouched until zkb_sync on the same stream. */
+int zkb_host_alloc(void** h_ptr, size_t bytes);
+int zkb_host_free(void* h_ptr);
+int zkb_memcpy_h2d_async(void* d_dst, const void* h_src, size_t bytes, void* stream);
+int zkb_memcpy_d2h_async(void* h_dst, const void* d_src, size_t bytes, void* stream);
 int zkb_memcpy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
 int zkb_memcpy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
 int zkb_memcpy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);

@@ -110,3 +110,13 @@ def tlookup_prove(S, T, m, alpha, beta, u, v, nthreads: int = 0):
     rc = lib().zko_tlookup_prove(_p(S), _p(T), _p(m), sz(D), sz(N), _p(alpha), _p(beta), _p(pad(u)), _p(pad(v)),
                                  _p(polys), _p(final), ctypes.c_int(nthreads))
     return rc, polys[:4 * kD], final
+
+
+def me_open(t: np.ndarray, gens: np.ndarray, u: np.ndarray):
+    """Commitment::me_open: returns (proof [3k+1, 36] Jacobian points, final scalar [1, 8])."""
+    n, k = t.shape[0], u.shape[0]
+    proof = np.zeros((3 * k + 1, 36), dtype=np.uint32)
+    out = np.zeros((1, 8), dtype=np.uint32)
+    pad = u if k else np.zeros((1, 8), dtype=np.uint32)
+    lib().zko_me_open(_p(t), _p(gens), sz(n), _p(pad), ctypes.c_uint(k), _p(proof), _p(out))
+    return proof, out

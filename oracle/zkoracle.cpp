@@ -210,6 +210,55 @@ void zko_commit_int_pippenger(const uint32_t* gens, size_t n, const int32_t* sca
     for (long r = 0; r < (long)m; ++r) st_g1(out + 36 * r, msm_row_pippenger(bases, scalars + (size_t)r * n, n, W));
 }
 
+// scalar product by the raw bits of k, as G1Jacobian_mul does (g1-tensor.cu:445-453)
+static G1 g1_mul_raw(G1 a, const FrE& k) {
+    G1 acc = g1_zero();
+    for (int bit = 0; bit < 256; ++bit) {
+        if ((k.l[bit >> 6] >> (bit & 63)) & 1) acc = g1_add(acc, a);
+        a = g1_double(a);
+    }
+    return acc;
+}
+
+// Commitment::me_open with me_open_step's five products per pair (commitment.cu:79-125).
+void zko_me_open(const uint32_t* t, const uint32_t* gens, size_t n, const uint32_t* u, unsigned k, uint32_t* proof, uint32_t* out) {
+    std::vector<FrE> sc(n);
+    std::vector<G1> g(n);
+    for (size_t i = 0; i < n; ++i) { sc[i] = ld_fr(t + 8 * i); g[i] = ld_g1(gens + 36 * i); }
+    for (unsigned r = 0; r < k; ++r) {
+        const size_t cur = sc.size(), nn = (cur + 1) / 2;
+        const FrE us = ld_fr(u + 8 * r), um = Fr::to_mont(us);
+        std::vector<FrE> ns(nn);
+        std::vector<G1> ng(nn), a(nn), a0(nn), a1(nn);
+#pragma omp parallel for schedule(dynamic)
+        for (long j = 0; j < (long)nn; ++j) {
+            const size_t i0 = 2 * j, i1 = 2 * j + 1;
+            if (i1 >= cur) {
+                ns[j] = Fr::sub(sc[i0], Fr::mmul(um, sc[i0]));
+                ng[j] = g1_mul_raw(g[i0], us);
+                a[j] = g1_mul_raw(g[i0], sc[i0]);
+                a0[j] = g1_zero();
+                a1[j] = g1_zero();
+                continue;
+            }
+            ns[j] = Fr::add(sc[i0], Fr::mmul(um, Fr::sub(sc[i1], sc[i0])));
+            ng[j] = g1_add(g[i1], g1_mul_raw(g1_add(g[i0], g1_neg(g[i1])), us));
+            a[j] = g1_add(g1_mul_raw(g[i0], sc[i0]), g1_mul_raw(g[i1], sc[i1]));
+            a0[j] = g1_mul_raw(g[i1], sc[i0]);
+            a1[j] = g1_mul_raw(g[i0], sc[i1]);
+        }
+        G1 s = g1_zero(), s0 = g1_zero(), s1 = g1_zero();
+        for (size_t j = 0; j < nn; ++j) { s = g1_add(s, a[j]); s0 = g1_add(s0, a0[j]); s1 = g1_add(s1, a1[j]); }
+        st_g1(proof + 36 * (3 * r), s);
+        st_g1(proof + 36 * (3 * r + 1), s0);
+        st_g1(proof + 36 * (3 * r + 2), s1);
+        sc.swap(ns);
+        g.swap(ng);
+    }
+    st_g1(proof + 36 * 3 * (size_t)k, g[0]);
+    st_fr(out, sc[0]);
+}
+
 void zko_mle_eval(const uint32_t* a, size_t n, const uint32_t* u, unsigned k, uint32_t* out) {
     std::vector<FrE> t(n), uu(k);
     for (size_t i = 0; i < n; ++i) t[i] = ld_fr(a + 8 * i);

@@ -23,6 +23,9 @@ int zko_zkfc_prove(const uint32_t* X, const uint32_t* W, const uint32_t* Y, size
 int zko_tlookup_prove(const uint32_t* S, const uint32_t* T, const uint32_t* m, size_t D, size_t N,
                       const uint32_t* alpha, const uint32_t* beta, const uint32_t* u, const uint32_t* v,
                       uint32_t* polys, uint32_t* final_claim, int threads);
+/* Commitment::me_open (commitment.cu:79-125): t[n] in the form the caller holds (raw limbs are read as scalar bits),
+ * gens[n] Jacobian, u[k] standard form.  proof gets 3k+1 Jacobian points, out the final scalar. */
+void zko_me_open(const uint32_t* t, const uint32_t* gens, size_t n, const uint32_t* u, unsigned k, uint32_t* proof, uint32_t* out);
 #ifdef __cplusplus
 }
 #endif

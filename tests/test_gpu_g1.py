@@ -192,7 +192,7 @@ def test_commit_full_width(dev, gens, m, n):
         assert affine_eq(out[r], exp[r]), r
 
 
-@pytest.mark.parametrize("n,k", [(1, 0), (2, 1), (4, 2), (5, 3), (8, 3)])
+@pytest.mark.parametrize("n,k", [(1, 0), (2, 1), (4, 2), (5, 3), (8, 3), (3, 4), (1, 2), (8, 2)])
 def test_me_open(dev, gens, n, k):
     z = dev.z
     rng = random.Random(n * 7 + k)

@@ -185,3 +185,81 @@ def test_matmul_with_general_field_elements_uses_the_field_kernel(dev):
     got = R.fr_unpack(dC.to_host(np.uint32, (M * P, 8)))
     for (i, j) in ((0, 0), (5, 7), (95, 95), (40, 3)):
         assert got[i * P + j] == sum(int(A[i, k]) * Bv[k * P + j] for k in range(N)) % R.R_MOD
+
+
+def _rand_fr_limbs(rng, n):
+    s = rng.integers(0, 1 << 32, size=(n, 8), dtype=np.uint64).astype(np.uint32)
+    s[:, 7] %= np.uint32(R.R_MOD >> 224)
+    return s
+
+
+def _me_open(dev, d_t, d_g, n, u):
+    z = dev.z
+    k = u.shape[0]
+    hp = np.zeros((3 * k + 1, 36), dtype=np.uint32)
+    ho = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_me_open", z._p(d_t), z._p(d_g), z.sz(n), z._p(u if k else np.zeros((1, 8), np.uint32)), z.u32(k), z._p(hp),
+             z._p(ho), z._p(0))
+    return hp, ho
+
+
+@pytest.mark.parametrize("n,k", [(300, 9), (1000, 10), (4096, 12), (4097, 13)])
+def test_me_open_against_cpp_oracle(dev, n, k):
+    """opening proof with odd lengths along the way (300 -> 150 -> 75 -> 38 -> 19 ...) and several column segments"""
+    z = dev.z
+    d_g, h_g = gpu_generators(dev, n, 31 + n)
+    rng = np.random.Generator(np.random.PCG64(n + k))
+    t, u = _rand_fr_limbs(rng, n), _rand_fr_limbs(rng, k)
+    hp, ho = _me_open(dev, z.DeviceBuffer.from_host(t), d_g, n, u)
+    exp_proof, exp_out = C.me_open(t, h_g, u)
+    assert np.array_equal(ho, exp_out)
+    assert np.array_equal(C.g1_normalise(hp), C.g1_normalise(exp_proof))
+
+
+def test_me_open_with_identity_generators_and_zero_scalars(dev):
+    z = dev.z
+    n, k = 600, 10
+    d_g, h_g = gpu_generators(dev, n, 5)
+    h_g = h_g.copy()
+    h_g[[0, 7, 8, 9, 599]] = 0                      # Z = 0: the identity
+    h_g[11] = h_g[10]                               # equal neighbours: g0 - g1 is the identity
+    d_g = z.DeviceBuffer.from_host(h_g)
+    rng = np.random.Generator(np.random.PCG64(77))
+    t, u = _rand_fr_limbs(rng, n), _rand_fr_limbs(rng, k)
+    t[[3, 4, 8, 100]] = 0
+    u[2] = 0
+    u[3] = R.fr_pack([1])[0]
+    hp, ho = _me_open(dev, z.DeviceBuffer.from_host(t), d_g, n, u)
+    exp_proof, exp_out = C.me_open(t, h_g, u)
+    assert np.array_equal(ho, exp_out)
+    assert np.array_equal(C.g1_normalise(hp), C.g1_normalise(exp_proof))
+
+
+@pytest.mark.parametrize("n", [100000, 1 << 19])
+def test_me_open_round_identities_at_full_width(dev, n):
+    """Size-independent check of an opening over 2^19 generators (the FFN weights' row length): with
+    s' = s0 + u (s1 - s0) and g' = g1 + u (g0 - g1), the next round's T is u(1-u) T + (1-u)^2 T0 + u^2 T1, the last one is
+    (final scalar) * (final generator), and the first T is the plain sum of products."""
+    z = dev.z
+    k = (n - 1).bit_length()
+    d_g, _ = gpu_generators(dev, n, 2024)
+    rng = np.random.Generator(np.random.PCG64(n))
+    t, u = _rand_fr_limbs(rng, n), _rand_fr_limbs(rng, k)
+    d_t = z.DeviceBuffer.from_host(t)
+    hp, ho = _me_open(dev, d_t, d_g, n, u)
+    # first T by the elementwise product kernel and the tree sum
+    prod = z.DeviceBuffer(144 * n)
+    dev.call("zkb_g1_mul", z._p(d_g), z.sz(n), z._p(d_t), z.sz(n), z._p(prod), z._p(0))
+    t0 = np.zeros((1, 36), dtype=np.uint32)
+    dev.call("zkb_g1_sum", z._p(prod), z.sz(n), z._p(t0), z._p(0))
+    assert np.array_equal(C.g1_normalise(t0), C.g1_normalise(np.ascontiguousarray(hp[0:1])))
+    uu = R.fr_unpack(u)
+    coeff = []
+    for x in uu:
+        coeff += [x * (1 - x) % R.R_MOD, (1 - x) * (1 - x) % R.R_MOD, x * x % R.R_MOD]
+    terms = C.g1_mul(np.ascontiguousarray(hp[:3 * k]), R.fr_pack(coeff))
+    part = [np.ascontiguousarray(terms[i::3]) for i in range(3)]
+    nxt = C.g1_add(C.g1_add(part[0], part[1]), part[2])          # T of round r + 1, for r = 0..k-1
+    last = C.g1_mul(np.ascontiguousarray(hp[3 * k:3 * k + 1]), ho)                                  # final scalar (raw limbs) * final generator
+    expect = np.ascontiguousarray(np.concatenate([hp[3:3 * k:3], last]))
+    assert np.array_equal(C.g1_normalise(nxt), C.g1_normalise(expect))

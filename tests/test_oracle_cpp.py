@@ -63,3 +63,15 @@ def test_zkfc_and_tlookup():
         p = R.fr_unpack(polys)
         assert [p[4 * i:4 * i + 4] for i in range(k)] == [(q + [0, 0, 0, 0])[:4] for q in exp_p]
         assert R.fr_unpack(final)[0] == exp_c
+
+
+def test_me_open():
+    rng = random.Random(5)
+    for n, k in [(1, 0), (5, 3), (8, 3)]:
+        gens = seeded_generators(n, 40 + n)
+        t, u = rand_fr(rng, n), rand_fr(rng, k)
+        proof = []
+        exp = R.me_open(t, gens, u, proof)
+        got_proof, got = C.me_open(R.fr_pack(t), R.g1_pack(gens), R.fr_pack(u) if k else np.zeros((0, 8), dtype=np.uint32))
+        assert R.fr_unpack(got)[0] == exp
+        assert [R.g1_affine(p) for p in R.g1_unpack(got_proof)] == [R.g1_affine(p) for p in proof]

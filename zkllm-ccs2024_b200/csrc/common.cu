@@ -137,13 +137,39 @@ int zkb_profile_read(char* buf, size_t cap) {
     return ZKB_OK;
 }
 
+// Device buffers come from the device's stream-ordered pool (which keeps freed
+// memory for reuse), allocated and released on the null stream.  zkb_malloc
+// returns memory that is usable at once on any stream; zkb_free first waits for
+// the whole device, like cudaFree, so work still running on any stream is safe.
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");
-    ZKB_CUDA(cudaMalloc(d_ptr, bytes ? bytes : 16));
+    ensure_pool_keeps_memory();
+    ZKB_CUDA(cudaMallocAsync(d_ptr, bytes ? bytes : 16, (cudaStream_t)0));
+    ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     return ZKB_OK;
 }
 int zkb_free(void* d_ptr) {
-    ZKB_CUDA(cudaFree(d_ptr));
+    if (!d_ptr) return ZKB_OK;
+    ZKB_CUDA(cudaDeviceSynchronize());
+    ZKB_CUDA(cudaFreeAsync(d_ptr, (cudaStream_t)0));
+    return ZKB_OK;
+}
+int zkb_host_alloc(void** h_ptr, size_t bytes) {
+    if (!h_ptr) return fail(ZKB_ERR_ARG, "zkb_host_alloc: null out pointer");
+    ZKB_CUDA(cudaHostAlloc(h_ptr, bytes ? bytes : 16, cudaHostAllocDefault));
+    return ZKB_OK;
+}
+int zkb_host_free(void* h_ptr) {
+    if (!h_ptr) return ZKB_OK;
+    ZKB_CUDA(cudaFreeHost(h_ptr));
+    return ZKB_OK;
+}
+int zkb_memcpy_h2d_async(void* d_dst, const void* h_src, size_t bytes, void* stream) {
+    ZKB_CUDA(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));
+    return ZKB_OK;
+}
+int zkb_memcpy_d2h_async(void* h_dst, const void* d_src, size_t bytes, void* stream) {
+    ZKB_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, as_stream(stream)));
     return ZKB_OK;
 }
 int zkb_memcpy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream) {

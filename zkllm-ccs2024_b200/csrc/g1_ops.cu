@@ -1,6 +1,6 @@
 // G1 tensor device work: elementwise group operations, affine normalisation,
 // scalar multiplication, sums, the multilinear fold in the exponent and the
-// opening rounds of the commitment (me_open).
+// (the opening rounds of the commitment, me_open, live beside the MSM).
 #include "frutil.cuh"
 #include "g1.cuh"
 #include "hostfr.hpp"
@@ -105,36 +105,6 @@ __global__ void __launch_bounds__(kG1Threads) g1_me_step_kernel(const G1Jac* __r
             r = g1_add(p0, g1_neg(g1_mul_bits(p0, x_bits)));
         }
         g1_store(out + g, r);
-    }
-}
-
-// One opening round (me_open_step, commitment.cu:79-107).  Per pair (2g, 2g+1):
-//   new_scalar = s0 + u (s1 - s0)            new_gen = g1 + u (g0 - g1)
-//   t  = s0 g0 + s1 g1        t0 = s0 g1        t1 = s1 g0
-// A lone last element folds against "nothing" exactly as the reference does.
-__global__ void __launch_bounds__(kG1Threads) me_open_step_kernel(const Fr* __restrict__ sc, const G1Jac* __restrict__ gen,
-                                                                   Fr u_std, Fr u_mont, size_t old_size, size_t new_size,
-                                                                   Fr* __restrict__ nsc, G1Jac* __restrict__ ngen,
-                                                                   G1Jac* __restrict__ t, G1Jac* __restrict__ t0, G1Jac* __restrict__ t1) {
-    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
-        const size_t i0 = 2 * g, i1 = 2 * g + 1;
-        const Fr s0 = fr_load(sc + i0);
-        const G1Jac g0 = g1_load(gen + i0);
-        if (i1 >= old_size) {
-            fr_store(nsc + g, fr_sub(s0, fr_mmul(u_mont, s0)));
-            g1_store(ngen + g, g1_mul_bits(g0, u_std));
-            g1_store(t + g, g1_mul_bits(g0, s0));
-            g1_store(t0 + g, g1_identity());
-            g1_store(t1 + g, g1_identity());
-            continue;
-        }
-        const Fr s1 = fr_load(sc + i1);
-        const G1Jac g1p = g1_load(gen + i1);
-        fr_store(nsc + g, fr_add(s0, fr_mmul(u_mont, fr_sub(s1, s0))));
-        g1_store(ngen + g, g1_add(g1p, g1_mul_bits(g1_add(g0, g1_neg(g1p)), u_std)));
-        g1_store(t + g, g1_add(g1_mul_bits(g0, s0), g1_mul_bits(g1p, s1)));
-        g1_store(t0 + g, g1_mul_bits(g1p, s0));
-        g1_store(t1 + g, g1_mul_bits(g0, s1));
     }
 }
 
@@ -259,40 +229,6 @@ int zkb_g1_mle_eval(const zkb_g1_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned
         n_in = n_out;
     }
     ZKB_CUDA(cudaMemcpyAsync(h_out, cur, sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
-    ZKB_CUDA(cudaStreamSynchronize(s));
-    return ZKB_OK;
-}
-
-int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
-                zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
-    cudaStream_t s = as_stream(stream);
-    if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
-    Scratch scratch(s);
-    const size_t h0 = (n + 1) / 2;
-    Fr* sc[2] = {scratch.get_n<Fr>(h0), scratch.get_n<Fr>(h0)};
-    G1Jac* gn[2] = {scratch.get_n<G1Jac>(h0), scratch.get_n<G1Jac>(h0)};
-    G1Jac* tmp = scratch.get_n<G1Jac>(3 * h0);
-    G1Jac* d_proof = scratch.get_n<G1Jac>(3 * (size_t)k + 1);
-    if (!sc[0] || !sc[1] || !gn[0] || !gn[1] || !tmp || !d_proof) return ZKB_ERR_CUDA;
-    const Fr* cs = CFR(d_t);
-    const G1Jac* cg = CG1(d_gens);
-    size_t cur = n;
-    for (unsigned r = 0; r < k; ++r) {
-        const size_t nn = (cur + 1) / 2;
-        const Fr u_std = host_fr(h_u[r]);
-        const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
-        ZKB_LAUNCH(me_open_step_kernel, grid_for(nn, kG1Threads), kG1Threads, 0, s, cs, cg, u_std, u_mont, cur, nn,
-                   sc[r & 1], gn[r & 1], tmp, tmp + h0, tmp + 2 * h0);
-        // the three sums of this round: rows of a [3, nn] view with row stride h0
-        for (int q = 0; q < 3; ++q)
-            ZKB_TRY(g1_rowwise_sum_device(tmp + q * h0, 1, nn, d_proof + 3 * r + q, scratch, s));
-        cs = sc[r & 1];
-        cg = gn[r & 1];
-        cur = nn;
-    }
-    ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k, cg, sizeof(G1Jac), cudaMemcpyDeviceToDevice, s));
-    ZKB_CUDA(cudaMemcpyAsync(h_proof, d_proof, (3 * (size_t)k + 1) * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
-    ZKB_CUDA(cudaMemcpyAsync(h_out, cs, 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return ZKB_OK;
 }

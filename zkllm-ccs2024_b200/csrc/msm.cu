@@ -23,6 +23,7 @@
 #include "g1.cuh"
 #include "hostfr.hpp"
 
+#include <mutex>
 #include <vector>
 
 namespace zkb {
@@ -274,14 +275,32 @@ __global__ void __launch_bounds__(128) msm_finish_kernel(const G1Jac* __restrict
     }
 }
 
-__global__ void g1_to_affine_simple_kernel(const G1Jac* __restrict__ a, G1Aff* __restrict__ out, size_t n) {
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+// Jacobian -> affine with one field inversion per thread shared by `per_thread`
+// points (Montgomery's trick).  A block owns blockDim.x * per_thread consecutive
+// points; thread t takes t, t + blockDim.x, ...  The running prefix product of
+// the z coordinates is parked in out[i].x until the way back.
+__global__ void __launch_bounds__(128) g1_to_affine_batched_kernel(const G1Jac* __restrict__ a, G1Aff* __restrict__ out, size_t n,
+                                                                    unsigned per_thread) {
+    const size_t tile0 = (size_t)blockIdx.x * blockDim.x * per_thread + threadIdx.x;
+    Fq acc = fe_mont_one<FqParams>();
+    for (unsigned j = 0; j < per_thread; ++j) {
+        const size_t i = tile0 + (size_t)j * blockDim.x;
+        if (i >= n) break;
+        const Fq z = fe_load(&a[i].z);
+        fe_store(&out[i].x, acc);
+        if (!fe_is_zero(z)) acc = fq_mul(acc, z);
+    }
+    Fq inv = mont_inv<FqParams>(acc);
+    for (int j = (int)per_thread - 1; j >= 0; --j) {
+        const size_t i = tile0 + (size_t)j * blockDim.x;
+        if (i >= n) continue;
         const G1Jac p = g1_load(a + i);
         G1Aff r;
         if (g1_is_identity(p)) {
             r.x = fe_zero<FqParams>(); r.y = fe_zero<FqParams>();
         } else {
-            const Fq zi = mont_inv<FqParams>(p.z);
+            const Fq zi = fq_mul(inv, fe_load(&out[i].x));
+            inv = fq_mul(inv, p.z);
             const Fq zi2 = fq_sqr(zi);
             r.x = fq_mul(p.x, zi2);
             r.y = fq_mul(p.y, fq_mul(zi2, zi));
@@ -290,16 +309,84 @@ __global__ void g1_to_affine_simple_kernel(const G1Jac* __restrict__ a, G1Aff* _
     }
 }
 
-// Shared driver.  `scalars` is int32[m*n] (FULL = false) or Fr[m*n] (FULL = true).
+static int to_affine_device(const G1Jac* d_a, G1Aff* d_out, size_t n, cudaStream_t s) {
+    if (n == 0) return ZKB_OK;
+    size_t per_thread = n / 32768;
+    if (per_thread < 1) per_thread = 1;
+    if (per_thread > 32) per_thread = 32;
+    const size_t tile = 128 * per_thread;
+    ZKB_LAUNCH(g1_to_affine_batched_kernel, (unsigned)((n + tile - 1) / tile), 128, 0, s, d_a, d_out, n, (unsigned)per_thread);
+    return ZKB_OK;
+}
+
+// ---- few rows, many windows: bucket partials are first summed over the segments,
+// then every (row, window) total is formed in parallel and one thread per row
+// runs Horner over the windows. -----------------------------------------------------
+// Block of 128 threads = 16 buckets x 8 segment parts.  red[(row*W + w)*64 + b].
+__global__ void __launch_bounds__(128) msm_seg_reduce_kernel(const G1Jac* __restrict__ buckets, MsmShape sh, G1Jac* __restrict__ red) {
+    __shared__ G1Jac sm[128];
+    const unsigned part = threadIdx.x & 7, bl = threadIdx.x >> 3;
+    const size_t rwq = blockIdx.x;                     // (row*W + w)*4 + quarter
+    const unsigned b = (unsigned)(rwq & 3) * 16 + bl;
+    const unsigned w = (unsigned)((rwq >> 2) % sh.W);
+    const size_t row = (rwq >> 2) / sh.W;
+    G1Jac acc = g1_identity();
+    for (unsigned sg = part; sg < sh.nseg; sg += 8) {
+        const size_t list_id = (row * sh.nseg + sg) * sh.W + w;
+        acc = g1_add(acc, g1_load(buckets + list_id * kBuckets + b));
+    }
+    sm[threadIdx.x] = acc;
+    __syncthreads();
+    for (unsigned step = 4; step > 0; step >>= 1) {
+        if (part < step) sm[threadIdx.x] = g1_add(sm[threadIdx.x], sm[threadIdx.x + step]);
+        __syncthreads();
+    }
+    if (part == 0) g1_store(red + (rwq >> 2) * kBuckets + b, sm[threadIdx.x]);
+}
+
+// Thread per (row, window): total of the window from its eight group results.
+__global__ void __launch_bounds__(64) msm_window_kernel(const G1Jac* __restrict__ Lg, const G1Jac* __restrict__ Gg, size_t n_rw,
+                                                         G1Jac* __restrict__ win) {
+    for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < n_rw; t += (size_t)gridDim.x * blockDim.x) {
+        const size_t base = t * 8;
+        G1Jac lsum = g1_identity(), run = g1_identity(), acc = g1_identity();
+        for (int g = 7; g >= 0; --g) {
+            lsum = g1_add(lsum, g1_load(Lg + base + g));
+            if (g >= 1) {
+                run = g1_add(run, g1_load(Gg + base + g));
+                acc = g1_add(acc, run);
+            }
+        }
+        acc = g1_double(g1_double(g1_double(acc)));
+        g1_store(win + t, g1_add(lsum, acc));
+    }
+}
+
+__global__ void __launch_bounds__(32) msm_horner_kernel(const G1Jac* __restrict__ win, MsmShape sh, G1Jac* __restrict__ out) {
+    for (size_t row = blockIdx.x * (size_t)blockDim.x + threadIdx.x; row < sh.m; row += (size_t)gridDim.x * blockDim.x) {
+        G1Jac acc = g1_load(win + row * sh.W + (sh.W - 1));
+        for (int w = sh.W - 2; w >= 0; --w) {
+            for (int d = 0; d < kWinBits; ++d) acc = g1_double(acc);
+            acc = g1_add(acc, g1_load(win + row * sh.W + w));
+        }
+        g1_store(out + row, acc);
+    }
+}
+
+// Shared driver over affine bases.  `scalars` is int32[m*n] (FULL = false) or raw
+// 256-bit Fr limbs [m*n] (FULL = true).
 template <bool FULL>
-static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t m, int W,
-                    G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, size_t m, int W,
+                           G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
     if (m == 0) return ZKB_OK;
     MsmShape sh;
     sh.m = m; sh.n = n; sh.W = W;
-    // enough (row, segment) lists to fill warps, segments no longer than kMaxSeg
-    size_t nseg = (4096 + m - 1) / m;
-    const size_t min_seg_len = 256;
+    // enough (row, segment) lists to fill warps, segments no longer than kMaxSeg.
+    // One list group of 32 lanes gives W * 64 warps, so full-width scalars need
+    // only a few groups and prefer long lists; small integers need thousands.
+    const size_t want_lists = FULL ? 96 : 4096;
+    size_t nseg = (want_lists + m - 1) / m;
+    const size_t min_seg_len = FULL ? 64 : 256;
     if (nseg > (n + min_seg_len - 1) / min_seg_len) nseg = (n + min_seg_len - 1) / min_seg_len;
     if (nseg < (n + kMaxSeg - 1) / kMaxSeg) nseg = (n + kMaxSeg - 1) / kMaxSeg;
     if (nseg < 1) nseg = 1;
@@ -309,18 +396,17 @@ static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t
     sh.seg = (unsigned)((n + nseg - 1) / nseg);
     const size_t n_rs = m * nseg;
     const size_t n_lists = n_rs * W;
+    const bool few_rows = m * W < 4096;
 
-    G1Aff* bases = scratch.get_n<G1Aff>(n);
     uint16_t* ent = scratch.get_n<uint16_t>(n_lists * sh.seg);
     uint16_t* offs = scratch.get_n<uint16_t>(n_lists * (kBuckets + 1));
     G1Jac* buckets = scratch.get_n<G1Jac>(n_lists * kBuckets);
     G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
     G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
     uint32_t* perm = scratch.get_n<uint32_t>((size_t)W * kBuckets * n_rs);
-    if (!bases || !ent || !offs || !buckets || !Lg || !Gg || !perm) return ZKB_ERR_CUDA;
+    if (!ent || !offs || !buckets || !Lg || !Gg || !perm) return ZKB_ERR_CUDA;
     if (n_rs > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
 
-    ZKB_LAUNCH(g1_to_affine_simple_kernel, grid_for(n, 128), 128, 0, s, d_gens, bases, n);
     // rows go to gridDim.y in slices of at most 65535
     for (size_t r0 = 0; r0 < m; r0 += 65535) {
         const size_t rows = (m - r0 < 65535) ? m - r0 : 65535;
@@ -337,9 +423,37 @@ static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t
     if (acc_blocks > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
     ZKB_LAUNCH(msm_schedule_kernel, (unsigned)(W * kBuckets), 256, 0, s, offs, sh, n_rs, perm);
     ZKB_LAUNCH(msm_accumulate_kernel, (unsigned)acc_blocks, kAccWarps * 32, 0, s, bases, sh, ent, offs, perm, buckets, n_units);
-    ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 128), 128, 0, s, buckets, sh, Lg, Gg);
-    ZKB_LAUNCH(msm_finish_kernel, grid_for(m, 128), 128, 0, s, Lg, Gg, sh, d_out);
+    if (!few_rows) {
+        ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 128), 128, 0, s, buckets, sh, Lg, Gg);
+        ZKB_LAUNCH(msm_finish_kernel, grid_for(m, 128), 128, 0, s, Lg, Gg, sh, d_out);
+        return ZKB_OK;
+    }
+    G1Jac* win = scratch.get_n<G1Jac>(m * W);
+    if (!win) return ZKB_ERR_CUDA;
+    const G1Jac* src = buckets;
+    MsmShape one = sh;
+    if (nseg > 1) {
+        G1Jac* red = scratch.get_n<G1Jac>(m * W * kBuckets);
+        if (!red) return ZKB_ERR_CUDA;
+        ZKB_LAUNCH(msm_seg_reduce_kernel, (unsigned)(m * W * 4), 128, 0, s, buckets, sh, red);
+        src = red;
+        one.nseg = 1;   // `red` is laid out like the bucket array of a single segment
+    }
+    ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 64), 64, 0, s, src, one, Lg, Gg);
+    ZKB_LAUNCH(msm_window_kernel, grid_for(m * W, 64), 64, 0, s, Lg, Gg, m * W, win);
+    ZKB_LAUNCH(msm_horner_kernel, grid_for(m, 32), 32, 0, s, win, sh, d_out);
     return ZKB_OK;
+}
+
+// The same over Jacobian generators: normalised to affine once per call.
+template <bool FULL>
+static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t m, int W,
+                    G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    if (m == 0) return ZKB_OK;
+    G1Aff* bases = scratch.get_n<G1Aff>(n);
+    if (!bases) return ZKB_ERR_CUDA;
+    ZKB_TRY(to_affine_device(d_gens, bases, n, s));
+    return msm_rows_affine<FULL>(bases, n, d_scalars, m, W, d_out, scratch, s);
 }
 
 // Smallest W such that |s| + K stays below 128^W for every |s| <= max_abs, where
@@ -365,6 +479,156 @@ static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d
     ZKB_CUDA(cudaMemcpyAsync(&h_max, d_max, 4, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return msm_rows<false>(d_gens, n_gen, d_scalars, m, windows_for_max(h_max), d_out, scratch, s);
+}
+
+// ---- opening rounds (Commitment::me_open / me_open_step, commitment.cu:79-125) ----
+// Round with scalars s and generators g, both of length `old`, pairs (2j, 2j+1):
+//   T  = sum_i s_i g_i     T0 = sum_j s_2j g_2j+1     T1 = sum_j s_2j+1 g_2j
+//   s'_j = s_2j + u (s_2j+1 - s_2j)          g'_j = g_2j+1 + u (g_2j - g_2j+1)
+// The reference forms five scalar products per pair and tree-sums three arrays.
+// Here T, T0, T1 are one three-row MSM over the round's generators (rows 1 and 2
+// are the pair-swapped scalars with every other entry zero), which leaves one
+// scalar product per pair, for g'.  Scalars are used by their raw limbs, as the
+// reference's G1Jacobian_mul reads them.  A lone last element pairs with nothing.
+__global__ void me_open_rows_kernel(const Fr* __restrict__ sc, size_t old_size, size_t new_size, Fr u_mont,
+                                    Fr* __restrict__ rows, Fr* __restrict__ nsc) {
+    const Fr zero = fr_zero();
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
+        const size_t i0 = 2 * g, i1 = 2 * g + 1;
+        const Fr s0 = fr_load(sc + i0);
+        fr_store(rows + i0, s0);
+        fr_store(rows + old_size + i0, zero);
+        if (i1 >= old_size) {
+            fr_store(rows + 2 * old_size + i0, zero);
+            fr_store(nsc + g, fr_sub(s0, fr_mmul(u_mont, s0)));
+            continue;
+        }
+        const Fr s1 = fr_load(sc + i1);
+        fr_store(rows + i1, s1);
+        fr_store(rows + old_size + i1, s0);        // T0: s_2j on g_2j+1
+        fr_store(rows + 2 * old_size + i0, s1);    // T1: s_2j+1 on g_2j
+        fr_store(rows + 2 * old_size + i1, zero);
+        fr_store(nsc + g, fr_add(s0, fr_mmul(u_mont, fr_sub(s1, s0))));
+    }
+}
+
+ZKB_DEV G1Jac g1_from_aff(const G1Aff& a) {
+    G1Jac r;
+    r.x = a.x; r.y = a.y;
+    r.z = g1_aff_is_identity(a) ? fe_zero<FqParams>() : fe_mont_one<FqParams>();
+    return r;
+}
+
+__global__ void __launch_bounds__(128) me_open_fold_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size, Fr u_std,
+                                                            G1Jac* __restrict__ ngen) {
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
+        const G1Aff a0 = g1_aff_load(bases + 2 * g);
+        if (2 * g + 1 >= old_size) {
+            g1_store(ngen + g, g1_mul_bits(g1_from_aff(a0), u_std));
+            continue;
+        }
+        const G1Aff a1 = g1_aff_load(bases + 2 * g + 1);
+        const G1Jac diff = g1_add_mixed(g1_from_aff(a0), g1_aff_neg(a1));
+        g1_store(ngen + g, g1_add_mixed(g1_mul_bits(diff, u_std), a1));
+    }
+}
+
+// ---- the last rounds of an opening, all at once --------------------------------
+// Once a round has at most kTailLen generators g (affine, in the order-r group),
+// every later generator is a known combination of them: with
+//   g'[j] = u g[2j] + (1-u) g[2j+1]
+// the generators t rounds on are g_t[j] = sum_b W_t(b) g[j 2^t + b], where
+//   W_0 = [1],  W_t+1(b) = u_t W_t(b) for b < 2^t,  (1-u_t) W_t(b - 2^t) above.
+// So T, T0, T1 of all remaining rounds, and the final generator, are rows of one
+// MSM over g: no generator is folded any more and the chain of short, latency-bound
+// rounds becomes a single call.
+static constexpr size_t kTailLen = 4096;
+
+// One block.  S[t*c + j]: scalars after t folds (t = 0..K);  Wt[t*c + b]: W_t(b) in
+// Montgomery form for b < min(2^t, c).
+__global__ void __launch_bounds__(1024) me_open_tail_prep_kernel(const Fr* __restrict__ s0, size_t c, const Fr* __restrict__ u_mont,
+                                                                  unsigned K, Fr* __restrict__ S, Fr* __restrict__ Wt) {
+    const Fr one = fe_mont_one<FrP>();
+    for (size_t i = threadIdx.x; i < c; i += blockDim.x) fr_store(S + i, fr_load(s0 + i));
+    if (threadIdx.x == 0) fr_store(Wt, one);
+    __syncthreads();
+    size_t len = c, wl = 1;
+    for (unsigned t = 0; t < K; ++t) {
+        const Fr u = fr_load(u_mont + t);
+        const Fr v = fr_sub(one, u);
+        const size_t nl = (len + 1) / 2;
+        const size_t nw = 2 * wl < c ? 2 * wl : c;
+        const Fr* St = S + (size_t)t * c;
+        const Fr* Wc = Wt + (size_t)t * c;
+        for (size_t j = threadIdx.x; j < nl; j += blockDim.x) {
+            const Fr a = fr_load(St + 2 * j);
+            const Fr b = 2 * j + 1 < len ? fr_load(St + 2 * j + 1) : fr_zero();
+            fr_store(S + (size_t)(t + 1) * c + j, fr_add(a, fr_mmul(u, fr_sub(b, a))));
+        }
+        for (size_t b = threadIdx.x; b < nw; b += blockDim.x)
+            fr_store(Wt + (size_t)(t + 1) * c + b, b < wl ? fr_mmul(u, fr_load(Wc + b)) : fr_mmul(v, fr_load(Wc + b - wl)));
+        __syncthreads();
+        len = nl;
+        wl = nw;
+    }
+}
+
+// rows[q*c + i], q = 3t + {0: T, 1: T0, 2: T1} of tail round t, q = 3K: the final
+// generator.  A scalar's raw limbs times W, as plain integer limbs.
+__global__ void me_open_tail_rows_kernel(const Fr* __restrict__ S, const Fr* __restrict__ Wt, size_t c, unsigned K,
+                                         Fr* __restrict__ rows) {
+    const size_t total = (3 * (size_t)K + 1) * c;
+    for (size_t x = blockIdx.x * (size_t)blockDim.x + threadIdx.x; x < total; x += (size_t)gridDim.x * blockDim.x) {
+        const size_t q = x / c, i = x % c;
+        const unsigned t = (unsigned)(q / 3), kind = (unsigned)(q % 3);
+        if (q == 3 * (size_t)K) {
+            Fr one_std = fr_zero();
+            one_std.v[0] = 1;
+            // g_K[0] takes the first 2^K generators only
+            const bool inside = K >= 63 || i < ((size_t)1 << K);
+            fr_store(rows + x, inside ? fr_mmul(fr_load(Wt + (size_t)K * c + i), one_std) : fr_zero());
+            continue;
+        }
+        const size_t j = t < 63 ? i >> t : 0;
+        const size_t b = t < 63 ? i & (((size_t)1 << t) - 1) : i;
+        const size_t len = t < 63 ? (c + (((size_t)1 << t) - 1)) >> t : 1;
+        const Fr* St = S + (size_t)t * c;
+        Fr sc = fr_zero();
+        bool live = true;
+        if (kind == 0) sc = fr_load(St + j);
+        else if (kind == 1) { if (j & 1) sc = fr_load(St + j - 1); else live = false; }
+        else { if (!(j & 1) && j + 1 < len) sc = fr_load(St + j + 1); else live = false; }
+        fr_store(rows + x, live ? fr_mmul(sc, fr_load(Wt + (size_t)t * c + b)) : fr_zero());
+    }
+}
+
+// A second stream per device for work that may run beside the caller's stream,
+// with the two events that fork from and join back into it.  Created on first use.
+// `busy` is held for the length of a call that uses the stream, so two host threads
+// on one device take turns.  Drain waits for the stream when a call leaves early.
+struct SideStream { cudaStream_t st; cudaEvent_t fork, join; std::mutex busy; };
+struct Drain {
+    cudaStream_t st;
+    ~Drain() { cudaStreamSynchronize(st); }
+};
+static SideStream* side_stream() {
+    static SideStream table[64];
+    static bool made[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { fail(ZKB_ERR_CUDA, "side stream: no current device"); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!made[dev]) {
+        SideStream& t = table[dev];
+        if (cudaStreamCreateWithFlags(&t.st, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) {
+            fail(ZKB_ERR_CUDA, "side stream: cannot create stream or events");
+            return nullptr;
+        }
+        made[dev] = true;
+    }
+    return &table[dev];
 }
 
 }  // namespace zkb
@@ -421,6 +685,85 @@ int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, 
     Scratch scratch(s);
     return msm_rows<true>(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars / n_gen, kMaxWindows,
                           reinterpret_cast<G1Jac*>(d_out), scratch, s);
+}
+
+int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
+                zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
+    SideStream* side = side_stream();
+    if (!side) return ZKB_ERR_CUDA;
+    std::lock_guard<std::mutex> turn(side->busy);
+    Scratch keep(s);
+    Drain drain{side->st};   // destroyed before `keep`: nothing of the side stream outlives the buffers
+    // The chain that cannot be shortened is generators -> affine -> folded
+    // generators, round after round, on the caller's stream.  The three-row MSM of
+    // a round only reads that round's affine generators and scalar rows, so it runs
+    // on a second stream beside the later rounds; every round has its own slice
+    // of `rows` and `bases` (the lengths halve, 2n + k entries cover them all).
+    const size_t h0 = (n + 1) / 2, total = 2 * n + k + 2;
+    Fr* sc[2] = {keep.get_n<Fr>(h0), keep.get_n<Fr>(h0)};
+    G1Jac* gn[2] = {keep.get_n<G1Jac>(h0), keep.get_n<G1Jac>(h0)};
+    Fr* rows = keep.get_n<Fr>(3 * total);
+    G1Aff* bases = keep.get_n<G1Aff>(total);
+    G1Jac* d_proof = keep.get_n<G1Jac>(3 * (size_t)k + 1);
+    if (!sc[0] || !sc[1] || !gn[0] || !gn[1] || !rows || !bases || !d_proof) return ZKB_ERR_CUDA;
+    const Fr* cs = reinterpret_cast<const Fr*>(d_t);
+    const G1Jac* cg = reinterpret_cast<const G1Jac*>(d_gens);
+    size_t cur = n, used = 0;
+    auto host_fr = [](const zkb_fr_t& h) { Fr r; memcpy(&r, &h, sizeof(Fr)); return r; };
+    int rc = ZKB_OK;
+    unsigned r = 0;
+    for (; r < k && cur > kTailLen && rc == ZKB_OK; ++r) {
+        const size_t nn = (cur + 1) / 2;
+        const Fr u_std = host_fr(h_u[r]);
+        const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
+        Fr* rows_r = rows + 3 * used;
+        G1Aff* bases_r = bases + used;
+        ZKB_LAUNCH(me_open_rows_kernel, grid_for(nn, 128), 128, 0, s, cs, cur, nn, u_mont, rows_r, sc[r & 1]);
+        ZKB_TRY(to_affine_device(cg, bases_r, cur, s));
+        ZKB_CUDA(cudaEventRecord(side->fork, s));
+        ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
+        {
+            Scratch round(side->st);   // MSM work buffers of this round, released in the side stream's order
+            rc = msm_rows_affine<true>(bases_r, cur, rows_r, 3, kMaxWindows, d_proof + 3 * r, round, side->st);
+        }
+        ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, u_std, gn[r & 1]);
+        cs = sc[r & 1];
+        cg = gn[r & 1];
+        used += cur;
+        cur = nn;
+    }
+    // the remaining K rounds and the final generator as one MSM over this round's generators
+    const unsigned K = k - r;
+    if (rc == ZKB_OK && K > 0) {
+        std::vector<zkb_fr_t> um(K);
+        for (unsigned t = 0; t < K; ++t) um[t] = hfr::store(hfr::to_mont(hfr::load(h_u[r + t])));
+        Fr* d_um = keep.get_n<Fr>(K);
+        Fr* S = keep.get_n<Fr>(((size_t)K + 1) * cur);
+        Fr* Wt = keep.get_n<Fr>(((size_t)K + 1) * cur);
+        Fr* tail_rows = keep.get_n<Fr>((3 * (size_t)K + 1) * cur);
+        G1Aff* bases_t = bases + used;
+        if (!d_um || !S || !Wt || !tail_rows) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemcpyAsync(d_um, um.data(), K * sizeof(Fr), cudaMemcpyHostToDevice, s));
+        ZKB_LAUNCH(me_open_tail_prep_kernel, 1, 1024, 0, s, cs, cur, d_um, K, S, Wt);
+        ZKB_LAUNCH(me_open_tail_rows_kernel, grid_for((3 * (size_t)K + 1) * cur, 128), 128, 0, s, S, Wt, cur, K, tail_rows);
+        ZKB_TRY(to_affine_device(cg, bases_t, cur, s));
+        rc = msm_rows_affine<true>(bases_t, cur, tail_rows, 3 * (size_t)K + 1, kMaxWindows, d_proof + 3 * r, keep, s);
+        cs = S + (size_t)K * cur;   // the fully folded scalar
+    }
+    // the caller's stream takes the side stream's work back before anything is read or released
+    ZKB_CUDA(cudaEventRecord(side->join, side->st));
+    ZKB_CUDA(cudaStreamWaitEvent(s, side->join, 0));
+    if (rc != ZKB_OK) {
+        cudaStreamSynchronize(s);
+        return rc;
+    }
+    if (K == 0) ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k, cg, sizeof(G1Jac), cudaMemcpyDeviceToDevice, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_proof, d_proof, (3 * (size_t)k + 1) * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, cs, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
 }
 
 }  // extern "C"

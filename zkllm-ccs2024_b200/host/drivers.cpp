@@ -9,13 +9,26 @@
 //   zkllm-driver self-attn <linear|attn> <in.bin> <seq> <embed> <workdir> <layer-prefix> <out.bin>
 //   zkllm-driver ffn <in.bin> <seq> <embed> <hidden> <workdir> <layer-prefix> <out.bin>
 //   zkllm-driver skip-connection <x.bin> <y.bin> <out.bin>
+//   zkllm-driver batch <script|->      (no counterpart in the reference)
 //
+// `batch` reads one stage command per line ("ffn in.bin 2048 4096 ..."; blank
+// lines and lines starting with # are skipped) and runs them in this one
+// process, so a whole layer pays for one CUDA context and one module load
+// instead of one per stage.  After each line it prints "[batch] <stage> <s> s"
+// to stderr; with ZKLLM_PROFILE=1 it also prints the library's per-kernel times.
+// The first failing stage ends the batch with its exception.
 // Each stage computes its fixed-point outputs in the field, proves them and
 // throws if a verifier equation fails, printing the reference's progress lines.
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <functional>
 #include <map>
+#include <sstream>
 #include <string>
+
+#include "../../include/zkllm_b200.h"
 
 #include "commitment.cuh"
 #include "fr-tensor.cuh"
@@ -27,6 +40,18 @@
 namespace {
 
 typedef std::vector<std::string> Args;
+
+// With ZKLLM_PROFILE=1: wall seconds since the previous mark, to stderr.
+struct StepClock {
+    std::chrono::steady_clock::time_point last = std::chrono::steady_clock::now();
+    bool on = std::getenv("ZKLLM_PROFILE") && std::getenv("ZKLLM_PROFILE")[0] == '1';
+    void mark(const char* what) {
+        if (!on) return;
+        const auto now = std::chrono::steady_clock::now();
+        cerr << "[step] " << what << " " << std::chrono::duration<double>(now - last).count() << " s" << endl;
+        last = now;
+    }
+};
 
 // generator, int weights and commitment of one parameter of one layer
 Weight load_param(const std::string& workdir, const std::string& prefix, const std::string& name, uint in_dim, uint out_dim) {
@@ -148,6 +173,7 @@ int run_self_attn(const Args& a) {
 }
 
 int run_ffn(const Args& a) {
+    StepClock clk;
     const uint seq = std::stoi(a.at(1)), embed = std::stoi(a.at(2)), hidden = std::stoi(a.at(3));
     const std::string workdir = a.at(4), prefix = a.at(5);
     Linear up(load_param(workdir, prefix, "mlp.up_proj.weight", embed, hidden), embed, hidden, 1 << 16);
@@ -156,6 +182,7 @@ int run_ffn(const Args& a) {
     Rescaling hidden_rescale(1 << 16);
     FrTensor swiglu_values = FrTensor::from_int_bin("swiglu-table.bin");   // written by the Python side
     tLookupRangeMapping swiglu(-(1 << 21), 1 << 22, swiglu_values);
+    clk.mark("load parameters");
 
     FrTensor input = FrTensor::from_int_bin(a.at(0));
     auto up_out = up.fc(input);
@@ -171,17 +198,28 @@ int run_ffn(const Args& a) {
     auto down_in_ = hidden_rescale(down_in);
     auto down_out = down.fc(down_in_);
     auto down_out_ = down.rs(down_out);
+    clk.mark("forward");
     down_out.save_int(a.at(6));   // the reference saves the value before the last rescaling
+    clk.mark("save");
 
     down.rs.prove(down_out, down_out_);
-    verifyWeightClaim(down.w, down.fc.prove(down_in_, down_out)[0]);
+    clk.mark("down rescale prove");
+    auto down_claim = down.fc.prove(down_in_, down_out)[0];
+    clk.mark("down fc prove");
+    verifyWeightClaim(down.w, down_claim);
+    clk.mark("down opening");
     hidden_rescale.prove(down_in, down_in_);
+    clk.mark("hidden rescale prove");
     swiglu.prove(gate_out_, act.first, act.second, temp_rand[0], temp_rand[1], temp_rand[2], swiglu_u, swiglu_v, swiglu_proof);
     cout << "SwiGLU proof complete." << endl;
+    clk.mark("swiglu prove");
     gate.rs.prove(gate_out, gate_out_);
+    clk.mark("gate rescale prove");
     verifyWeightClaim(gate.w, gate.fc.prove(input, gate_out)[0]);
+    clk.mark("gate fc prove + opening");
     up.rs.prove(up_out, up_out_);
     verifyWeightClaim(up.w, up.fc.prove(input, up_out)[0]);
+    clk.mark("up rescale + fc prove + opening");
     return 0;
 }
 
@@ -192,12 +230,54 @@ int run_skip(const Args& a) {
     return 0;
 }
 
+typedef std::map<std::string, std::pair<std::function<int(const Args&)>, size_t>> StageTable;
+
+const StageTable& stage_table() {
+    static const StageTable stages = {
+        {"ppgen", {run_ppgen, 2}},         {"commit-param", {run_commit_param, 5}}, {"rmsnorm", {run_rmsnorm, 7}},
+        {"self-attn", {run_self_attn, 7}}, {"ffn", {run_ffn, 7}},                   {"skip-connection", {run_skip, 3}}};
+    return stages;
+}
+
+int run_batch(const Args& a) {
+    std::ifstream file;
+    if (a.at(0) != "-") {
+        file.open(a.at(0));
+        if (!file) throw std::runtime_error("batch: cannot open " + a.at(0));
+    }
+    std::istream& in = a.at(0) == "-" ? std::cin : file;
+    const char* prof_env = std::getenv("ZKLLM_PROFILE");
+    const bool profile = prof_env && prof_env[0] == '1';
+    if (profile) zkb_profile_enable(1);
+    std::string line;
+    while (std::getline(in, line)) {
+        std::istringstream words(line);
+        Args cmd;
+        for (std::string w; words >> w;) cmd.push_back(w);
+        if (cmd.empty() || cmd[0][0] == '#') continue;
+        const std::string stage = cmd[0];
+        if (!stage_table().count(stage)) throw std::runtime_error("batch: unknown stage " + stage);
+        cmd.erase(cmd.begin());
+        if (cmd.size() < stage_table().at(stage).second) throw std::runtime_error("batch: too few arguments for " + stage);
+        if (profile) zkb_profile_reset();
+        const auto t0 = std::chrono::steady_clock::now();
+        const int rc = stage_table().at(stage).first(cmd);
+        const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        cerr << "[batch] " << stage << (stage == "self-attn" || stage == "rmsnorm" ? " " + cmd[0] : "") << " " << secs << " s" << endl;
+        if (profile) {
+            std::vector<char> buf(1 << 16);
+            if (zkb_profile_read(buf.data(), buf.size()) == 0) cerr << buf.data();
+        }
+        if (rc) return rc;
+    }
+    return 0;
+}
+
 }  // namespace
 
 int main(int argc, char* argv[]) {
-    const std::map<std::string, std::pair<std::function<int(const Args&)>, size_t>> stages = {
-        {"ppgen", {run_ppgen, 2}},         {"commit-param", {run_commit_param, 5}}, {"rmsnorm", {run_rmsnorm, 7}},
-        {"self-attn", {run_self_attn, 7}}, {"ffn", {run_ffn, 7}},                   {"skip-connection", {run_skip, 3}}};
+    StageTable stages = stage_table();
+    stages["batch"] = {run_batch, 1};
     std::string self = argv[0];
     const size_t slash = self.find_last_of('/');
     if (slash != std::string::npos) self = self.substr(slash + 1);
@@ -205,7 +285,7 @@ int main(int argc, char* argv[]) {
     std::string stage = self;
     if (!stages.count(stage)) {
         if (argc < 2 || !stages.count(argv[1])) {
-            cerr << "usage: " << self << " <ppgen|commit-param|rmsnorm|self-attn|ffn|skip-connection> <stage arguments>" << endl;
+            cerr << "usage: " << self << " <ppgen|commit-param|rmsnorm|self-attn|ffn|skip-connection|batch> <stage arguments>" << endl;
             return 2;
         }
         stage = argv[1];
