@@ -577,7 +577,8 @@ def run_layer(args) -> dict:
         import hashlib
         digest = hashlib.sha256((w / "x4.bin").read_bytes() + (w / "temp_head_out.bin").read_bytes()).hexdigest()
     prove = sum(v for k, v in stages.items() if not k.startswith(("ppgen", "commit-param")))
-    return {"metric": "Llama-2-7B-shape layer prove time", "unit": "s", "value": prove, "higher_is_better": False,
+    shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((embed, hidden), "decoder")
+    return {"metric": f"{shape} layer prove time", "unit": "s", "value": prove, "higher_is_better": False,
             "impl": args.impl, "workload": f"layer seq {seq} hidden {embed} ffn {hidden}", "stages_s": stages,
             "mode": "one resident driver process" if batch else "one process per stage",
             "passes_s": [sum(p.values()) for p in passes],

@@ -55,7 +55,8 @@ unsigned long long zkb_launch_count(void);
 /* Per-kernel timing for benchmarks (no counterpart in the reference).  While
  * enabled, every kernel launch of the library is bracketed by CUDA events on its
  * stream.  zkb_profile_read synchronises the device and writes one line per
- * kernel, "name,launches,total_ms\n", into buf. */
+ * kernel, "name,launches,total_ms\n", into buf, followed by "host:<call>,calls,total_ms"
+ * lines for the host time spent in the device-memory allocator. */
 int zkb_profile_enable(int on);
 int zkb_profile_reset(void);
 int zkb_profile_read(char* buf, size_t cap);

@@ -156,10 +156,13 @@ def _fr_of_ints(a):
 
 
 @pytest.mark.parametrize("M,N,P,amax,bmax", [(128, 256, 128, 1 << 20, 3000), (100, 300, 150, (1 << 31) - 1, (1 << 31) - 1),
-                                             (257, 129, 131, 70000, 70000), (64, 1024, 64, 1 << 31, 1 << 31)])
+                                             (257, 129, 131, 70000, 70000), (64, 1024, 64, 1 << 31, 1 << 31),
+                                             (128, 256, 128, 1 << 40, 3000), (100, 2048, 96, 1 << 60, 1 << 10),
+                                             (64, 1024, 64, 1 << 60, 1 << 25), (70, 1000, 66, (1 << 62) + 5, 100)])
 def test_matmul_integer_path_and_its_fallbacks(dev, M, N, P, amax, bmax):
-    """large products of int32-encodings take the exact int64 kernel; products whose sum could pass 2^62 and
-    operands that are not small integers take the field kernel; all agree with exact integer arithmetic"""
+    """large products of int32-encodings take the exact int64 kernel; a left operand beyond int32 (up to 2^61) is split
+    into two 31-bit halves; products whose sums could pass 2^62 and operands that are not small integers take the field
+    kernel; all agree with exact integer arithmetic"""
     z = dev.z
     rng = np.random.Generator(np.random.PCG64(M * N + P))
     A = rng.integers(-amax, amax, size=(M, N), dtype=np.int64)

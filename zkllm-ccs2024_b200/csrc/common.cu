@@ -3,6 +3,7 @@
 
 #include <atomic>
 #include <cstring>
+#include <chrono>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -72,6 +73,22 @@ static void ensure_pool_keeps_memory() {
     done[dev] = true;
 }
 
+// Host time spent inside the allocator calls, reported by zkb_profile_read as
+// "host:<what>" lines next to the kernels (only while profiling is enabled).
+static std::atomic<unsigned long long> g_alloc_ns[3], g_alloc_calls[3];
+static const char* const kAllocNames[3] = {"host:scratch_alloc", "host:zkb_malloc", "host:zkb_free"};
+struct AllocClock {
+    int which;
+    std::chrono::steady_clock::time_point t0;
+    explicit AllocClock(int w) : which(w) { if (g_profile_on) t0 = std::chrono::steady_clock::now(); }
+    ~AllocClock() {
+        if (!g_profile_on) return;
+        g_alloc_ns[which] += (unsigned long long)std::chrono::duration_cast<std::chrono::nanoseconds>(
+                                 std::chrono::steady_clock::now() - t0).count();
+        g_alloc_calls[which] += 1;
+    }
+};
+
 Scratch::~Scratch() {
     for (int i = 0; i < n_; ++i) cudaFreeAsync(blocks_[i], stream_);
 }
@@ -83,6 +100,7 @@ void* Scratch::get(size_t bytes) {
     }
     if (bytes == 0) bytes = 16;
     ensure_pool_keeps_memory();
+    AllocClock clock(0);
     void* p = nullptr;
     cudaError_t e = cudaMallocAsync(&p, bytes, stream_);
     if (e != cudaSuccess) {
@@ -111,6 +129,7 @@ int zkb_profile_reset(void) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
     for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
     g_prof.clear();
+    for (int i = 0; i < 3; ++i) { g_alloc_ns[i] = 0; g_alloc_calls[i] = 0; }
     return ZKB_OK;
 }
 int zkb_profile_read(char* buf, size_t cap) {
@@ -132,6 +151,12 @@ int zkb_profile_read(char* buf, size_t cap) {
         snprintf(line, sizeof(line), "%s,%llu,%.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
         out += line;
     }
+    for (int i = 0; i < 3; ++i) {
+        if (!g_alloc_calls[i]) continue;
+        char line[256];
+        snprintf(line, sizeof(line), "%s,%llu,%.6f\n", kAllocNames[i], (unsigned long long)g_alloc_calls[i], g_alloc_ns[i] * 1e-6);
+        out += line;
+    }
     if (out.size() + 1 > cap) return fail(ZKB_ERR_LIMIT, "zkb_profile_read: buffer too small");
     memcpy(buf, out.c_str(), out.size() + 1);
     return ZKB_OK;
@@ -144,12 +169,14 @@ int zkb_profile_read(char* buf, size_t cap) {
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");
     ensure_pool_keeps_memory();
+    AllocClock clock(1);
     ZKB_CUDA(cudaMallocAsync(d_ptr, bytes ? bytes : 16, (cudaStream_t)0));
     ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     return ZKB_OK;
 }
 int zkb_free(void* d_ptr) {
     if (!d_ptr) return ZKB_OK;
+    AllocClock clock(2);
     ZKB_CUDA(cudaDeviceSynchronize());
     ZKB_CUDA(cudaFreeAsync(d_ptr, (cudaStream_t)0));
     return ZKB_OK;

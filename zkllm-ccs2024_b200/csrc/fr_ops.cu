@@ -524,18 +524,70 @@ __global__ void fr_to_small_kernel(const Fr* __restrict__ a, size_t n, int32_t* 
     if (mx) atomicMax(flags + 1, mx);
 }
 
+// Wider left operand (softmax output times V: entries beyond int32, rows that
+// sum to about the output scale).  One CTA per row: every entry with |v| < 2^61
+// is split as v = hi * 2^31 + lo with lo in [-2^30, 2^30); wflags[0] = 1 if some
+// entry is out of range, wl1 = the largest row sum of |hi|.
+__global__ void __launch_bounds__(256) fr_to_wide_kernel(const Fr* __restrict__ a, size_t cols, int32_t* __restrict__ lo,
+                                                          int32_t* __restrict__ hi, unsigned* __restrict__ wflags,
+                                                          unsigned long long* __restrict__ wl1) {
+    __shared__ unsigned long long red[256];
+    const size_t row = blockIdx.x;
+    unsigned long long l1 = 0;
+    unsigned bad = 0;
+    for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const Fr x = fr_load(a + row * cols + c);
+        long long v = 0;
+        const Fr m = fr_neg(x);
+        if (fr_fits_u64(x) && !(x.v[1] >> 29)) v = (long long)(((unsigned long long)x.v[1] << 32) | x.v[0]);
+        else if (fr_fits_u64(m) && !(m.v[1] >> 29)) v = -(long long)(((unsigned long long)m.v[1] << 32) | m.v[0]);
+        else bad = 1;
+        const long long l = ((v + (1ll << 30)) & ((1ll << 31) - 1)) - (1ll << 30);
+        const long long h = (v - l) >> 31;   // exact: v - l is a multiple of 2^31
+        lo[row * cols + c] = (int32_t)l;
+        hi[row * cols + c] = (int32_t)h;
+        l1 += (unsigned long long)(h < 0 ? -h : h);
+    }
+    red[threadIdx.x] = l1;
+    __syncthreads();
+    for (unsigned st = 128; st > 0; st >>= 1) {
+        if (threadIdx.x < st) red[threadIdx.x] += red[threadIdx.x + st];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) atomicMax(wl1, red[0]);
+    if (bad) atomicOr(wflags, 1u);
+}
+
+// acc_hi * 2^31 + acc_lo as a field element (|acc_hi|, |acc_lo| < 2^62)
+ZKB_DEV Fr fr_from_split(long long acc_lo, long long acc_hi) {
+    const unsigned long long mag = acc_hi < 0 ? 0ull - (unsigned long long)acc_hi : (unsigned long long)acc_hi;
+    Fr r = fr_zero();
+    // mag << 31 over three limbs
+    r.v[0] = (uint32_t)(mag << 31);
+    r.v[1] = (uint32_t)(mag >> 1);
+    r.v[2] = (uint32_t)(mag >> 33);
+    if (acc_hi < 0) r = fr_neg(r);
+    return fr_add(r, fr_from_i64(acc_lo));
+}
+
 static constexpr int kImTile = 64, kImK = 16;
-__global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restrict__ A, const int32_t* __restrict__ B,
-                                                          Fr* __restrict__ C, size_t M, size_t N, size_t P) {
+template <bool WIDE>
+__global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restrict__ A, const int32_t* __restrict__ Ahi,
+                                                          const int32_t* __restrict__ B, Fr* __restrict__ C, size_t M, size_t N,
+                                                          size_t P) {
     __shared__ int32_t As[kImK][kImTile + 1];   // [k][row]
+    __shared__ int32_t Ah[WIDE ? kImK : 1][kImTile + 1];
     __shared__ int32_t Bs[kImK][kImTile];       // [k][col]
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const size_t row0 = (size_t)blockIdx.y * kImTile, col0 = (size_t)blockIdx.x * kImTile;
-    long long acc[4][4];
+    long long acc[4][4], acch[WIDE ? 4 : 1][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0;
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0;
+            if constexpr (WIDE) acch[i][j] = 0;
+        }
     for (size_t k0 = 0; k0 < N; k0 += kImK) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -543,6 +595,7 @@ __global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restri
             const int ar = l >> 4, ak = l & 15;           // A tile: 64 rows x 16 k, k fastest (coalesced along k)
             const size_t gr = row0 + ar, gk = k0 + ak;
             As[ak][ar] = (gr < M && gk < N) ? A[gr * N + gk] : 0;
+            if constexpr (WIDE) Ah[ak][ar] = (gr < M && gk < N) ? Ahi[gr * N + gk] : 0;
             const int bk = l >> 6, bc = l & 63;           // B tile: 16 k x 64 cols
             const size_t gk2 = k0 + bk, gc = col0 + bc;
             Bs[bk][bc] = (gk2 < N && gc < P) ? B[gk2 * P + gc] : 0;
@@ -550,13 +603,20 @@ __global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restri
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < kImK; ++kk) {
-            int a[4], b[4];
+            int a[4], ah[4], b[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty + 16 * i]; b[i] = Bs[kk][tx + 16 * i]; }
+            for (int i = 0; i < 4; ++i) {
+                a[i] = As[kk][ty + 16 * i];
+                if constexpr (WIDE) ah[i] = Ah[kk][ty + 16 * i]; else ah[i] = 0;
+                b[i] = Bs[kk][tx + 16 * i];
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] += (long long)a[i] * (long long)b[j];
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] += (long long)a[i] * (long long)b[j];
+                    if constexpr (WIDE) acch[i][j] += (long long)ah[i] * (long long)b[j];
+                }
         }
         __syncthreads();
     }
@@ -565,7 +625,10 @@ __global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restri
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const size_t r = row0 + ty + 16 * i, c = col0 + tx + 16 * j;
-            if (r < M && c < P) fr_store(C + r * P + c, fr_from_i64(acc[i][j]));
+            if (r < M && c < P) {
+                if constexpr (WIDE) fr_store(C + r * P + c, fr_from_split(acc[i][j], acch[i][j]));
+                else fr_store(C + r * P + c, fr_from_i64(acc[i][j]));
+            }
         }
 }
 
@@ -794,11 +857,29 @@ int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_
         ZKB_CUDA(cudaStreamSynchronize(s));
         // |sum| <= N * maxA * maxB must stay below 2^62
         const unsigned __int128 bound = (unsigned __int128)h[1] * h[3] * N;
-        if (!h[0] && !h[2] && bound < ((unsigned __int128)1 << 62)) {
-            dim3 gi(div_up(P, kImTile), div_up(M, kImTile));
-            if (gi.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^22 rows");
-            ZKB_LAUNCH(i32_matmul_kernel, gi, 256, 0, s, ia, ib, FR(d_c), M, N, P);
+        const unsigned __int128 limit = (unsigned __int128)1 << 62;
+        dim3 gi(div_up(P, kImTile), div_up(M, kImTile));
+        if (gi.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^22 rows");
+        if (!h[0] && !h[2] && bound < limit) {
+            ZKB_LAUNCH(i32_matmul_kernel<false>, gi, 256, 0, s, ia, nullptr, ib, FR(d_c), M, N, P);
             return ZKB_OK;
+        }
+        if (!h[2] && M <= 0x7fffffffull) {
+            // left operand beyond int32: two 31-bit halves, the high half bounded by its row sums
+            int32_t* ih = scratch.get_n<int32_t>(M * N);
+            unsigned long long* wl1 = scratch.get_n<unsigned long long>(2);
+            if (!ih || !wl1) return ZKB_ERR_CUDA;
+            ZKB_CUDA(cudaMemsetAsync(wl1, 0, 16, s));
+            ZKB_LAUNCH(fr_to_wide_kernel, (unsigned)M, 256, 0, s, CFR(d_a), N, ia, ih, reinterpret_cast<unsigned*>(wl1 + 1), wl1);
+            unsigned long long hw[2];
+            ZKB_CUDA(cudaMemcpyAsync(hw, wl1, 16, cudaMemcpyDeviceToHost, s));
+            ZKB_CUDA(cudaStreamSynchronize(s));
+            const unsigned __int128 lo_bound = ((unsigned __int128)N << 30) * h[3];
+            const unsigned __int128 hi_bound = (unsigned __int128)hw[0] * h[3];
+            if (!(hw[1] & 1u) && lo_bound < limit && hi_bound < limit) {
+                ZKB_LAUNCH(i32_matmul_kernel<true>, gi, 256, 0, s, ia, ih, ib, FR(d_c), M, N, P);
+                return ZKB_OK;
+            }
         }
     }
     dim3 grid(div_up(P, kMmTile), div_up(M, kMmTile));

@@ -519,18 +519,111 @@ ZKB_DEV G1Jac g1_from_aff(const G1Aff& a) {
     return r;
 }
 
-__global__ void __launch_bounds__(128) me_open_fold_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size, Fr u_std,
-                                                            G1Jac* __restrict__ ngen) {
+// u * P for the one scalar u all pairs of a round share, through the curve's
+// endomorphism phi(x, y) = (beta x, y) = lambda (x, y) on the order-r group:
+// u = k1 + k2 lambda with 128-bit halves (host: fold_digits), and
+// k1 P + k2 phi(P) by one pass of 33 signed 4-bit windows over both halves with
+// a table of 1P..8P.  128 doublings and 66 additions instead of 255 and ~128.
+struct FoldDigits { signed char d1[33], d2[33]; };
+
+ZKB_DEV Fq fq_beta_mont() {
+    constexpr uint32_t t[12] = {0x8671f071u, 0xcd03c9e4u, 0x1fcda5d2u, 0x5dab2246u, 0xd3851b95u, 0x587042afu,
+                                0x01bacb9eu, 0x8eb60ebeu, 0x83d050d2u, 0x03f97d6eu, 0x54638741u, 0x18f02065u};
+    Fq r;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) r.v[i] = t[i];
+    return r;
+}
+
+__device__ __noinline__ static G1Jac g1_add_call(const G1Jac& p, const G1Jac& q) { return g1_add(p, q); }
+__device__ __noinline__ static G1Jac g1_double_call(const G1Jac& p) { return g1_double(p); }
+
+__device__ static G1Jac g1_mul_shared_scalar(const G1Jac& p, const FoldDigits& dg) {
+    G1Jac tab[8];
+    tab[0] = p;
+#pragma unroll 1
+    for (int i = 1; i < 8; ++i) tab[i] = (i & 1) ? g1_double_call(tab[i >> 1]) : g1_add_call(tab[i - 1], p);
+    const Fq beta = fq_beta_mont();
+    G1Jac acc = g1_identity();
+#pragma unroll 1
+    for (int w = 32; w >= 0; --w) {
+        if (w != 32) {
+#pragma unroll 1
+            for (int d = 0; d < 4; ++d) acc = g1_double_call(acc);
+        }
+        const int a = dg.d1[w], b = dg.d2[w];
+        if (a) {
+            G1Jac t = tab[(a < 0 ? -a : a) - 1];
+            if (a < 0) t = g1_neg(t);
+            acc = g1_add_call(acc, t);
+        }
+        if (b) {
+            G1Jac t = tab[(b < 0 ? -b : b) - 1];
+            t.x = fq_mul(t.x, beta);
+            if (b < 0) t = g1_neg(t);
+            acc = g1_add_call(acc, t);
+        }
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(128) me_open_fold_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size,
+                                                            FoldDigits dg, G1Jac* __restrict__ ngen) {
     for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
         const G1Aff a0 = g1_aff_load(bases + 2 * g);
         if (2 * g + 1 >= old_size) {
-            g1_store(ngen + g, g1_mul_bits(g1_from_aff(a0), u_std));
+            g1_store(ngen + g, g1_mul_shared_scalar(g1_from_aff(a0), dg));
             continue;
         }
         const G1Aff a1 = g1_aff_load(bases + 2 * g + 1);
         const G1Jac diff = g1_add_mixed(g1_from_aff(a0), g1_aff_neg(a1));
-        g1_store(ngen + g, g1_add_mixed(g1_mul_bits(diff, u_std), a1));
+        g1_store(ngen + g, g1_add_mixed(g1_mul_shared_scalar(diff, dg), a1));
     }
+}
+
+// Host: u (standard form, below r) = k1 + k2 * lambda, then signed 4-bit digits of both halves.
+static FoldDigits fold_digits(const zkb_fr_t& u) {
+    typedef unsigned __int128 u128;
+    const u128 lambda = ((u128)0xac45a4010001a402ull << 64) | 0x00000000ffffffffull;
+    // schoolbook long division of the 256-bit u by lambda, one bit at a time
+    uint64_t limb[4];
+    for (int i = 0; i < 4; ++i) limb[i] = ((uint64_t)u.val[2 * i + 1] << 32) | u.val[2 * i];
+    // a raw value of r or more names the same multiple as its residue (2^256 < 3r)
+    const uint64_t rmod[4] = {0xffffffff00000001ull, 0x53bda402fffe5bfeull, 0x3339d80809a1d805ull, 0x73eda753299d7d48ull};
+    for (int pass = 0; pass < 2; ++pass) {
+        bool ge = true;
+        for (int i = 3; i >= 0; --i)
+            if (limb[i] != rmod[i]) { ge = limb[i] > rmod[i]; break; }
+        if (!ge) break;
+        uint64_t borrow = 0;
+        for (int i = 0; i < 4; ++i) {
+            const uint64_t d = limb[i] - rmod[i] - borrow;
+            borrow = (limb[i] < rmod[i] + borrow || (borrow && rmod[i] == ~0ull)) ? 1 : 0;
+            limb[i] = d;
+        }
+    }
+    u128 rem = 0, quo = 0;
+    for (int bit = 255; bit >= 0; --bit) {
+        const bool top = (bool)(rem >> 127);
+        rem = (rem << 1) | ((limb[bit >> 6] >> (bit & 63)) & 1u);
+        quo <<= 1;                         // the quotient of a value below r fits 128 bits
+        if (top || rem >= lambda) { rem -= lambda; quo |= 1; }
+    }
+    FoldDigits out;
+    u128 k[2] = {rem, quo};
+    for (int h = 0; h < 2; ++h) {
+        signed char* d = h ? out.d2 : out.d1;
+        u128 v = k[h];
+        int carry = 0;
+        for (int w = 0; w < 33; ++w) {
+            int x = (int)(v & 15u) + carry;
+            v >>= 4;
+            carry = 0;
+            if (x >= 8) { x -= 16; carry = 1; }
+            d[w] = (signed char)x;
+        }
+    }
+    return out;
 }
 
 // ---- the last rounds of an opening, all at once --------------------------------
@@ -716,7 +809,6 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     unsigned r = 0;
     for (; r < k && cur > kTailLen && rc == ZKB_OK; ++r) {
         const size_t nn = (cur + 1) / 2;
-        const Fr u_std = host_fr(h_u[r]);
         const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
         Fr* rows_r = rows + 3 * used;
         G1Aff* bases_r = bases + used;
@@ -728,7 +820,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
             Scratch round(side->st);   // MSM work buffers of this round, released in the side stream's order
             rc = msm_rows_affine<true>(bases_r, cur, rows_r, 3, kMaxWindows, d_proof + 3 * r, round, side->st);
         }
-        ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, u_std, gn[r & 1]);
+        ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
         cs = sc[r & 1];
         cg = gn[r & 1];
         used += cur;
