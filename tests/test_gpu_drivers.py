@@ -122,3 +122,27 @@ def test_self_attention_both_driver_sets_agree(tmp_path):
         assert np.all(np.abs(sums - 1.0) < 0.05)
     if len(results) == 2:
         assert results["own"] == results["reference-source"]
+
+
+def test_batch_mode_runs_stages_in_one_process(tmp_path):
+    """`zkllm-driver batch -`: the same stage command lines, one per line, in one resident process; a line is answered
+    by "[batch] <stage> <seconds> s" on stderr and gives the same files as separate processes; a bad line ends the batch."""
+    rng = np.random.Generator(np.random.PCG64(12))
+    seq, embed = 128, 256
+    x = np.rint(rng.standard_normal((seq, embed)) * 65536).astype(np.int64)
+    y = np.rint(rng.standard_normal((seq, embed)) * 65536).astype(np.int64)
+    save_int(tmp_path / "x.bin", x)
+    save_int(tmp_path / "y.bin", y)
+    script = tmp_path / "stages.txt"
+    script.write_text("# two stages\nskip-connection x.bin y.bin z.bin\n\nskip-connection z.bin y.bin w.bin\n")
+    env = dict(os.environ, ZKLLM_CHALLENGE_SEED="1234")
+    res = subprocess.run([str(BIN / "zkllm-driver"), "batch", str(script)], cwd=tmp_path, env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert res.stderr.count("[batch] skip-connection") == 2
+    assert np.array_equal(np.fromfile(tmp_path / "w.bin", dtype=np.int32).astype(np.int64), (x + 2 * y).reshape(-1))
+    # from standard input, and an unknown stage fails loudly
+    res = subprocess.run([str(BIN / "zkllm-driver"), "batch", "-"], cwd=tmp_path, env=env, capture_output=True, text=True,
+                         input="skip-connection x.bin y.bin z2.bin\nno-such-stage a b\n", timeout=600)
+    assert res.returncode != 0
+    assert np.array_equal(np.fromfile(tmp_path / "z2.bin", dtype=np.int32), np.fromfile(tmp_path / "z.bin", dtype=np.int32))

@@ -95,8 +95,8 @@ struct MsmShape {
     int W;                // windows
 };
 
-// One CTA per (segment, row): for each window, counting-sort the non-zero
-// digits of the segment by bucket.  ent: u16 lists, offs: 65 offsets per list.
+// One CTA per (segment, row, window class z): for each of its windows (z, z + gridDim.z, ...),
+// counting-sort the non-zero digits of the segment by bucket.  ent: u16 lists, offs: 65 offsets per list.
 template <bool FULL>
 __global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ scalars, MsmShape sh,
                                                         uint16_t* __restrict__ ent, uint16_t* __restrict__ offs) {
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ 
     const size_t col0 = (size_t)seg_id * sh.seg;
     const size_t ncol = (col0 + sh.seg <= sh.n) ? sh.seg : (sh.n > col0 ? sh.n - col0 : 0);
     const size_t rs = row * sh.nseg + seg_id;
-    for (int w = 0; w < sh.W; ++w) {
+    for (int w = blockIdx.z; w < sh.W; w += gridDim.z) {
         if (threadIdx.x <= kBuckets) hist[threadIdx.x] = 0;
         __syncthreads();
         for (size_t c = threadIdx.x; c < ncol; c += blockDim.x) {
@@ -373,40 +373,50 @@ __global__ void __launch_bounds__(32) msm_horner_kernel(const G1Jac* __restrict_
     }
 }
 
-// Shared driver over affine bases.  `scalars` is int32[m*n] (FULL = false) or raw
-// 256-bit Fr limbs [m*n] (FULL = true).
-template <bool FULL>
-static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, size_t m, int W,
-                           G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
-    if (m == 0) return ZKB_OK;
+// Shape of one MSM call: enough (row, segment) lists to fill warps, segments no
+// longer than kMaxSeg.  One list group of 32 lanes gives W * 64 warps, so
+// full-width scalars need only a few groups and prefer long lists; small integers
+// need thousands.  nseg_fixed != 0 prescribes the segment count (callers that
+// put the buckets of several calls into one array for a common reduction).
+static int msm_shape(size_t n, size_t m, int W, bool full, size_t nseg_fixed, MsmShape* out) {
     MsmShape sh;
     sh.m = m; sh.n = n; sh.W = W;
-    // enough (row, segment) lists to fill warps, segments no longer than kMaxSeg.
-    // One list group of 32 lanes gives W * 64 warps, so full-width scalars need
-    // only a few groups and prefer long lists; small integers need thousands.
-    const size_t want_lists = FULL ? 96 : 4096;
+    const size_t want_lists = full ? 96 : 4096;
     size_t nseg = (want_lists + m - 1) / m;
-    const size_t min_seg_len = FULL ? 64 : 256;
+    const size_t min_seg_len = full ? 64 : 256;
     if (nseg > (n + min_seg_len - 1) / min_seg_len) nseg = (n + min_seg_len - 1) / min_seg_len;
     if (nseg < (n + kMaxSeg - 1) / kMaxSeg) nseg = (n + kMaxSeg - 1) / kMaxSeg;
     if (nseg < 1) nseg = 1;
+    if (nseg_fixed) {
+        if (nseg_fixed < (n + kMaxSeg - 1) / kMaxSeg) return fail(ZKB_ERR_LIMIT, "commit: prescribed segment count too small");
+        nseg = nseg_fixed;
+    }
     if (nseg > 65535) return fail(ZKB_ERR_LIMIT, "commit: more than 2^30 generators");
     if (m > 65535 * 32) return fail(ZKB_ERR_LIMIT, "commit: too many rows");
+    if (m * nseg > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
     sh.nseg = (unsigned)nseg;
     sh.seg = (unsigned)((n + nseg - 1) / nseg);
+    *out = sh;
+    return ZKB_OK;
+}
+static size_t msm_bucket_count(const MsmShape& sh) { return sh.m * sh.nseg * (size_t)sh.W * kBuckets; }
+
+// Phase 1: digits -> sorted lists -> bucket sums per (row, segment, window), into
+// `buckets` (msm_bucket_count entries).  `scalars` is int32[m*n] (FULL = false) or
+// raw 256-bit Fr limbs [m*n] (FULL = true).
+template <bool FULL>
+static int msm_accumulate_phase(const G1Aff* bases, const void* d_scalars, const MsmShape& sh, G1Jac* buckets,
+                                Scratch& scratch, cudaStream_t s) {
+    const size_t m = sh.m, n = sh.n, nseg = sh.nseg;
+    const int W = sh.W;
     const size_t n_rs = m * nseg;
     const size_t n_lists = n_rs * W;
-    const bool few_rows = m * W < 4096;
-
     uint16_t* ent = scratch.get_n<uint16_t>(n_lists * sh.seg);
     uint16_t* offs = scratch.get_n<uint16_t>(n_lists * (kBuckets + 1));
-    G1Jac* buckets = scratch.get_n<G1Jac>(n_lists * kBuckets);
-    G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
-    G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
     uint32_t* perm = scratch.get_n<uint32_t>((size_t)W * kBuckets * n_rs);
-    if (!ent || !offs || !buckets || !Lg || !Gg || !perm) return ZKB_ERR_CUDA;
-    if (n_rs > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
-
+    if (!ent || !offs || !perm) return ZKB_ERR_CUDA;
+    // full-width scalars: few lists, many windows -> one CTA per (segment, row, window)
+    const unsigned zdim = FULL ? (unsigned)W : 1u;
     // rows go to gridDim.y in slices of at most 65535
     for (size_t r0 = 0; r0 < m; r0 += 65535) {
         const size_t rows = (m - r0 < 65535) ? m - r0 : 65535;
@@ -414,7 +424,7 @@ static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, 
         part.m = rows;
         const void* sc = FULL ? static_cast<const void*>(static_cast<const Fr*>(d_scalars) + r0 * n)
                               : static_cast<const void*>(static_cast<const int32_t*>(d_scalars) + r0 * n);
-        ZKB_LAUNCH(msm_sort_kernel<FULL>, dim3(sh.nseg, (unsigned)rows), 256, sh.seg * sizeof(uint16_t), s,
+        ZKB_LAUNCH(msm_sort_kernel<FULL>, dim3(sh.nseg, (unsigned)rows, zdim), 256, sh.seg * sizeof(uint16_t), s,
                    sc, part, ent + r0 * nseg * W * sh.seg, offs + r0 * nseg * W * (kBuckets + 1));
     }
     const size_t n_groups = (n_rs + 31) / 32;
@@ -423,16 +433,28 @@ static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, 
     if (acc_blocks > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
     ZKB_LAUNCH(msm_schedule_kernel, (unsigned)(W * kBuckets), 256, 0, s, offs, sh, n_rs, perm);
     ZKB_LAUNCH(msm_accumulate_kernel, (unsigned)acc_blocks, kAccWarps * 32, 0, s, bases, sh, ent, offs, perm, buckets, n_units);
-    if (!few_rows) {
+    return ZKB_OK;
+}
+
+// Phase 2: bucket sums -> one point per row.  Only m, nseg and W of the shape are used,
+// so the buckets of several phase-1 calls with equal nseg and W reduce together.
+static int msm_reduce_phase(const G1Jac* buckets, const MsmShape& sh, G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    const size_t m = sh.m;
+    const int W = sh.W;
+    G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
+    G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
+    if (!Lg || !Gg) return ZKB_ERR_CUDA;
+    if (m * W >= 4096) {
         ZKB_LAUNCH(msm_group_kernel, grid_for(m * W * 8, 128), 128, 0, s, buckets, sh, Lg, Gg);
         ZKB_LAUNCH(msm_finish_kernel, grid_for(m, 128), 128, 0, s, Lg, Gg, sh, d_out);
         return ZKB_OK;
     }
+    // few rows: sum over the segments first, all window totals in parallel, one Horner thread per row
     G1Jac* win = scratch.get_n<G1Jac>(m * W);
     if (!win) return ZKB_ERR_CUDA;
     const G1Jac* src = buckets;
     MsmShape one = sh;
-    if (nseg > 1) {
+    if (sh.nseg > 1) {
         G1Jac* red = scratch.get_n<G1Jac>(m * W * kBuckets);
         if (!red) return ZKB_ERR_CUDA;
         ZKB_LAUNCH(msm_seg_reduce_kernel, (unsigned)(m * W * 4), 128, 0, s, buckets, sh, red);
@@ -443,6 +465,18 @@ static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, 
     ZKB_LAUNCH(msm_window_kernel, grid_for(m * W, 64), 64, 0, s, Lg, Gg, m * W, win);
     ZKB_LAUNCH(msm_horner_kernel, grid_for(m, 32), 32, 0, s, win, sh, d_out);
     return ZKB_OK;
+}
+
+template <bool FULL>
+static int msm_rows_affine(const G1Aff* bases, size_t n, const void* d_scalars, size_t m, int W,
+                           G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    if (m == 0) return ZKB_OK;
+    MsmShape sh;
+    ZKB_TRY(msm_shape(n, m, W, FULL, 0, &sh));
+    G1Jac* buckets = scratch.get_n<G1Jac>(msm_bucket_count(sh));
+    if (!buckets) return ZKB_ERR_CUDA;
+    ZKB_TRY(msm_accumulate_phase<FULL>(bases, d_scalars, sh, buckets, scratch, s));
+    return msm_reduce_phase(buckets, sh, d_out, scratch, s);
 }
 
 // The same over Jacobian generators: normalised to affine once per call.
@@ -806,8 +840,23 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     size_t cur = n, used = 0;
     auto host_fr = [](const zkb_fr_t& h) { Fr r; memcpy(&r, &h, sizeof(Fr)); return r; };
     int rc = ZKB_OK;
+    // Rounds above kTailLen generators ("big" rounds): each one only forms its bucket
+    // sums on the side stream; all share one segment count, so a single reduction
+    // after the last of them turns the buckets of every round into proof points
+    // (the Horner chain over 37 windows is latency-bound: once, not once per round).
+    unsigned n_big = 0;
+    for (size_t c = n; n_big < k && c > kTailLen; c = (c + 1) / 2) ++n_big;
+    MsmShape big0;
+    G1Jac* big_buckets = nullptr;
+    size_t per_round = 0;
+    if (n_big) {
+        ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
+        per_round = msm_bucket_count(big0);
+        big_buckets = keep.get_n<G1Jac>(per_round * n_big);
+        if (!big_buckets) return ZKB_ERR_CUDA;
+    }
     unsigned r = 0;
-    for (; r < k && cur > kTailLen && rc == ZKB_OK; ++r) {
+    for (; r < n_big && rc == ZKB_OK; ++r) {
         const size_t nn = (cur + 1) / 2;
         const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
         Fr* rows_r = rows + 3 * used;
@@ -817,14 +866,22 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         ZKB_CUDA(cudaEventRecord(side->fork, s));
         ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
         {
-            Scratch round(side->st);   // MSM work buffers of this round, released in the side stream's order
-            rc = msm_rows_affine<true>(bases_r, cur, rows_r, 3, kMaxWindows, d_proof + 3 * r, round, side->st);
+            Scratch round(side->st);   // sorted lists of this round, released in the side stream's order
+            MsmShape sh;
+            rc = msm_shape(cur, 3, kMaxWindows, true, big0.nseg, &sh);
+            if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_round * r, round, side->st);
         }
         ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
         cs = sc[r & 1];
         cg = gn[r & 1];
         used += cur;
         cur = nn;
+    }
+    if (rc == ZKB_OK && n_big) {
+        MsmShape all = big0;
+        all.m = 3 * (size_t)n_big;
+        Scratch fin(side->st);
+        rc = msm_reduce_phase(big_buckets, all, d_proof, fin, side->st);
     }
     // the remaining K rounds and the final generator as one MSM over this round's generators
     const unsigned K = k - r;
