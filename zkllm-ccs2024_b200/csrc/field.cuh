@@ -321,7 +321,7 @@ template <class P> __host__ __device__ constexpr uint32_t fe_pm2_limb(int i) {
     return out;
 }
 
-template <class P> ZKB_DEV Fe<P> mont_inv(const Fe<P>& a) {
+template <class P> ZKB_DEV Fe<P> mont_inv_fermat(const Fe<P>& a) {
     constexpr int N = P::N;
     Fe<P> res = fe_mont_one<P>();
     Fe<P> base = a;
@@ -339,6 +339,80 @@ template <class P> ZKB_DEV Fe<P> mont_inv(const Fe<P>& a) {
         }
     }
     return res;
+}
+
+// Plain-integer helpers of the binary inversion below (values below 2^(32N)).
+template <class P> ZKB_DEV void fe_shr1(Fe<P>& a, uint32_t carry_in) {
+    constexpr int N = P::N;
+#pragma unroll
+    for (int i = 0; i < N - 1; ++i) a.v[i] = __funnelshift_r(a.v[i], a.v[i + 1], 1);
+    a.v[N - 1] = (a.v[N - 1] >> 1) | (carry_in << 31);
+}
+// x / 2 mod p for x in [0, p)
+template <class P> ZKB_DEV void fe_half(Fe<P>& x) {
+    constexpr int N = P::N;
+    const uint32_t odd = 0u - (x.v[0] & 1u);
+    x.v[0] = ptx_add_cc3(x.v[0], P::mod(0) & odd);
+#pragma unroll
+    for (int i = 1; i < N; ++i) x.v[i] = ptx_addc_cc3(x.v[i], P::mod(i) & odd);
+    const uint32_t carry = ptx_addc3(0u, 0u);
+    fe_shr1(x, carry);
+}
+// a >= b as integers
+template <class P> ZKB_DEV bool fe_geq(const Fe<P>& a, const Fe<P>& b) {
+    constexpr int N = P::N;
+    (void)ptx_sub_cc3(a.v[0], b.v[0]);
+#pragma unroll
+    for (int i = 1; i < N; ++i) (void)ptx_subc_cc3(a.v[i], b.v[i]);
+    return ptx_subc3(0u, 0u) == 0u;
+}
+// a -= b as integers, a >= b
+template <class P> ZKB_DEV void fe_sub_raw(Fe<P>& a, const Fe<P>& b) {
+    constexpr int N = P::N;
+    a.v[0] = ptx_sub_cc3(a.v[0], b.v[0]);
+#pragma unroll
+    for (int i = 1; i < N - 1; ++i) a.v[i] = ptx_subc_cc3(a.v[i], b.v[i]);
+    a.v[N - 1] = ptx_subc3(a.v[N - 1], b.v[N - 1]);
+}
+// 1/a in Montgomery form for a in Montgomery form; 0 maps to 0 like the
+// reference's Fermat inverse (bls12-381.cu:597-609), with the same value for
+// every other input.  Binary extended Euclid on plain integers: u, v shrink by
+// halving and subtracting while x1, x2 track u = x1 a, v = x2 a (mod p); at most
+// 2 * bits(p) short passes of shifts and additions instead of ~1.5 * bits(p) field
+// products.  The pass count is capped above that bound.
+template <class P> ZKB_DEV Fe<P> mont_inv(const Fe<P>& a) {
+    constexpr int N = P::N;
+    if (fe_is_zero(a)) return a;
+    Fe<P> u = a, v, x1 = fe_zero<P>(), x2 = fe_zero<P>();
+#pragma unroll
+    for (int i = 0; i < N; ++i) v.v[i] = P::mod(i);
+    x1.v[0] = 1u;
+    // every pass halves u or v once, so at most bits(u) + bits(v) passes run
+#pragma unroll 1
+    for (int it = 0; it < 64 * N + 64; ++it) {
+        if (!(u.v[0] & 1u)) {
+            fe_shr1(u, 0u);
+            fe_half(x1);
+        } else if (!(v.v[0] & 1u)) {
+            fe_shr1(v, 0u);
+            fe_half(x2);
+        } else {
+            if (fe_eq(u, v)) break;          // both equal the gcd, which is 1
+            if (fe_geq(u, v)) {
+                fe_sub_raw(u, v);            // odd - odd: even, halve at once
+                fe_shr1(u, 0u);
+                x1 = fe_sub(x1, x2);
+                fe_half(x1);
+            } else {
+                fe_sub_raw(v, u);
+                fe_shr1(v, 0u);
+                x2 = fe_sub(x2, x1);
+                fe_half(x2);
+            }
+        }
+    }
+    // u = v = 1 = x1 (a R): x1 is (a R)^-1 as a plain residue; the Montgomery form of 1/a is that times R^2
+    return mont_mul(mont_mul(x1, fe_r2<P>()), fe_r2<P>());
 }
 
 // ---------------------------------------------------------------------------

@@ -155,11 +155,38 @@ __global__ void __launch_bounds__(kThreads) fr_rowdot_kernel(const Fr* __restric
     __shared__ Fr red[32];
     for (size_t o = blockIdx.x; o < rows; o += gridDim.x) {
         const Fr* row = a + o * J;
-        Fr acc = fr_zero();
-        for (size_t j = threadIdx.x; j < J; j += blockDim.x)
-            acc = fr_add(acc, fr_mmul(fr_load(row + j), fr_load(E + j)));
-        acc = block_sum(acc, red);
+        LazyDot dot;
+        dot.init();
+        for (size_t j = threadIdx.x; j < J; j += blockDim.x) dot.add(fr_load(row + j), fr_load(E + j));
+        Fr acc = block_sum(dot.finish(), red);
         if (threadIdx.x == 0) fr_store(out + o, acc);
+    }
+}
+// The same with one warp per (row, part of the j range): no block barrier, four
+// loads in flight per lane.  out[p * rows + o] = partial sum of part p (parts > 1:
+// the caller adds the slices).
+__global__ void __launch_bounds__(kThreads) fr_rowdot_warp_kernel(const Fr* __restrict__ a, const Fr* __restrict__ E,
+                                                                   size_t rows, size_t J, unsigned parts, Fr* __restrict__ out) {
+    const unsigned lane = threadIdx.x & 31u;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t jper = (J + parts - 1) / parts;
+    for (size_t unit = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; unit < rows * parts; unit += warps) {
+        const size_t o = unit / parts, p = unit % parts;
+        const Fr* row = a + o * J;
+        const size_t j0 = p * jper, j1 = (j0 + jper < J) ? j0 + jper : J;
+        LazyDot dot;
+        dot.init();
+        size_t j = j0 + lane;
+        for (; j + 96 < j1; j += 128) {
+            const Fr x0 = fr_load(row + j), x1 = fr_load(row + j + 32), x2 = fr_load(row + j + 64), x3 = fr_load(row + j + 96);
+            dot.add(x0, fr_load(E + j));
+            dot.add(x1, fr_load(E + j + 32));
+            dot.add(x2, fr_load(E + j + 64));
+            dot.add(x3, fr_load(E + j + 96));
+        }
+        for (; j < j1; j += 32) dot.add(fr_load(row + j), fr_load(E + j));
+        const Fr acc = warp_sum(dot.finish());
+        if (lane == 0) fr_store(out + p * rows + o, acc);
     }
 }
 // window > 1: one thread per output element, loop over j (coalesced across w).
@@ -173,12 +200,13 @@ __global__ void __launch_bounds__(kThreads) fr_coldot_kernel(const Fr* __restric
     const size_t j1 = (j0 + jper < J) ? j0 + jper : J;
     for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < total; g += (size_t)gridDim.x * blockDim.x) {
         const size_t o = g / window, w = g % window;
-        Fr acc = fr_zero();
+        LazyDot dot;
+        dot.init();
         for (size_t j = j0; j < j1; ++j) {
             const size_t idx = (o * J + j) * window + w;
-            if (idx < a_len) acc = fr_add(acc, fr_mmul(fr_load(a + idx), fr_load(E + j)));
+            if (idx < a_len) dot.add(fr_load(a + idx), fr_load(E + j));
         }
-        fr_store(out + blockIdx.y * total + g, acc);
+        fr_store(out + blockIdx.y * total + g, dot.finish());
     }
 }
 // out[g] = sum_{s<S} part[s*total + g]
@@ -202,9 +230,10 @@ __global__ void __launch_bounds__(kThreads) fr_mle_kernel(const Fr* __restrict__
     Fr acc = fr_zero();
     for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const size_t base = c << kl;
-        Fr part = fr_zero();
-        for (size_t j = threadIdx.x; j < L && base + j < n; j += blockDim.x)
-            part = fr_add(part, fr_mmul(fr_load(a + base + j), fr_load(Elo + j)));
+        LazyDot dot;
+        dot.init();
+        for (size_t j = threadIdx.x; j < L && base + j < n; j += blockDim.x) dot.add(fr_load(a + base + j), fr_load(Elo + j));
+        Fr part = dot.finish();
         if (Ehi) part = fr_mmul(part, fr_load(Ehi + c));
         acc = fr_add(acc, part);
     }
@@ -241,6 +270,20 @@ int partial_me_device(const Fr* d_a, size_t a_len, size_t other, size_t J, size_
     if (!E) return ZKB_ERR_CUDA;
     ZKB_TRY(build_eq_table(h_u, k, E, stream));
     if (window == 1 && (other * J) <= a_len) {
+        if (other >= (size_t)sm_count() * 16) {
+            // enough (row, part) units for several waves of warps, parts of at least 512 entries
+            unsigned parts = 1;
+            while (parts < 8 && other * parts < (size_t)sm_count() * 128 && J / (parts * 2) >= 512) parts *= 2;
+            if (parts == 1) {
+                ZKB_LAUNCH(fr_rowdot_warp_kernel, grid_for(other, kThreads / 32, 8), kThreads, 0, stream, d_a, E, other, J, 1u, d_out);
+                return ZKB_OK;
+            }
+            Fr* part = scratch.get_n<Fr>(other * parts);
+            if (!part) return ZKB_ERR_CUDA;
+            ZKB_LAUNCH(fr_rowdot_warp_kernel, grid_for(other * parts, kThreads / 32, 8), kThreads, 0, stream, d_a, E, other, J, parts, part);
+            ZKB_LAUNCH(fr_sum_slices_kernel, grid_for(other, kThreads), kThreads, 0, stream, part, other, parts, d_out);
+            return ZKB_OK;
+        }
         ZKB_LAUNCH(fr_rowdot_kernel, grid_for(other, 1, 8), kThreads, 0, stream, d_a, E, other, J, d_out);
         return ZKB_OK;
     }

@@ -49,6 +49,74 @@ ZKB_DEV Fr block_sum(Fr v, Fr* smem) {
     return r;
 }
 
+// Sum of x_j * E_j where E_j is a Montgomery-form weight and most x_j are small
+// signed integers held as field elements (fixed-point tensors: |x| < 2^64, a
+// negative value stored as r - |x|).  A small x costs 8 (or 16) 32x32 multiply-adds
+// into an unreduced 352-bit accumulator instead of a 256-multiply-add Montgomery
+// product; positives and negatives accumulate apart, anything else goes through
+// the field product.  finish() returns sum x_j * e_j (e = E / R) as a field element.
+// Room: a term is below 2^319, so 2^33 terms fit.
+struct LazyDot {
+    uint32_t pos[11], neg[11];
+    Fr gen;
+    ZKB_DEV void init() {
+#pragma unroll
+        for (int i = 0; i < 11; ++i) pos[i] = neg[i] = 0u;
+        gen = fr_zero();
+    }
+    ZKB_DEV static void mac(uint32_t (&acc)[11], uint32_t x0, uint32_t x1, const Fr& e) {
+        unsigned long long c = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c += (unsigned long long)e.v[i] * x0 + acc[i];
+            acc[i] = (uint32_t)c;
+            c >>= 32;
+        }
+#pragma unroll
+        for (int i = 8; i < 11; ++i) {
+            c += acc[i];
+            acc[i] = (uint32_t)c;
+            c >>= 32;
+        }
+        if (x1) {
+            c = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                c += (unsigned long long)e.v[i] * x1 + acc[i + 1];
+                acc[i + 1] = (uint32_t)c;
+                c >>= 32;
+            }
+#pragma unroll
+            for (int i = 9; i < 11; ++i) {
+                c += acc[i];
+                acc[i] = (uint32_t)c;
+                c >>= 32;
+            }
+        }
+    }
+    ZKB_DEV void add(const Fr& x, const Fr& e) {
+        if ((x.v[2] | x.v[3] | x.v[4] | x.v[5] | x.v[6] | x.v[7]) == 0u) {
+            mac(pos, x.v[0], x.v[1], e);
+            return;
+        }
+        const Fr m = fr_neg(x);
+        if ((m.v[2] | m.v[3] | m.v[4] | m.v[5] | m.v[6] | m.v[7]) == 0u) mac(neg, m.v[0], m.v[1], e);
+        else gen = fr_add(gen, fr_mmul(x, e));
+    }
+    // T * R^-1 for an unreduced T = lo + hi * 2^256: (lo mod r) * R^-1 + hi
+    ZKB_DEV static Fr redc(const uint32_t (&acc)[11]) {
+        Fr lo, hi = fr_zero(), one = fr_zero();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo.v[i] = acc[i];
+        fe_final_sub(lo);   // 2^256 < 3r: two conditional subtractions make lo canonical
+        fe_final_sub(lo);
+        hi.v[0] = acc[8]; hi.v[1] = acc[9]; hi.v[2] = acc[10];
+        one.v[0] = 1u;
+        return fr_add(fr_mmul(lo, one), hi);
+    }
+    ZKB_DEV Fr finish() const { return fr_add(fr_sub(redc(pos), redc(neg)), gen); }
+};
+
 // Up to 32 challenges passed by value as a kernel argument (1 KiB).
 struct Challenges {
     Fr u[32];

@@ -43,19 +43,67 @@ struct EqTab {
     unsigned kl;
 };
 
-// Builds the tables for the first `k` challenges of h_u.
-static int make_eq(const zkb_fr_t* h_u, unsigned k, EqTab* out, Scratch& scratch, cudaStream_t s) {
-    const unsigned kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
-    Fr* lo = scratch.get_n<Fr>((size_t)1 << kl);
-    if (!lo) return ZKB_ERR_CUDA;
-    ZKB_TRY(build_eq_table(h_u, kl, lo, s));
-    Fr* hi = nullptr;
-    if (kh) {
-        hi = scratch.get_n<Fr>((size_t)1 << kh);
-        if (!hi) return ZKB_ERR_CUDA;
-        ZKB_TRY(build_eq_table(h_u + kl, kh, hi, s));
+// The tables of every round of a proof in ONE launch: round r uses the k0 - r
+// challenges that start at h_u[r * dstart] (dstart 0: a shrinking prefix, as in the
+// MSB-first provers; dstart 1: a shrinking suffix, as in the legacy provers).
+struct EqSeries {
+    unsigned k0, rounds, dstart;
+    unsigned lo_off[33], hi_off[33];   // entry offsets of each round's tables
+};
+__global__ void __launch_bounds__(256) eq_series_kernel(Challenges ch, EqSeries sr, Fr* __restrict__ lo_base, Fr* __restrict__ hi_base) {
+    __shared__ Fr f1[32], f0[32];   // u_j * R and (1 - u_j) * R
+    const unsigned r = blockIdx.y;
+    const unsigned k = sr.k0 - r, start = r * sr.dstart;
+    if (threadIdx.x < k) {
+        const Fr um = to_mont<FrP>(ch.u[start + threadIdx.x]);
+        f1[threadIdx.x] = um;
+        f0[threadIdx.x] = fr_sub(fe_mont_one<FrP>(), um);
     }
-    out->lo = lo; out->hi = hi; out->kl = kl;
+    __syncthreads();
+    const unsigned kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
+    const size_t n_lo = (size_t)1 << kl, n_all = n_lo + (kh ? (size_t)1 << kh : 0);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_all; i += (size_t)gridDim.x * blockDim.x) {
+        const bool high = i >= n_lo;
+        const size_t idx = high ? i - n_lo : i;
+        const unsigned nb = high ? kh : kl, b0 = high ? kl : 0;
+        Fr acc = fe_mont_one<FrP>();
+        for (unsigned j = 0; j < nb; ++j) acc = fr_mmul(acc, ((idx >> j) & 1) ? f1[b0 + j] : f0[b0 + j]);
+        fr_store((high ? hi_base + sr.hi_off[r] : lo_base + sr.lo_off[r]) + idx, acc);
+    }
+}
+
+static int make_eq_series(const zkb_fr_t* h_u, unsigned k0, unsigned rounds, unsigned dstart, EqTab* tabs,
+                          Scratch& scratch, cudaStream_t s) {
+    if (rounds == 0) return ZKB_OK;
+    if (rounds > 33 || rounds > k0 + 1 || k0 > 32) return fail(ZKB_ERR_LIMIT, "eq tables: more than 32 variables");
+    EqSeries sr;
+    memset(&sr, 0, sizeof(sr));
+    sr.k0 = k0; sr.rounds = rounds; sr.dstart = dstart;
+    size_t lo_total = 0, hi_total = 0, max_entries = 0;
+    for (unsigned r = 0; r < rounds; ++r) {
+        const unsigned k = k0 - r, kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
+        sr.lo_off[r] = (unsigned)lo_total;
+        sr.hi_off[r] = (unsigned)hi_total;
+        lo_total += (size_t)1 << kl;
+        if (kh) hi_total += (size_t)1 << kh;
+        const size_t e = ((size_t)1 << kl) + (kh ? (size_t)1 << kh : 0);
+        if (e > max_entries) max_entries = e;
+    }
+    if (hi_total > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "eq tables: too large");
+    Fr* lo = scratch.get_n<Fr>(lo_total);
+    Fr* hi = hi_total ? scratch.get_n<Fr>(hi_total) : nullptr;
+    if (!lo || (hi_total && !hi)) return ZKB_ERR_CUDA;
+    Challenges ch;
+    memset(&ch, 0, sizeof(ch));
+    for (unsigned j = 0; j < k0; ++j) memcpy(ch.u[j].v, h_u[j].val, 32);
+    unsigned gx = grid_for(max_entries, 256, 2);
+    ZKB_LAUNCH(eq_series_kernel, dim3(gx, rounds), 256, 0, s, ch, sr, lo, hi);
+    for (unsigned r = 0; r < rounds; ++r) {
+        const unsigned k = k0 - r, kl = k < kEqLoBits ? k : kEqLoBits, kh = k - kl;
+        tabs[r].lo = lo + sr.lo_off[r];
+        tabs[r].hi = kh ? hi + sr.hi_off[r] : nullptr;
+        tabs[r].kl = kl;
+    }
     return ZKB_OK;
 }
 
@@ -102,6 +150,63 @@ __global__ void __launch_bounds__(kThreads) zkip_round_kernel(const Fr* __restri
     grid_sum_finish<3>(acc, partial, ticket, out, 0x7u, red);
 }
 
+// The last rounds of zkip in ONE launch of one CTA: from kZkipTailHalf pairs down,
+// a round is a few microseconds of work and a separate launch each would cost
+// more than the arithmetic.  `vs` holds the challenges of these rounds in round
+// order (Montgomery form); wa/wb are two ping-pong buffers of `half` entries each.
+static constexpr size_t kZkipTailHalf = 2048;
+__global__ void __launch_bounds__(1024) zkip_tail_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n_in, size_t half,
+                                                          Challenges vs, unsigned rounds, Fr* __restrict__ wa, Fr* __restrict__ wb,
+                                                          Fr* __restrict__ out) {
+    __shared__ Fr red3[3][32];
+    const size_t stride = half;
+    const Fr* ca = a;
+    const Fr* cb = b;
+    for (unsigned r = 0; r < rounds; ++r) {
+        Fr* oa = wa + (r & 1) * stride;
+        Fr* ob = wb + (r & 1) * stride;
+        const Fr v_mont = vs.u[r];
+        Fr acc[3];
+        acc[0] = acc[1] = acc[2] = fr_zero();
+        for (size_t g = threadIdx.x; g < half; g += blockDim.x) {
+            const Fr a0 = g < n_in ? fr_load(ca + g) : fr_zero();
+            const Fr b0 = g < n_in ? fr_load(cb + g) : fr_zero();
+            const Fr a1 = g + half < n_in ? fr_load(ca + g + half) : fr_zero();
+            const Fr b1 = g + half < n_in ? fr_load(cb + g + half) : fr_zero();
+            const Fr da = fr_sub(a1, a0), db = fr_sub(b1, b0);
+            const Fr t0 = fr_mmul(a0, b0), t2 = fr_mmul(da, db);
+            const Fr t1 = fr_sub(fr_sub(fr_mmul(a1, b1), t0), t2);
+            acc[0] = fr_add(acc[0], t0);
+            acc[1] = fr_add(acc[1], t1);
+            acc[2] = fr_add(acc[2], t2);
+            fr_store(oa + g, fr_add(a0, fr_mmul(v_mont, da)));
+            fr_store(ob + g, fr_add(b0, fr_mmul(v_mont, db)));
+        }
+        // the three sums in one pass over the block (raw Montgomery sums; fixed up after the last round)
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+            acc[q] = warp_sum(acc[q]);
+            if (lane == 0) red3[q][warp] = acc[q];
+        }
+        __syncthreads();                       // also orders this round's stores before the next round's loads
+        if (warp == 0) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const Fr v = warp_sum(red3[q][lane]);
+                if (lane == 0) fr_store(out + 3 * r + q, v);
+            }
+        }
+        __syncthreads();
+        ca = oa;
+        cb = ob;
+        n_in = half;
+        half >>= 1;
+    }
+    // sums of raw Montgomery products carry 1/R: one multiplication by R^2 each, all in parallel
+    if (threadIdx.x < 3 * rounds) fr_store(out + threadIdx.x, fr_mmul(fr_load(out + threadIdx.x), fe_r2<FrP>()));
+}
+
 // Queues all rounds of zkip on `s`.  d_polys receives 3 Fr per round.  The final
 // folded scalars are not needed by the protocol and are dropped.
 static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h_u, unsigned k,
@@ -110,29 +215,42 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
     const unsigned kn = clog2(n);
     if (k > kn) return fail(ZKB_ERR_DIM, "zkip: more challenges than variables");
     size_t half = ((size_t)1 << kn) >> 1;
-    Fr* buf[2][2];
-    for (int i = 0; i < 2; ++i)
-        for (int j = 0; j < 2; ++j) {
-            buf[i][j] = scratch.get_n<Fr>(half >> i ? half >> i : 1);
-            if (!buf[i][j]) return ZKB_ERR_CUDA;
-        }
-    const unsigned max_grid = grid_for(half, kThreads, 4);
-    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
-    unsigned* ticket = scratch.get_n<unsigned>(4);
-    if (!partial || !ticket) return ZKB_ERR_CUDA;
-    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
     const Fr* ca = d_a;
     const Fr* cb = d_b;
     size_t n_in = n;
-    for (unsigned r = 0; r < k; ++r) {
-        const Fr v = dev_fr_mont(h_u[k - 1 - r]);
-        Fr* oa = buf[r & 1][0];
-        Fr* ob = buf[r & 1][1];
-        ZKB_LAUNCH(zkip_round_kernel, grid_for(half, kThreads, 4), kThreads, 0, s,
-                   ca, cb, n_in, half, v, oa, ob, partial, ticket, d_polys + 3 * r);
-        ca = oa; cb = ob;
-        n_in = half;
-        half >>= 1;
+    unsigned r = 0;
+    if (half > kZkipTailHalf) {
+        Fr* buf[2][2];
+        for (int i = 0; i < 2; ++i)
+            for (int j = 0; j < 2; ++j) {
+                buf[i][j] = scratch.get_n<Fr>(half >> i ? half >> i : 1);
+                if (!buf[i][j]) return ZKB_ERR_CUDA;
+            }
+        const unsigned max_grid = grid_for(half, kThreads, 4);
+        Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
+        unsigned* ticket = scratch.get_n<unsigned>(4);
+        if (!partial || !ticket) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+        for (; r < k && half > kZkipTailHalf; ++r) {
+            const Fr v = dev_fr_mont(h_u[k - 1 - r]);
+            Fr* oa = buf[r & 1][0];
+            Fr* ob = buf[r & 1][1];
+            ZKB_LAUNCH(zkip_round_kernel, grid_for(half, kThreads, 4), kThreads, 0, s,
+                       ca, cb, n_in, half, v, oa, ob, partial, ticket, d_polys + 3 * r);
+            ca = oa; cb = ob;
+            n_in = half;
+            half >>= 1;
+        }
+    }
+    if (r < k) {
+        const unsigned rounds = k - r;   // at most 12: half <= 2048 here
+        Challenges vs;
+        memset(&vs, 0, sizeof(vs));
+        for (unsigned t = 0; t < rounds; ++t) vs.u[t] = dev_fr_mont(h_u[k - 1 - (r + t)]);
+        Fr* wa = scratch.get_n<Fr>(2 * half);
+        Fr* wb = scratch.get_n<Fr>(2 * half);
+        if (!wa || !wb) return ZKB_ERR_CUDA;
+        ZKB_LAUNCH(zkip_tail_kernel, 1, 1024, 0, s, ca, cb, n_in, half, vs, rounds, wa, wb, d_polys + 3 * r);
     }
     return ZKB_OK;
 }
@@ -435,6 +553,17 @@ static int legacy_sumcheck(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_
     const Fr* ca = d_a;
     const Fr* cb = d_b;
     size_t n_in = n;
+    EqTab tabs[33];
+    if (MODE != 0 && k) {
+        // the reference requires the half-size arrays to fit their challenges exactly: check before any launch
+        size_t ni = n;
+        for (unsigned r = 0; r < k; ++r) {
+            const size_t no = (ni + 1) / 2, f = (size_t)1 << (k - 1 - r);
+            if (no <= f / 2 || no > f) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
+            ni = no;
+        }
+        ZKB_TRY(make_eq_series(h_u + 1, k - 1, k, 1, tabs, scratch, s));
+    }
     for (unsigned r = 0; r < k; ++r) {
         const size_t n_out = (n_in + 1) / 2;
         EqTab eq = {nullptr, nullptr, 0};
@@ -444,7 +573,7 @@ static int legacy_sumcheck(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_
             const unsigned kk = k - 1 - r;
             const size_t f = (size_t)1 << kk;
             if (n_out <= f / 2 || n_out > f) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
-            ZKB_TRY(make_eq(h_u + r + 1, kk, &eq, scratch, s));
+            eq = tabs[r];
         } else {
             eq.kl = kEqLoBits;
         }
@@ -598,10 +727,11 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
     const Fr* cm = CFR(d_m);
     size_t M = D;
     unsigned nu = kD;   // challenges of u still unbound
+    EqTab tabs[33];
+    if (kD) ZKB_TRY(make_eq_series(h_u, kD - 1, kD, 0, tabs, scratch, s));
     for (unsigned r = 0; r < kD; ++r) {
         const size_t half = M / 2;
-        EqTab eq;
-        ZKB_TRY(make_eq(h_u, nu - 1, &eq, scratch, s));
+        const EqTab eq = tabs[r];
         unsigned R, grid;
         pieces_for(half, &R, &grid);
         Fr* out = d_sums + 1 + 11 * (size_t)r;
@@ -703,10 +833,11 @@ int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, u
     HadamardPtrs ptrs;
     for (unsigned j = 0; j < K; ++j) ptrs.in[j] = CFR(h_d_Xs[j]);
     size_t M = N;
+    EqTab tabs[33];
+    if (kN) ZKB_TRY(make_eq_series(h_u, kN - 1, kN, 0, tabs, scratch, s));
     for (unsigned r = 0; r < kN; ++r) {
         const size_t half = M / 2;
-        EqTab eq;
-        ZKB_TRY(make_eq(h_u, kN - 1 - r, &eq, scratch, s));
+        const EqTab eq = tabs[r];
         for (unsigned j = 0; j < K; ++j) ptrs.out[j] = bufs[r & 1][j];
         const Fr v = dev_fr_mont(h_v[kN - 1 - r]);
         unsigned R, grid;
