@@ -37,6 +37,10 @@ ZKB_DEV void ptx_mad_lo_cc(uint32_t& acc, uint32_t a, uint32_t b) {
 ZKB_DEV void ptx_madc_lo_cc(uint32_t& acc, uint32_t a, uint32_t b) {
     asm volatile("madc.lo.cc.u32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));
 }
+// acc = a*b(hi) + acc, sets CC
+ZKB_DEV void ptx_mad_hi_cc(uint32_t& acc, uint32_t a, uint32_t b) {
+    asm volatile("mad.hi.cc.u32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));
+}
 // acc = a*b(hi) + acc + CC, sets CC
 ZKB_DEV void ptx_madc_hi_cc(uint32_t& acc, uint32_t a, uint32_t b) {
     asm volatile("madc.hi.cc.u32 %0, %1, %2, %0;" : "+r"(acc) : "r"(a), "r"(b));

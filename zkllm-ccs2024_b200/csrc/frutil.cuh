@@ -51,60 +51,66 @@ ZKB_DEV Fr block_sum(Fr v, Fr* smem) {
 
 // Sum of x_j * E_j where E_j is a Montgomery-form weight and most x_j are small
 // signed integers held as field elements (fixed-point tensors: |x| < 2^64, a
-// negative value stored as r - |x|).  A small x costs 8 (or 16) 32x32 multiply-adds
-// into an unreduced 352-bit accumulator instead of a 256-multiply-add Montgomery
-// product; positives and negatives accumulate apart, anything else goes through
-// the field product.  finish() returns sum x_j * e_j (e = E / R) as a field element.
-// Room: a term is below 2^319, so 2^33 terms fit.
+// negative value stored as r - |x|).  A small x costs two carry chains of 8
+// 32x32 multiply-adds (four chains above 2^32) into an unreduced 352-bit
+// accumulator instead of a 256-multiply-add Montgomery product; a negative x
+// is accumulated as |x| * (r - E), the same residue.  Anything that is not small
+// goes through the field product.  finish() returns sum x_j * e_j (e = E / R) as a
+// field element.  Room: a term is below 2^320, so 2^32 terms fit.
 struct LazyDot {
-    uint32_t pos[11], neg[11];
+    uint32_t acc[11];
     Fr gen;
     ZKB_DEV void init() {
 #pragma unroll
-        for (int i = 0; i < 11; ++i) pos[i] = neg[i] = 0u;
+        for (int i = 0; i < 11; ++i) acc[i] = 0u;
         gen = fr_zero();
     }
-    ZKB_DEV static void mac(uint32_t (&acc)[11], uint32_t x0, uint32_t x1, const Fr& e) {
-        unsigned long long c = 0;
+    // acc += x * e * 2^(32 * SH)
+    template <int SH>
+    ZKB_DEV void mac(uint32_t x, const Fr& e) {
+        ptx_mad_lo_cc(acc[SH], e.v[0], x);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c += (unsigned long long)e.v[i] * x0 + acc[i];
-            acc[i] = (uint32_t)c;
-            c >>= 32;
-        }
+        for (int i = 1; i < 8; ++i) ptx_madc_lo_cc(acc[SH + i], e.v[i], x);
 #pragma unroll
-        for (int i = 8; i < 11; ++i) {
-            c += acc[i];
-            acc[i] = (uint32_t)c;
-            c >>= 32;
-        }
-        if (x1) {
-            c = 0;
+        for (int i = SH + 8; i < 10; ++i) ptx_addc_cc(acc[i], 0u);
+        ptx_addc(acc[10], 0u);
+        ptx_mad_hi_cc(acc[SH + 1], e.v[0], x);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                c += (unsigned long long)e.v[i] * x1 + acc[i + 1];
-                acc[i + 1] = (uint32_t)c;
-                c >>= 32;
-            }
+        for (int i = 1; i < 8; ++i) ptx_madc_hi_cc(acc[SH + 1 + i], e.v[i], x);
 #pragma unroll
-            for (int i = 9; i < 11; ++i) {
-                c += acc[i];
-                acc[i] = (uint32_t)c;
-                c >>= 32;
-            }
-        }
+        for (int i = SH + 9; i < 10; ++i) ptx_addc_cc(acc[i], 0u);
+        if (SH + 9 <= 10) ptx_addc(acc[10], 0u);
+    }
+    // r - a as plain integers (a in [0, r])
+    ZKB_DEV static Fr rsub(const Fr& a) {
+        Fr d;
+        d.v[0] = ptx_sub_cc3(FrP::mod(0), a.v[0]);
+#pragma unroll
+        for (int i = 1; i < 7; ++i) d.v[i] = ptx_subc_cc3(FrP::mod(i), a.v[i]);
+        d.v[7] = ptx_subc3(FrP::mod(7), a.v[7]);
+        return d;
     }
     ZKB_DEV void add(const Fr& x, const Fr& e) {
-        if ((x.v[2] | x.v[3] | x.v[4] | x.v[5] | x.v[6] | x.v[7]) == 0u) {
-            mac(pos, x.v[0], x.v[1], e);
-            return;
+        uint32_t m0 = x.v[0], m1 = x.v[1];
+        Fr w = e;
+        bool small = (x.v[2] | x.v[3] | x.v[4] | x.v[5] | x.v[6] | x.v[7]) == 0u;
+        if (!small) {
+            const Fr m = rsub(x);
+            if ((m.v[2] | m.v[3] | m.v[4] | m.v[5] | m.v[6] | m.v[7]) == 0u) {
+                small = true;
+                m0 = m.v[0]; m1 = m.v[1];
+                w = rsub(e);
+            }
         }
-        const Fr m = fr_neg(x);
-        if ((m.v[2] | m.v[3] | m.v[4] | m.v[5] | m.v[6] | m.v[7]) == 0u) mac(neg, m.v[0], m.v[1], e);
-        else gen = fr_add(gen, fr_mmul(x, e));
+        if (small) {
+            mac<0>(m0, w);
+            if (m1) mac<1>(m1, w);
+        } else {
+            gen = fr_add(gen, fr_mmul(x, e));
+        }
     }
-    // T * R^-1 for an unreduced T = lo + hi * 2^256: (lo mod r) * R^-1 + hi
-    ZKB_DEV static Fr redc(const uint32_t (&acc)[11]) {
+    // T * R^-1 for the unreduced T = lo + hi * 2^256: (lo mod r) * R^-1 + hi
+    ZKB_DEV Fr finish() const {
         Fr lo, hi = fr_zero(), one = fr_zero();
 #pragma unroll
         for (int i = 0; i < 8; ++i) lo.v[i] = acc[i];
@@ -112,9 +118,8 @@ struct LazyDot {
         fe_final_sub(lo);
         hi.v[0] = acc[8]; hi.v[1] = acc[9]; hi.v[2] = acc[10];
         one.v[0] = 1u;
-        return fr_add(fr_mmul(lo, one), hi);
+        return fr_add(fr_add(fr_mmul(lo, one), hi), gen);
     }
-    ZKB_DEV Fr finish() const { return fr_add(fr_sub(redc(pos), redc(neg)), gen); }
 };
 
 // Up to 32 challenges passed by value as a kernel argument (1 KiB).
@@ -160,14 +165,25 @@ ZKB_DEV Fr fr_load_cg(const Fr* p) {   // L2-coherent load for data written by o
 // CTA waits on another.
 template <int NS>
 ZKB_DEV void grid_sum_finish(Fr (&acc)[NS], Fr* __restrict__ partial, unsigned* __restrict__ ticket,
-                             Fr* __restrict__ out, unsigned fix_mask, Fr* red /* shared, 32 Fr */,
+                             Fr* __restrict__ out, unsigned fix_mask, Fr* /* red: kept for the callers' signature */,
                              int fix_reps = 1) {
+    __shared__ Fr stage[NS][32];
     __shared__ bool is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    // all NS sums move together: one barrier per level instead of two per sum
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
-        Fr v = block_sum(acc[s], red);
-        if (threadIdx.x == 0) fr_store(partial + (size_t)blockIdx.x * NS + s, v);
+        acc[s] = warp_sum(acc[s]);
+        if (lane == 0) stage[s][warp] = acc[s];
     }
+    __syncthreads();
+    for (int s = warp; s < NS; s += nwarps) {
+        Fr v = lane < nwarps ? stage[s][lane] : fr_zero();
+        v = warp_sum(v);
+        if (lane == 0) fr_store(partial + (size_t)blockIdx.x * NS + s, v);
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         const unsigned t = atomicAdd(ticket, 1u);
@@ -176,13 +192,12 @@ ZKB_DEV void grid_sum_finish(Fr (&acc)[NS], Fr* __restrict__ partial, unsigned* 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-#pragma unroll 1
-    for (int s = 0; s < NS; ++s) {
+    // the CTA that drew the last ticket: one warp per sum over the per-CTA rows
+    for (int s = warp; s < NS; s += nwarps) {
         Fr v = fr_zero();
-        for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x)
-            v = fr_add(v, fr_load_cg(partial + (size_t)b * NS + s));
-        v = block_sum(v, red);
-        if (threadIdx.x == 0) {
+        for (unsigned b = lane; b < gridDim.x; b += 32) v = fr_add(v, fr_load_cg(partial + (size_t)b * NS + s));
+        v = warp_sum(v);
+        if (lane == 0) {
             if ((fix_mask >> s) & 1u)
                 for (int t = 0; t < fix_reps; ++t) v = fr_mmul(v, fe_r2<FrP>());
             fr_store(out + s, v);
