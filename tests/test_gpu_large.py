@@ -266,3 +266,28 @@ def test_me_open_round_identities_at_full_width(dev, n):
     last = C.g1_mul(np.ascontiguousarray(hp[3 * k:3 * k + 1]), ho)                                  # final scalar (raw limbs) * final generator
     expect = np.ascontiguousarray(np.concatenate([hp[3:3 * k:3], last]))
     assert np.array_equal(C.g1_normalise(nxt), C.g1_normalise(expect))
+
+
+def test_block_evaluations_combine_like_the_sharded_path(dev):
+    """The multi-GPU split of a multilinear evaluation, with the ranks emulated in one process: each block of a 2^20-element
+    tensor is evaluated on the device at the low challenges, the blocks are weighted by eq(high challenges; rank) as
+    sharding.sharded_mle_combine does, and the sum equals the device evaluation of the whole tensor."""
+    from zkllm_ccs2024_b200 import sharding as S
+    z = dev.z
+    k, kw = 20, 2                                   # 4 ranks
+    rng = np.random.Generator(np.random.PCG64(5))
+    t = _rand_fr_limbs(rng, 1 << k)
+    u = _rand_fr_limbs(rng, k)
+    d_t = z.DeviceBuffer.from_host(t)
+    whole = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_fr_mle_eval", z._p(d_t), z.sz(1 << k), z._p(u), z.u32(k), z._p(whole), z._p(0))
+    u_high = S.fr_limbs_to_ints(u[k - kw:])
+    acc = 0
+    n_local = 1 << (k - kw)
+    for rank in range(1 << kw):
+        d_block = z.DeviceBuffer.from_host(np.ascontiguousarray(t[rank * n_local:(rank + 1) * n_local]))
+        part = np.zeros((1, 8), dtype=np.uint32)
+        dev.call("zkb_fr_mle_eval", z._p(d_block), z.sz(n_local), z._p(np.ascontiguousarray(u[:k - kw])), z.u32(k - kw), z._p(part),
+                 z._p(0))
+        acc = (acc + S.fr_limbs_to_ints(part)[0] * S.block_weight(u_high, rank)) % S.R_MOD
+    assert acc == S.fr_limbs_to_ints(whole)[0]

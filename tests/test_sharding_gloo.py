@@ -34,7 +34,14 @@ def _worker(rank, world, port, m, q):
     rng = random.Random(100 + rank)
     parts = [rng.randrange(S.R_MOD) for _ in range(3)]
     red = S.fr_limbs_to_ints(S.fr_allreduce_sum(S.fr_ints_to_limbs(parts)))
-    q.put((rank, ok_rows, parts, red))
+    # a 64-element tensor in two blocks: block evaluations at the low challenges combine into the whole evaluation
+    from oracle import pyref as R
+    rs = random.Random(7)
+    t = [rs.randrange(R.R_MOD) for _ in range(64)]
+    u = [rs.randrange(R.R_MOD) for _ in range(6)]
+    local = R.mle_eval(t[rank * 32:(rank + 1) * 32], u[:5])
+    whole = S.fr_limbs_to_ints(S.sharded_mle_combine(S.fr_ints_to_limbs([local]), u[5:]))[0]
+    q.put((rank, ok_rows and whole == R.mle_eval(t, u), parts, red))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -9,7 +9,10 @@ splits without changing any result:
   * sums of field elements (round-polynomial coefficients of a sharded sumcheck)
     are gathered and added modulo r on every rank - modular addition is not a
     reduction NCCL offers;
-  * a sum of G1 points is gathered and added in rank order.
+  * a sum of G1 points is gathered and added in rank order;
+  * a multilinear evaluation (FrTensor::operator()(u), fr-tensor.cu:437-442) of a
+    tensor split into equal contiguous blocks is the sum of the blocks' own
+    evaluations at the low challenges, each weighted by eq(high challenges; rank).
 
 Everything here runs on the `gloo` backend as well, which is how it is tested
 without GPUs.
@@ -74,3 +77,24 @@ def fr_allreduce_sum(partials: np.ndarray, group=None) -> np.ndarray:
         for i, v in enumerate(fr_limbs_to_ints(b.cpu().numpy().view(np.uint32).reshape(k, 8))):
             acc[i] = (acc[i] + v) % R_MOD
     return fr_ints_to_limbs(acc)
+
+
+def block_weight(u_high, rank: int) -> int:
+    """eq(u_high; rank): challenge j pairs with bit j of the rank (the index bits above a block)"""
+    w = 1
+    for j, u in enumerate(u_high):
+        w = w * (u if (rank >> j) & 1 else (1 - u)) % R_MOD
+    return w
+
+
+def sharded_mle_combine(local_value: np.ndarray, u_high, group=None) -> np.ndarray:
+    """The tensor is split into world = 2^len(u_high) equal contiguous blocks, rank p holding block p.
+    `local_value` ((1, 8) uint32) is this rank's block evaluated at the low challenges (zkb_fr_mle_eval
+    on the block); returns the evaluation of the whole tensor at (u_low, u_high) on every rank."""
+    import torch.distributed as dist
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if world != 1 << len(u_high):
+        raise ValueError("world size must be 2^len(u_high)")
+    v = fr_limbs_to_ints(local_value)[0]
+    return fr_allreduce_sum(fr_ints_to_limbs([v * block_weight(u_high, rank) % R_MOD]), group)
