@@ -1,0 +1,37 @@
+"""GPU: the parts of the class API that no stage driver reaches - zkip_stacked / zkFCStacked and zkAttn / zkAttnStacked.
+
+oracle/api_check.cu uses only the public class API; it is built twice, against this repository's host library
+(zkllm-ccs2024_b200/bin/api-check) and against the reference's own CUDA sources (oracle/_ref/api_check_ref, present where the
+reference was available at build time).  Both print the round polynomials and final claims of the same seeded inputs.
+The library's output must equal the lines recorded from the reference build (tests/golden/api_check_<case>.txt) and,
+when the reference build is present, what that build prints now.  Every prove() also checks its own verifier equations.
+"""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+OURS = ROOT / "zkllm-ccs2024_b200" / "bin" / "api-check"
+REF = ROOT / "oracle" / "_ref" / "api_check_ref"
+GOLDEN = ROOT / "tests" / "golden"
+
+
+def run(exe: Path, case: str) -> list:
+    res = subprocess.run([str(exe), case], capture_output=True, text=True, timeout=1200)
+    assert res.returncode == 0, f"{exe.name} {case}: {res.stdout[-1500:]}\n{res.stderr[-1500:]}"
+    return [ln for ln in res.stdout.splitlines() if ln.split(" ")[0].startswith(("poly", "final", "out", "ok"))]
+
+
+@pytest.mark.parametrize("case", ["fcstacked", "attn", "attnstacked"])
+def test_class_api_matches_the_reference_build(case):
+    assert OURS.exists(), "bin/api-check is missing: run zkllm-ccs2024_b200/build.py"
+    ours = run(OURS, case)
+    assert ours and ours[-1] == "ok 1"
+    golden = GOLDEN / f"api_check_{case}.txt"
+    assert golden.exists(), f"{golden} is missing"
+    assert ours == golden.read_text().splitlines(), "output differs from the lines recorded from the reference build"
+    if REF.exists():
+        assert ours == run(REF, case), "output differs from the reference build run now"
