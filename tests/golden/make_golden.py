@@ -8,6 +8,10 @@ reference sources are present; device-LTO like the reference's own Makefile):
 Every case writes its seeded inputs to raw .bin files, runs one harness command
 (which calls the reference's public classes) and records inputs and outputs as
 hex strings.  tests/test_oracle_golden.py replays the cases through the oracle.
+
+With --api-check it also runs oracle/_ref/api_check_ref (oracle/api_check.cu built
+against the reference, `make -C oracle ref-api`) and writes the lines it prints for
+each case to tests/golden/api_check_<case>.txt (tests/test_gpu_api_check.py).
 """
 from __future__ import annotations
 
@@ -213,7 +217,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--harness", default=str(ROOT / "oracle" / "_ref" / "ref_harness"))
     ap.add_argument("--out", default=str(ROOT / "tests" / "golden" / "ref_golden.json"))
+    ap.add_argument("--api-check", action="store_true", help="also record the output of oracle/_ref/api_check_ref")
     args = ap.parse_args()
+    if args.api_check:
+        exe = ROOT / "oracle" / "_ref" / "api_check_ref"
+        for case in ("fcstacked", "attn", "attnstacked"):
+            res = subprocess.run([str(exe), case], capture_output=True, text=True, check=True)
+            keep = [ln for ln in res.stdout.splitlines() if ln.split(" ")[0].startswith(("poly", "final", "out", "ok"))]
+            (ROOT / "tests" / "golden" / f"api_check_{case}.txt").write_text("\n".join(keep) + "\n")
+            print(f"wrote {len(keep)} lines for {case}")
     with tempfile.TemporaryDirectory() as tmp:
         cases = build(Ctx(args.harness, Path(tmp)))
     Path(args.out).parent.mkdir(parents=True, exist_ok=True)
