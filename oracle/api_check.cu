@@ -2,7 +2,7 @@
 // class API that the reference's headers and zkllm-ccs2024_b200/host/ both
 // declare (zkfc.cuh, zksoftmax.cuh, fr-tensor.cuh, polynomial.cuh), so the same
 // program runs the reference's own CUDA code (oracle/Makefile: `make ref-api`,
-// _ref/api_check_ref) and this repository's library (build.py: bin/api-check).
+// _ref/api_check_ref) and this repository's library (`make api`, _build/api_check).
 // Inputs and challenges come from a fixed integer generator, so the two builds
 // print the same lines when the implementations agree.  Covered here are the
 // parts of the API that no stage driver reaches: zkip_stacked / zkFCStacked

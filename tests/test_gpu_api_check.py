@@ -1,7 +1,7 @@
 """GPU: the parts of the class API that no stage driver reaches - zkip_stacked / zkFCStacked and zkAttn / zkAttnStacked.
 
 oracle/api_check.cu uses only the public class API; it is built twice, against this repository's host library
-(zkllm-ccs2024_b200/bin/api-check) and against the reference's own CUDA sources (oracle/_ref/api_check_ref, present where the
+(oracle/_build/api_check, `make -C oracle api`) and against the reference's own CUDA sources (oracle/_ref/api_check_ref, present where the
 reference was available at build time).  Both print the round polynomials and final claims of the same seeded inputs.
 The library's output must equal the lines recorded from the reference build (tests/golden/api_check_<case>.txt) and,
 when the reference build is present, what that build prints now.  Every prove() also checks its own verifier equations.
@@ -14,7 +14,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
-OURS = ROOT / "zkllm-ccs2024_b200" / "bin" / "api-check"
+OURS = ROOT / "oracle" / "_build" / "api_check"
 REF = ROOT / "oracle" / "_ref" / "api_check_ref"
 GOLDEN = ROOT / "tests" / "golden"
 
@@ -27,7 +27,7 @@ def run(exe: Path, case: str) -> list:
 
 @pytest.mark.parametrize("case", ["fcstacked", "attn", "attnstacked"])
 def test_class_api_matches_the_reference_build(case):
-    assert OURS.exists(), "bin/api-check is missing: run zkllm-ccs2024_b200/build.py"
+    assert OURS.exists(), "oracle/_build/api_check is missing: run make -C oracle api"
     ours = run(OURS, case)
     assert ours and ours[-1] == "ok 1"
     golden = GOLDEN / f"api_check_{case}.txt"

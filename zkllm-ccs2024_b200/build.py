@@ -102,14 +102,6 @@ def build_host(force: bool = False) -> Path:
         if link.is_symlink() or link.exists():
             link.unlink()
         link.symlink_to("zkllm-driver")
-    # the class-API check program of the test suite (source shared with the reference build of it)
-    api_src = HERE.parent / "oracle" / "api_check.cu"
-    if api_src.exists():
-        api_obj = out / "api_check.o"
-        if force or not api_obj.exists() or api_obj.stat().st_mtime < max(api_src.stat().st_mtime, newest_hdr):
-            _run([HOST_CXX, "-x", "c++", "-std=c++17", "-O1", f"-I{HOST}", "-c", str(api_src), "-o", str(api_obj)])
-        _run([HOST_CXX, "-o", str(BIN / "api-check"), str(api_obj), f"-L{LIB.parent}", "-lzkllm_host", "-lzkllm_b200",
-              "-Wl,-rpath,$ORIGIN/../lib"])
     print(f"linked: {HOST_LIB} and {exe}")
     return HOST_LIB
 

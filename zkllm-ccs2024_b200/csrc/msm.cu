@@ -629,11 +629,11 @@ static FoldDigits fold_digits(const zkb_fr_t& u) {
         for (int i = 3; i >= 0; --i)
             if (limb[i] != rmod[i]) { ge = limb[i] > rmod[i]; break; }
         if (!ge) break;
-        uint64_t borrow = 0;
+        u128 borrow = 0;
         for (int i = 0; i < 4; ++i) {
-            const uint64_t d = limb[i] - rmod[i] - borrow;
-            borrow = (limb[i] < rmod[i] + borrow || (borrow && rmod[i] == ~0ull)) ? 1 : 0;
-            limb[i] = d;
+            const u128 d = (u128)limb[i] - rmod[i] - borrow;   // wraps modulo 2^128 when negative
+            limb[i] = (uint64_t)d;
+            borrow = (d >> 64) ? 1 : 0;
         }
     }
     u128 rem = 0, quo = 0;
@@ -818,6 +818,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
                 zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
     cudaStream_t s = as_stream(stream);
     if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
+    if (k > 62) return fail(ZKB_ERR_LIMIT, "Commitment::me_open - more than 62 rounds");
     SideStream* side = side_stream();
     if (!side) return ZKB_ERR_CUDA;
     std::lock_guard<std::mutex> turn(side->busy);
