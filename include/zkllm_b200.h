@@ -217,6 +217,10 @@ int zkb_binary_sumcheck(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, cons
  * in [-sf/2, sf/2) */
 int zkb_rescale(const zkb_fr_t* d_in, uint64_t scaling_factor, zkb_fr_t* d_out, zkb_fr_t* d_rem,
                 size_t n, void* stream);
+/* zkrelu_decomp_kernel (zkrelu.cu:9-30): with q = round-to-nearest x / sf as above,
+ * sign = (q >= 0), abs = |q|, rem = x - q*sf, res = max(q, 0) */
+int zkb_relu_decomp(const zkb_fr_t* d_in, uint64_t scaling_factor, zkb_fr_t* d_sign, zkb_fr_t* d_abs,
+                    zkb_fr_t* d_rem, zkb_fr_t* d_res, size_t n, void* stream);
 /* zksoftmax_calculate_table (zksoftmax.cu:4-16) */
 int zkb_softmax_table(double theta_k, double scaling_factor_in, double d, double Bk, uint32_t bk,
                       zkb_fr_t* d_table, void* stream);

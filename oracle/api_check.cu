@@ -6,10 +6,11 @@
 // Inputs and challenges come from a fixed integer generator, so the two builds
 // print the same lines when the implementations agree.  Covered here are the
 // parts of the API that no stage driver reaches: zkip_stacked / zkFCStacked
-// (zkfc.cu:153-307) and zkAttn / zkAttnStacked (zksoftmax.cu:222-320).  Every
+// (zkfc.cu:153-307), zkAttn / zkAttnStacked (zksoftmax.cu:222-320) and zkReLU
+// (zkrelu.cu:3-66).  Every
 // prove() below throws if one of its verifier equations fails.
 //
-// usage: api_check <fcstacked|attn|attnstacked>
+// usage: api_check <fcstacked|attn|attnstacked|relu>
 // output: "poly<i> <coefficients>" per round polynomial, "final <Fr>", "ok 1".
 #include <iostream>
 #include <string>
@@ -18,6 +19,7 @@
 #include "fr-tensor.cuh"
 #include "polynomial.cuh"
 #include "zkfc.cuh"
+#include "zkrelu.cuh"
 #include "zksoftmax.cuh"
 
 using namespace std;
@@ -48,6 +50,12 @@ struct Gen {
         return FrTensor(n, h.data());
     }
 };
+
+static void print_tensor(const char* key, const FrTensor& t) {
+    cout << key;
+    for (uint i = 0; i < t.size; ++i) cout << " " << t(i);
+    cout << endl;
+}
 
 static void print_polys(vector<Polynomial>& ps) {
     for (size_t i = 0; i < ps.size(); ++i) cout << "poly" << i << " " << ps[i] << endl;
@@ -127,13 +135,33 @@ static int attn_stacked() {
     return 0;
 }
 
+static int relu() {
+    Gen g(0x5EED0004);
+    const uint n = 1 << 12;
+    vector<long> h(n);
+    for (auto& x : h) x = (long)(g.next() % (1UL << 41)) - (1L << 40);
+    h[0] = 0; h[1] = 32768; h[2] = -32768; h[3] = -32769; h[4] = 65536;
+    FrTensor X(n, h.data());
+    zkReLU act(1 << 16);
+    FrTensor res = act(X);
+    print_tensor("out_res", res);
+    print_tensor("out_sign", *act.sign_tensor_ptr);
+    print_tensor("out_abs", *act.abs_tensor_ptr);
+    print_tensor("out_rem", *act.rem_tensor_ptr);
+    cout << "out_m_sum " << act.m_tensor_ptr->sum() << endl;
+    act.prove(X, res);
+    cout << "ok 1" << endl;
+    return 0;
+}
+
 int main(int argc, char** argv) {
     const string cmd = argc > 1 ? argv[1] : "";
     try {
         if (cmd == "fcstacked") return fc_stacked();
         if (cmd == "attn") return attn();
         if (cmd == "attnstacked") return attn_stacked();
-        cerr << "usage: api_check <fcstacked|attn|attnstacked>" << endl;
+        if (cmd == "relu") return relu();
+        cerr << "usage: api_check <fcstacked|attn|attnstacked|relu>" << endl;
         return 2;
     } catch (const std::exception& e) {
         cout << "exception " << e.what() << endl;

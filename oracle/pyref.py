@@ -554,6 +554,18 @@ def _c_mod(a: int, b: int) -> int:
     return a - q * b
 
 
+def relu_decomp(X: list, sf: int):
+    """zkrelu_decomp_kernel, zkrelu.cu:9-30: returns (sign, magnitude, remainder, relu) Fr lists of the rescaled values"""
+    q, rem = rescale(X, sf)
+    sign, mag, res = [], [], []
+    for v in q:
+        pos = v < (R_MOD + 1) // 2        # a non-negative small integer
+        sign.append(1 if pos else 0)
+        mag.append(v if pos else (R_MOD - v) % R_MOD)
+        res.append(v if pos else 0)
+    return sign, mag, rem, res
+
+
 def rescale(X: list, sf: int):
     """returns (rescaled, remainder) Fr lists"""
     out, rem = [], []

@@ -235,6 +235,24 @@ def test_inv_shifted(dev, n):
     assert dev.read_fr(do, n) == [R.fr_inv((x + beta) % R.R_MOD) for x in a]
 
 
+def test_relu_decomposition(dev):
+    """zkReLU's kernel: sign, magnitude, remainder and max(q, 0) of the rescaled value q"""
+    z = dev.z
+    rng = random.Random(12)
+    vals = [0, 1, -1, 32767, 32768, -32768, -32769, 65536, -65536, 98304, -98304, 2**40 + 12345, -(2**40) - 77]
+    vals += [rng.randrange(-2**45, 2**45) for _ in range(300)]
+    for sf in (1 << 16, 1 << 20, 3):
+        x = [R.int_to_fr(v) for v in vals]
+        outs = [dev.fr_out(len(x)) for _ in range(4)]
+        dev.call("zkb_relu_decomp", z._p(dev.fr(x)), z.u64(sf), *[z._p(o) for o in outs], z.sz(len(x)), z._p(0))
+        exp = R.relu_decomp(x, sf)
+        for got, e in zip(outs, exp):
+            assert dev.read_fr(got, len(x)) == e
+        for v, sg, mg, rm, rs in zip(vals, *exp):
+            q = (v - R.fr_to_long(rm)) // sf
+            assert (sg, mg, R.fr_to_long(rs)) == (1 if q >= 0 else 0, abs(q), max(q, 0))
+
+
 def test_rescale(dev):
     z = dev.z
     rng = random.Random(11)

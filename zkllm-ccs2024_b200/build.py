@@ -64,7 +64,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 HOST = HERE / "host"
-HOST_SOURCES = ["ioutils", "fr-tensor", "polynomial", "g1-tensor", "commitment", "proof", "zkfc", "tlookup", "rescaling", "zksoftmax"]
+HOST_SOURCES = ["ioutils", "fr-tensor", "polynomial", "g1-tensor", "commitment", "proof", "zkfc", "tlookup", "rescaling", "zksoftmax", "zkrelu"]
 HOST_LIB = HERE / "lib" / "libzkllm_host.so"
 BIN = HERE / "bin"
 STAGES = ["ppgen", "commit-param", "rmsnorm", "self-attn", "ffn", "skip-connection"]

@@ -16,6 +16,24 @@ __global__ void rescale_kernel(const Fr* __restrict__ in, long sf, Fr* __restric
     }
 }
 
+// zkrelu_decomp_kernel (zkrelu.cu:9-30): the rescaled value split into sign,
+// magnitude and centred remainder; res = max(rescaled, 0).
+__global__ void relu_decomp_kernel(const Fr* __restrict__ in, long sf, Fr* __restrict__ sign, Fr* __restrict__ mag,
+                                   Fr* __restrict__ rem, Fr* __restrict__ res, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const long hsf = sf >> 1;
+        const long x = fr_to_i64(fr_load(in + i));
+        const long t = (x + hsf) % sf;
+        const long x_rem = (t < 0 ? t + sf : t) - hsf;
+        const long x_res = (x - x_rem) / sf;
+        const bool pos = x_res >= 0;
+        fr_store(sign + i, fr_from_u64(pos ? 1ull : 0ull));
+        fr_store(mag + i, fr_from_i64(pos ? x_res : -x_res));
+        fr_store(rem + i, fr_from_i64(x_rem));
+        fr_store(res + i, pos ? fr_from_i64(x_res) : fr_zero());
+    }
+}
+
 // zksoftmax_calculate_table (zksoftmax.cu:4-16).  The expression is kept in the
 // reference's form so that the double-precision result rounds identically.
 __global__ void softmax_table_kernel(Fr* __restrict__ table, double theta_k, double scaling_factor_in, double d, double Bk, uint32_t bk) {
@@ -93,6 +111,15 @@ int zkb_rescale(const zkb_fr_t* d_in, uint64_t scaling_factor, zkb_fr_t* d_out, 
     if (scaling_factor == 0) return fail(ZKB_ERR_ARG, "Rescaling: scaling factor is zero");
     ZKB_LAUNCH(rescale_kernel, grid_for(n, 256), 256, 0, as_stream(stream), reinterpret_cast<const Fr*>(d_in),
                (long)scaling_factor, reinterpret_cast<Fr*>(d_out), reinterpret_cast<Fr*>(d_rem), n);
+    return ZKB_OK;
+}
+int zkb_relu_decomp(const zkb_fr_t* d_in, uint64_t scaling_factor, zkb_fr_t* d_sign, zkb_fr_t* d_abs, zkb_fr_t* d_rem,
+                    zkb_fr_t* d_res, size_t n, void* stream) {
+    if (!n) return ZKB_OK;
+    if (scaling_factor == 0) return fail(ZKB_ERR_ARG, "zkReLU: scaling factor is zero");
+    ZKB_LAUNCH(relu_decomp_kernel, grid_for(n, 256), 256, 0, as_stream(stream), reinterpret_cast<const Fr*>(d_in),
+               (long)scaling_factor, reinterpret_cast<Fr*>(d_sign), reinterpret_cast<Fr*>(d_abs), reinterpret_cast<Fr*>(d_rem),
+               reinterpret_cast<Fr*>(d_res), n);
     return ZKB_OK;
 }
 int zkb_softmax_table(double theta_k, double scaling_factor_in, double d, double Bk, uint32_t bk, zkb_fr_t* d_table, void* stream) {
