@@ -17,25 +17,27 @@ public:
     using G1TensorJacobian::operator*=;
 
     // t holds t.size / size rows of `size` scalars
-    G1TensorJacobian commit(const FrTensor& t) const;                      // full-width scalars
-    G1TensorJacobian commit_int(const FrTensor& t) const;                  // scalars that encode int32 values
-    G1TensorJacobian commit_int_multi(const vector<FrTensor>& t) const;    // rows of several tensors, concatenated
+    static Commitment random(uint n_generators);
 
-    Fr_t open(const FrTensor& t, const G1TensorJacobian& c, const vector<Fr_t>& u) const;
+    G1TensorJacobian commit_int(const FrTensor& values) const;                    // scalars that encode int32 values
+    G1TensorJacobian commit_int_multi(const vector<FrTensor>& tensors) const;     // rows of several tensors, concatenated
+    G1TensorJacobian commit(const FrTensor& values) const;                        // full-width scalars
 
-    static Commitment random(uint size);
-    static Fr_t me_open(const FrTensor& t, const Commitment& generators, vector<Fr_t>::const_iterator begin,
-                        vector<Fr_t>::const_iterator end, vector<G1Jacobian_t>& proof);
+    // opening of the committed tensor at `point`: rows folded by the high challenges, then me_open
+    Fr_t open(const FrTensor& values, const G1TensorJacobian& row_commitments, const vector<Fr_t>& point) const;
+    static Fr_t me_open(const FrTensor& row, const Commitment& gens, vector<Fr_t>::const_iterator first,
+                        vector<Fr_t>::const_iterator last, vector<G1Jacobian_t>& transcript);
 };
 
+// a committed parameter: generators, padded integer weights, row commitments
 struct Weight {
     Commitment generator;
     FrTensor weight;
     G1TensorJacobian com;
-    uint in_dim;
-    uint out_dim;
+    uint in_dim, out_dim;
 };
 
-Weight create_weight(string generator_filename, string weight_filename, string com_filename, uint in_dim, uint out_dim);
+// reads the three files one parameter has (-pp.bin, -int.bin, -commitment.bin)
+Weight create_weight(string pp_file, string int_file, string commitment_file, uint in_dim, uint out_dim);
 
 #endif

@@ -34,62 +34,66 @@ public:
 class G1TensorAffine;
 class G1TensorJacobian;
 
+// affine points (x, y), Montgomery coordinates
 class G1TensorAffine : public G1Tensor {
 public:
     G1Affine_t* gpu_data;
 
-    G1TensorAffine(const G1TensorAffine&);
-    G1TensorAffine(uint size);
-    G1TensorAffine(uint size, const G1Affine_t&);
-    G1TensorAffine(uint size, const G1Affine_t* cpu_data);
-    G1TensorAffine(const string& filename);
+    G1TensorAffine(uint n);                               // uninitialised
+    G1TensorAffine(uint n, const G1Affine_t& fill);
+    G1TensorAffine(uint n, const G1Affine_t* host_points);
+    G1TensorAffine(const string& path);                   // raw file, 96 bytes per point
+    G1TensorAffine(const G1TensorAffine& src);
     ~G1TensorAffine();
 
-    void save(const string& filename) const;
-    G1Affine_t operator()(uint idx) const;
+    G1Affine_t operator()(uint index) const;
     G1TensorAffine operator-() const;
+    void save(const string& path) const;
 };
 
+// Jacobian points (X, Y, Z), Z = 0 for the identity
 class G1TensorJacobian : public G1Tensor {
 public:
     G1Jacobian_t* gpu_data;
 
-    G1TensorJacobian(const G1TensorJacobian&);
-    G1TensorJacobian(uint size);
-    G1TensorJacobian(uint size, const G1Jacobian_t&);
-    G1TensorJacobian(uint size, const G1Jacobian_t* cpu_data);
-    G1TensorJacobian(const G1TensorAffine& affine_tensor);
-    G1TensorJacobian(const string& filename);
+    G1TensorJacobian(uint n);                             // uninitialised
+    G1TensorJacobian(uint n, const G1Jacobian_t& fill);
+    G1TensorJacobian(uint n, const G1Jacobian_t* host_points);
+    G1TensorJacobian(const string& path);                 // raw file, 144 bytes per point
+    G1TensorJacobian(const G1TensorAffine& src);
+    G1TensorJacobian(const G1TensorJacobian& src);
     ~G1TensorJacobian();
 
-    void save(const string& filename) const;
-    G1Jacobian_t operator()(uint) const;
+    G1Jacobian_t operator()(uint index) const;
+    void save(const string& path) const;
 
+    // elementwise group operations; a single point on the right is applied to every element
     G1TensorJacobian operator-() const;
-    G1TensorJacobian operator+(const G1TensorJacobian&) const;
-    G1TensorJacobian operator+(const G1TensorAffine&) const;
-    G1TensorJacobian operator+(const G1Jacobian_t&) const;
-    G1TensorJacobian operator+(const G1Affine_t&) const;
-    G1TensorJacobian& operator+=(const G1TensorJacobian&);
-    G1TensorJacobian& operator+=(const G1TensorAffine&);
-    G1TensorJacobian& operator+=(const G1Jacobian_t&);
-    G1TensorJacobian& operator+=(const G1Affine_t&);
-    G1TensorJacobian operator-(const G1TensorJacobian&) const;
-    G1TensorJacobian operator-(const G1TensorAffine&) const;
-    G1TensorJacobian operator-(const G1Jacobian_t&) const;
-    G1TensorJacobian operator-(const G1Affine_t&) const;
-    G1TensorJacobian& operator-=(const G1TensorJacobian&);
-    G1TensorJacobian& operator-=(const G1TensorAffine&);
-    G1TensorJacobian& operator-=(const G1Jacobian_t&);
-    G1TensorJacobian& operator-=(const G1Affine_t&);
+    G1TensorJacobian operator+(const G1TensorJacobian& rhs) const;
+    G1TensorJacobian operator-(const G1TensorJacobian& rhs) const;
+    G1TensorJacobian operator+(const G1TensorAffine& rhs) const;
+    G1TensorJacobian operator-(const G1TensorAffine& rhs) const;
+    G1TensorJacobian operator+(const G1Jacobian_t& point) const;
+    G1TensorJacobian operator-(const G1Jacobian_t& point) const;
+    G1TensorJacobian operator+(const G1Affine_t& point) const;
+    G1TensorJacobian operator-(const G1Affine_t& point) const;
+    G1TensorJacobian& operator+=(const G1TensorJacobian& rhs);
+    G1TensorJacobian& operator-=(const G1TensorJacobian& rhs);
+    G1TensorJacobian& operator+=(const G1TensorAffine& rhs);
+    G1TensorJacobian& operator-=(const G1TensorAffine& rhs);
+    G1TensorJacobian& operator+=(const G1Jacobian_t& point);
+    G1TensorJacobian& operator-=(const G1Jacobian_t& point);
+    G1TensorJacobian& operator+=(const G1Affine_t& point);
+    G1TensorJacobian& operator-=(const G1Affine_t& point);
+
+    // out[i] = scalars[i] * (*this)[i mod size]; the scalar tensor may hold several rows
+    G1TensorJacobian operator*(const FrTensor& scalars) const;
+    G1TensorJacobian& operator*=(const FrTensor& scalars);
 
     G1Jacobian_t sum() const;
-    // out[i] = scalars[i] * (*this)[i mod size]; the scalar tensor may hold several rows
-    G1TensorJacobian operator*(const FrTensor&) const;
-    G1TensorJacobian& operator*=(const FrTensor&);
+    G1TensorJacobian rowwise_sum(uint rows, uint cols) const;
     // multilinear extension "in the exponent"
-    G1Jacobian_t operator()(const vector<Fr_t>& u) const;
-    G1TensorJacobian rowwise_sum(uint nrow, uint ncol) const;
+    G1Jacobian_t operator()(const vector<Fr_t>& point) const;
 };
 
 #endif

@@ -5,9 +5,9 @@
 #include <string>
 using namespace std;
 
-// device buffer -> file
-void savebin(const string& filename, const void* gpudata, uint size);
 // file length in bytes
-uint findsize(const string& filename);
-// file -> device buffer
-void loadbin(const string& filename, void* gpudata, uint size);
+uint findsize(const string& path);
+// the first n_bytes of the file -> device buffer
+void loadbin(const string& path, void* device_dst, uint n_bytes);
+// device buffer -> file (created or truncated)
+void savebin(const string& path, const void* device_src, uint n_bytes);

@@ -12,15 +12,18 @@
 
 class Rescaling {
 public:
-    uint scaling_factor;
-    tLookupRange tl_rem;        // remainders lie in [-sf/2, sf/2)
-    Rescaling decomp(const FrTensor& X, FrTensor& rem);
-    FrTensor* rem_tensor_ptr;   // remainders of the last operator() call
-
-    Rescaling(uint scaling_factor);
-    FrTensor operator()(const FrTensor& X);
-    vector<Claim> prove(const FrTensor& X, const FrTensor& X_);
+    Rescaling(uint divisor);
     ~Rescaling();
+
+    uint scaling_factor;        // the divisor
+    tLookupRange tl_rem;        // remainders lie in [-divisor/2, divisor/2)
+    FrTensor* rem_tensor_ptr;   // remainders of the last operator() call (owned)
+
+    // quotient rounded to nearest; keeps the remainders for prove()
+    FrTensor operator()(const FrTensor& values);
+    // values = quotients * divisor + remainders at a random point, and the remainders' range proof
+    vector<Claim> prove(const FrTensor& values, const FrTensor& quotients);
+    Rescaling decomp(const FrTensor& values, FrTensor& remainders);   // declared by the reference, defined nowhere
 };
 
 #endif

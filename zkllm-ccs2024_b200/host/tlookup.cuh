@@ -11,38 +11,39 @@
 class tLookup {
 public:
     FrTensor table;
-    tLookup(const FrTensor& table);
+    tLookup(const FrTensor& table_values);
 
-    // multiplicities of D table indices (a device array of uint)
-    FrTensor prep(const uint* indices, const uint D);
+    // multiplicities of n table indices (a device array of uint)
+    FrTensor prep(const uint* device_indices, const uint n);
 
     // S: looked-up values (D, a power of two, a multiple of the table size), m: multiplicities
-    Fr_t prove(const FrTensor& S, const FrTensor& m, const Fr_t& alpha, const Fr_t& beta, const vector<Fr_t>& u,
-               const vector<Fr_t>& v, vector<Polynomial>& proof);
+    Fr_t prove(const FrTensor& S, const FrTensor& m, const Fr_t& alpha, const Fr_t& beta,
+               const vector<Fr_t>& u, const vector<Fr_t>& v, vector<Polynomial>& transcript);
 };
 
 class tLookupRange : public tLookup {
 public:
     const int low;
-    tLookupRange(int low, uint len);
+    tLookupRange(int first, uint count);            // table = first, first + 1, ..., padded to a power of two
 
-    FrTensor prep(const int* vals, const uint D);   // device ints
-    FrTensor prep(const FrTensor& vals);
     using tLookup::prove;
+    FrTensor prep(const FrTensor& values);
+    FrTensor prep(const int* device_values, const uint n);
 };
 
 class tLookupRangeMapping : public tLookupRange {
 public:
     FrTensor mapped_vals;
-    tLookupRangeMapping(int low, uint len, const FrTensor& mapped_vals);
+    tLookupRangeMapping(int first, uint count, const FrTensor& images);
 
     using tLookupRange::prep;
     // (mapped values, multiplicities)
-    pair<FrTensor, FrTensor> operator()(const int* vals, const uint D);
-    pair<FrTensor, FrTensor> operator()(const FrTensor& mvals);
+    pair<FrTensor, FrTensor> operator()(const FrTensor& values);
+    pair<FrTensor, FrTensor> operator()(const int* device_values, const uint n);
 
-    Fr_t prove(const FrTensor& S_in, const FrTensor& S_out, const FrTensor& m, const Fr_t& r, const Fr_t& alpha, const Fr_t& beta,
-               const vector<Fr_t>& u, const vector<Fr_t>& v, vector<Polynomial>& proof);
+    // lookup of the pairs (S_in, S_out) combined as S_in + r * S_out
+    Fr_t prove(const FrTensor& S_in, const FrTensor& S_out, const FrTensor& m, const Fr_t& r, const Fr_t& alpha,
+               const Fr_t& beta, const vector<Fr_t>& u, const vector<Fr_t>& v, vector<Polynomial>& transcript);
 };
 
 #endif

@@ -13,15 +13,18 @@
 
 class zkReLU {
 public:
-    uint scaling_factor;
-    tLookupRange tl_rem;   // table for the remainder
-    FrTensor decomp(const FrTensor& X, FrTensor& sign, FrTensor& abs, FrTensor& rem);
+    zkReLU(uint divisor);
+    ~zkReLU();
+
+    uint scaling_factor;   // the divisor of the rescaling
+    tLookupRange tl_rem;   // remainders lie in [-divisor/2, divisor/2)
+    // parts of the last operator() call (owned): sign bit, magnitude, remainder, remainder multiplicities
     FrTensor *sign_tensor_ptr, *abs_tensor_ptr, *rem_tensor_ptr, *m_tensor_ptr;
 
-    zkReLU(uint scaling_factor);
-    FrTensor operator()(const FrTensor& X);
-    void prove(const FrTensor& Z, const FrTensor& A);
-    ~zkReLU();
+    // max(round(values / divisor), 0); keeps the parts
+    FrTensor operator()(const FrTensor& values);
+    FrTensor decomp(const FrTensor& values, FrTensor& sign_out, FrTensor& abs_out, FrTensor& rem_out);
+    void prove(const FrTensor& pre_activation, const FrTensor& activation);
 };
 
 #endif
