@@ -169,6 +169,14 @@ int zkb_fr_add_bias(zkb_fr_t* d_z, const zkb_fr_t* d_bias, size_t rows, size_t c
  * The inputs are not modified. */
 int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
              const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* The first `rounds` rounds of zkip (zkfc.cu:94-151) without the verifier replay: no counterpart
+ * in the reference; the building block of the multi-GPU split, where a rank's sums
+ * are only part of each round polynomial.  Round r uses h_u[k - 1 - r].
+ * h_sums receives 3 coefficient sums per round; h_tail_a / h_tail_b receive the two
+ * vectors as folded by the last of these rounds, 2^(ceilLog2(n) - rounds) entries each
+ * (the inputs themselves, n entries, when rounds is 0). */
+int zkb_zkip_partial(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n, const zkb_fr_t* h_u, unsigned k,
+                     unsigned rounds, zkb_fr_t* h_sums, zkb_fr_t* h_tail_a, zkb_fr_t* h_tail_b, void* stream);
 /* Body of zkFC::prove (zkfc.cu:61-87) with the challenge vectors passed in
  * (the reference draws them from random_vec).  X is [B, I], W is [I, O], Y is
  * [B, O].  Outputs: h_polys (3 * ceilLog2(I) coefficients), h_claims[4] =

@@ -291,3 +291,65 @@ def test_block_evaluations_combine_like_the_sharded_path(dev):
                  z._p(0))
         acc = (acc + S.fr_limbs_to_ints(part)[0] * S.block_weight(u_high, rank)) % S.R_MOD
     assert acc == S.fr_limbs_to_ints(whole)[0]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_zkip_equals_the_whole_sumcheck(dev, world):
+    """The multi-GPU split of zkip with the ranks emulated in one process: every rank's round-robin share runs its
+    local rounds on the device (zkb_zkip_partial), sharding.zkip_combine adds the coefficient sums, runs the last
+    log2(world) rounds on the surviving pairs and replays the verifier; polynomials and final claim equal zkb_zkip's."""
+    from zkllm_ccs2024_b200 import sharding as S
+    z = dev.z
+    k = 16
+    n = 1 << k
+    rng = np.random.Generator(np.random.PCG64(world))
+    a, b, u = _rand_fr_limbs(rng, n), _rand_fr_limbs(rng, n), _rand_fr_limbs(rng, k)
+    ai, bi = S.fr_limbs_to_ints(a), S.fr_limbs_to_ints(b)
+    claim = sum(x * y for x, y in zip(ai, bi)) % S.R_MOD
+    polys = np.zeros((3 * k, 8), dtype=np.uint32)
+    final = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_zkip", z._p(S.fr_ints_to_limbs([claim])), z._p(z.DeviceBuffer.from_host(a)), z._p(z.DeviceBuffer.from_host(b)), z.sz(n),
+             z._p(u), z.u32(k), z._p(polys), z._p(final), z._p(0))
+    rounds = S.zkip_local_rounds(n // world)
+    per_rank = []
+    for rank in range(world):
+        la, lb = np.ascontiguousarray(a[rank::world]), np.ascontiguousarray(b[rank::world])
+        sums = np.zeros((3 * rounds, 8), dtype=np.uint32)
+        ta, tb = np.zeros((1, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        dev.call("zkb_zkip_partial", z._p(z.DeviceBuffer.from_host(la)), z._p(z.DeviceBuffer.from_host(lb)), z.sz(n // world), z._p(u),
+                 z.u32(k), z.u32(rounds), z._p(sums), z._p(ta), z._p(tb), z._p(0))
+        v = S.fr_limbs_to_ints(sums)
+        per_rank.append(([v[3 * r:3 * r + 3] for r in range(rounds)], S.fr_limbs_to_ints(ta), S.fr_limbs_to_ints(tb)))
+    got_polys, got_final = S.zkip_combine(per_rank, S.fr_limbs_to_ints(u), claim)
+    want = S.fr_limbs_to_ints(polys)
+    assert got_polys == [want[3 * r:3 * r + 3] for r in range(k)]
+    assert got_final == S.fr_limbs_to_ints(final)[0]
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_sharded_zkfc_prove_equals_the_single_gpu_proof(dev, world):
+    """zkFC::prove's body with W dealt out by rows (and X by the matching columns) over `world` emulated ranks: the
+    proof polynomials and the four claims equal what zkb_zkfc_prove returns for the whole tensors."""
+    from zkllm_ccs2024_b200 import sharding as S
+    z = dev.z
+    B, I, O = 16, 512, 128
+    rng = np.random.Generator(np.random.PCG64(40 + world))
+    X = rng.integers(-3000, 3000, size=(B, I), dtype=np.int64)
+    W = rng.integers(-3000, 3000, size=(I, O), dtype=np.int64)
+    Y = X @ W
+    ub, ui, uo = _rand_fr_limbs(rng, 4), _rand_fr_limbs(rng, 9), _rand_fr_limbs(rng, 7)
+    dX, dW, dY = (z.fr_buffer(_fr_of_ints(t)) for t in (X, W, Y))
+    polys = np.zeros((27, 8), dtype=np.uint32)
+    claims = np.zeros((4, 8), dtype=np.uint32)
+    dev.call("zkb_zkfc_prove", z._p(dX), z._p(dW), z._p(dY), z.sz(B), z.sz(I), z.sz(O), z._p(ub), z._p(ui), z._p(uo), z._p(polys),
+             z._p(claims), z._p(0))
+    parts = []
+    for rank in range(world):
+        dXl = z.fr_buffer(_fr_of_ints(np.ascontiguousarray(X[:, rank::world])))
+        dWl = z.fr_buffer(_fr_of_ints(np.ascontiguousarray(W[rank::world, :])))
+        parts.append(S.zkfc_local_part(z, dXl, dWl, B, I // world, O, ub, ui, uo, world))
+    want_claims = S.fr_limbs_to_ints(claims)
+    got = S.zkfc_combine(parts, want_claims[0], S.fr_limbs_to_ints(ui))
+    want_polys = S.fr_limbs_to_ints(polys)
+    assert got["proof"] == [want_polys[3 * r:3 * r + 3] for r in range(9)]
+    assert [got["claim"], got["final_claim"], got["claim_x"], got["claim_w"]] == want_claims

@@ -41,7 +41,25 @@ def _worker(rank, world, port, m, q):
     u = [rs.randrange(R.R_MOD) for _ in range(6)]
     local = R.mle_eval(t[rank * 32:(rank + 1) * 32], u[:5])
     whole = S.fr_limbs_to_ints(S.sharded_mle_combine(S.fr_ints_to_limbs([local]), u[5:]))[0]
-    q.put((rank, ok_rows and whole == R.mle_eval(t, u), parts, red))
+    ok_mle = whole == R.mle_eval(t, u)
+    # inner-product sumcheck on 64-element vectors dealt out round-robin: local rounds, one exchange, shared last round
+    a = [rs.randrange(R.R_MOD) for _ in range(64)]
+    b = [rs.randrange(R.R_MOD) for _ in range(64)]
+    claim = sum(x * y for x, y in zip(a, b)) % R.R_MOD
+    la, lb, sums = a[rank::world], b[rank::world], []
+    for r in range(S.zkip_local_rounds(len(la))):
+        v, half = u[5 - r], len(la) // 2
+        c = [0, 0, 0]
+        for g in range(half):
+            da, db = la[g + half] - la[g], lb[g + half] - lb[g]
+            c = [c[0] + la[g] * lb[g], c[1] + la[g] * db + lb[g] * da, c[2] + da * db]
+        sums += [x % R.R_MOD for x in c]
+        la = [(la[g] + v * (la[g + half] - la[g])) % R.R_MOD for g in range(half)]
+        lb = [(lb[g] + v * (lb[g + half] - lb[g])) % R.R_MOD for g in range(half)]
+    polys, final = S.sharded_zkip(S.fr_ints_to_limbs(sums), S.fr_ints_to_limbs(la), S.fr_ints_to_limbs(lb), u, claim)
+    proof = []
+    ok_zkip = final == R.zkip(claim, a, b, u, proof) and polys == proof
+    q.put((rank, ok_rows and ok_mle and ok_zkip, parts, red))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -207,13 +207,18 @@ __global__ void __launch_bounds__(1024) zkip_tail_kernel(const Fr* __restrict__ 
     if (threadIdx.x < 3 * rounds) fr_store(out + threadIdx.x, fr_mmul(fr_load(out + threadIdx.x), fe_r2<FrP>()));
 }
 
-// Queues all rounds of zkip on `s`.  d_polys receives 3 Fr per round.  The final
-// folded scalars are not needed by the protocol and are dropped.
-static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h_u, unsigned k,
-                       Fr* d_polys, Scratch& scratch, cudaStream_t s) {
-    if (k == 0) return ZKB_OK;
+// Queues the first `run` of the k rounds of zkip on `s` (round r uses h_u[k - 1 - r]).
+// d_polys receives 3 Fr per round.  fin_a / fin_b (optional) receive device pointers
+// to the arrays as folded by the last round queued (length 2^(ceilLog2(n) - run)); the
+// protocol itself does not need them after its last round.
+static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h_u, unsigned k, unsigned run,
+                       Fr* d_polys, Scratch& scratch, cudaStream_t s, const Fr** fin_a = nullptr, const Fr** fin_b = nullptr) {
+    if (fin_a) *fin_a = d_a;
+    if (fin_b) *fin_b = d_b;
+    if (run == 0) return ZKB_OK;
     const unsigned kn = clog2(n);
     if (k > kn) return fail(ZKB_ERR_DIM, "zkip: more challenges than variables");
+    if (run > k) return fail(ZKB_ERR_ARG, "zkip: more rounds than challenges");
     size_t half = ((size_t)1 << kn) >> 1;
     const Fr* ca = d_a;
     const Fr* cb = d_b;
@@ -231,7 +236,7 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
         unsigned* ticket = scratch.get_n<unsigned>(4);
         if (!partial || !ticket) return ZKB_ERR_CUDA;
         ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
-        for (; r < k && half > kZkipTailHalf; ++r) {
+        for (; r < run && half > kZkipTailHalf; ++r) {
             const Fr v = dev_fr_mont(h_u[k - 1 - r]);
             Fr* oa = buf[r & 1][0];
             Fr* ob = buf[r & 1][1];
@@ -242,8 +247,8 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
             half >>= 1;
         }
     }
-    if (r < k) {
-        const unsigned rounds = k - r;   // at most 12: half <= 2048 here
+    if (r < run) {
+        const unsigned rounds = run - r;   // at most 12: half <= 2048 here
         Challenges vs;
         memset(&vs, 0, sizeof(vs));
         for (unsigned t = 0; t < rounds; ++t) vs.u[t] = dev_fr_mont(h_u[k - 1 - (r + t)]);
@@ -251,7 +256,12 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
         Fr* wb = scratch.get_n<Fr>(2 * half);
         if (!wa || !wb) return ZKB_ERR_CUDA;
         ZKB_LAUNCH(zkip_tail_kernel, 1, 1024, 0, s, ca, cb, n_in, half, vs, rounds, wa, wb, d_polys + 3 * r);
+        // the tail's round t writes to the half of the ping-pong pair with index t & 1
+        ca = wa + ((rounds - 1) & 1) * half;
+        cb = wb + ((rounds - 1) & 1) * half;
     }
+    if (fin_a) *fin_a = ca;
+    if (fin_b) *fin_b = cb;
     return ZKB_OK;
 }
 
@@ -610,10 +620,31 @@ int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, 
     Scratch scratch(s);
     Fr* d_polys = scratch.get_n<Fr>(3 * (size_t)k);
     if (!d_polys) return ZKB_ERR_CUDA;
-    ZKB_TRY(zkip_device(CFR(d_a), CFR(d_b), n, h_u, k, d_polys, scratch, s));
+    ZKB_TRY(zkip_device(CFR(d_a), CFR(d_b), n, h_u, k, k, d_polys, scratch, s));
     ZKB_CUDA(cudaMemcpyAsync(h_polys, d_polys, 96 * (size_t)k, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return zkip_verify(h_claim, h_u, k, h_polys, h_final);
+}
+
+int zkb_zkip_partial(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n, const zkb_fr_t* h_u, unsigned k, unsigned rounds,
+                     zkb_fr_t* h_sums, zkb_fr_t* h_tail_a, zkb_fr_t* h_tail_b, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (n == 0) return fail(ZKB_ERR_DIM, "zkip: empty input");
+    if (rounds > k) return fail(ZKB_ERR_ARG, "zkip: more rounds than challenges");
+    const unsigned kn = clog2(n);
+    if (rounds > kn) return fail(ZKB_ERR_DIM, "zkip: more rounds than variables");
+    Scratch scratch(s);
+    Fr* d_polys = scratch.get_n<Fr>(3 * (size_t)rounds + 1);
+    if (!d_polys) return ZKB_ERR_CUDA;
+    const Fr *fa = nullptr, *fb = nullptr;
+    // the challenge of local round r is h_u[k - 1 - r]: present the k - rounds unused ones as absent variables
+    ZKB_TRY(zkip_device(CFR(d_a), CFR(d_b), n, h_u + (k - rounds), rounds, rounds, d_polys, scratch, s, &fa, &fb));
+    const size_t tail = rounds ? ((size_t)1 << kn) >> rounds : n;
+    if (rounds) ZKB_CUDA(cudaMemcpyAsync(h_sums, d_polys, 96 * (size_t)rounds, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_tail_a, fa, 32 * tail, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_tail_b, fb, 32 * tail, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
 }
 
 int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y,
@@ -647,7 +678,7 @@ int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y
     else ZKB_CUDA(cudaMemcpyAsync(x_red, d_X, I * 32, cudaMemcpyDeviceToDevice, s));
     if (kO) ZKB_TRY(partial_me_device(CFR(d_W), I * O, I, O, 1, h_u_output, kO, w_red, scratch, s));
     else ZKB_CUDA(cudaMemcpyAsync(w_red, d_W, I * 32, cudaMemcpyDeviceToDevice, s));
-    ZKB_TRY(zkip_device(x_red, w_red, I, h_u_input, kI, d_res + 3, scratch, s));
+    ZKB_TRY(zkip_device(x_red, w_red, I, h_u_input, kI, kI, d_res + 3, scratch, s));
     ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, x_red, E_in, I, partial, ticket, d_res + 1, 0u);
     ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, w_red, E_in, I, partial, ticket, d_res + 2, 0u);
     std::vector<zkb_fr_t> res(3 + 3 * (size_t)kI);

@@ -12,7 +12,13 @@ splits without changing any result:
   * a sum of G1 points is gathered and added in rank order;
   * a multilinear evaluation (FrTensor::operator()(u), fr-tensor.cu:437-442) of a
     tensor split into equal contiguous blocks is the sum of the blocks' own
-    evaluations at the low challenges, each weighted by eq(high challenges; rank).
+    evaluations at the low challenges, each weighted by eq(high challenges; rank);
+  * the inner-product sumcheck (zkip, zkfc.cu:94-151) pairs index i with i + N/2, so
+    with the vectors dealt out round-robin (rank p holds i = p, p + P, ...) every
+    round but the last log2 P is local.  All challenges are arguments, so a rank
+    runs all its local rounds back to back (zkb_zkip_partial) and the ranks exchange
+    their coefficient sums and their one surviving pair ONCE; the last log2 P rounds
+    and the verifier replay then run on every rank on P-element vectors.
 
 Everything here runs on the `gloo` backend as well, which is how it is tested
 without GPUs.
@@ -98,3 +104,154 @@ def sharded_mle_combine(local_value: np.ndarray, u_high, group=None) -> np.ndarr
         raise ValueError("world size must be 2^len(u_high)")
     v = fr_limbs_to_ints(local_value)[0]
     return fr_allreduce_sum(fr_ints_to_limbs([v * block_weight(u_high, rank) % R_MOD]), group)
+
+
+def zkip_local_rounds(n_local: int) -> int:
+    """rounds a rank can run alone on its round-robin share of n_local (a power of two) entries"""
+    if n_local < 1 or n_local & (n_local - 1):
+        raise ValueError("the local share must be a power of two long")
+    return n_local.bit_length() - 1
+
+
+def zkip_combine(per_rank, u, claim: int):
+    """per_rank[p] = (sums, tail_a, tail_b) of rank p in integers: `sums` the 3 coefficient sums of each local
+    round, tail_a / tail_b the share as folded by those rounds (one entry each when every local round ran).
+    u: all k challenges (consumed from the back, as zkip does).  Returns (polys, final_claim): the k round
+    polynomials [c0, c1, c2] and the claim after the last round - what zkip on the whole vectors produces.
+    Raises RuntimeError("claim != p(0) + p(1)") like the reference when a round does not verify."""
+    world = len(per_rank)
+    if world < 1 or world & (world - 1):
+        raise ValueError("the number of ranks must be a power of two")
+    n_local_rounds = len(per_rank[0][0])
+    polys = [[sum(pr[0][r][c] for pr in per_rank) % R_MOD for c in range(3)] for r in range(n_local_rounds)]
+    # entry j of rank p is global index j * world + p
+    tail = len(per_rank[0][1])
+    a = [per_rank[i % world][1][i // world] for i in range(tail * world)]
+    b = [per_rank[i % world][2][i // world] for i in range(tail * world)]
+    k = len(u)
+    for r in range(n_local_rounds, k):
+        v = u[k - 1 - r]
+        half = len(a) // 2
+        if half < 1:
+            raise ValueError("more challenges than variables")
+        c0 = c1 = c2 = 0
+        na, nb = [], []
+        for g in range(half):
+            da, db = a[g + half] - a[g], b[g + half] - b[g]
+            c0 += a[g] * b[g]
+            c1 += a[g] * db + b[g] * da
+            c2 += da * db
+            na.append((a[g] + v * da) % R_MOD)
+            nb.append((b[g] + v * db) % R_MOD)
+        polys.append([c0 % R_MOD, c1 % R_MOD, c2 % R_MOD])
+        a, b = na, nb
+    for r, (c0, c1, c2) in enumerate(polys):
+        if claim != (2 * c0 + c1 + c2) % R_MOD:
+            raise RuntimeError("claim != p(0) + p(1)")
+        v = u[k - 1 - r]
+        claim = (c0 + v * (c1 + v * c2)) % R_MOD
+    return polys, claim
+
+
+def sharded_zkip(local_sums: np.ndarray, tail_a: np.ndarray, tail_b: np.ndarray, u, claim: int, group=None):
+    """The exchange step: every rank passes what zkb_zkip_partial returned for its share ((rounds*3, 8),
+    (tail, 8), (tail, 8) uint32) and receives (polys, final_claim) of the whole sumcheck."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    rounds, tail = local_sums.shape[0] // 3, tail_a.shape[0]
+    payload = np.concatenate([np.ascontiguousarray(x, dtype=np.uint32).reshape(-1, 8) for x in (local_sums, tail_a, tail_b)])
+    t = torch.from_numpy(payload.view(np.int32).copy()).to(dev)
+    bufs = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(bufs, t, group=group)
+    per_rank = []
+    for bfr in bufs:
+        vals = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
+        sums = [vals[3 * r:3 * r + 3] for r in range(rounds)]
+        per_rank.append((sums, vals[3 * rounds:3 * rounds + tail], vals[3 * rounds + tail:3 * rounds + 2 * tail]))
+    return zkip_combine(per_rank, u, claim)
+
+
+# ---- zkFC::prove (zkfc.cu:61-87) with the weights split over the ranks -------------------
+# W [I, O] is dealt out by rows round-robin and X [B, I] by the matching columns: rank p
+# holds W[p::P, :] and X[:, p::P]; Y [B, O] is on every rank.  The heavy pass - every
+# entry of W once - is local, and the inner-product sumcheck over I splits as zkip does.
+
+def zkfc_local_part(z, d_X_local, d_W_local, B: int, I_local: int, O: int, u_batch, u_input, u_output, world: int):
+    """One rank's device work through the C ABI (z: the loaded binding).  u_*: (k, 8) uint32 challenge arrays;
+    the first log2(world) entries of u_input belong to the rank index.  Returns host integers:
+    (sums, tail_a, tail_b, X_local(u_batch, u_input_high), W_local(u_input_high, u_output))."""
+    kP = world.bit_length() - 1
+    kI = u_input.shape[0]
+    u_in_high = fr_host_or_dummy(u_input[kP:])
+    x_red, w_red = z.DeviceBuffer(32 * I_local), z.DeviceBuffer(32 * I_local)
+    if u_batch.shape[0]:
+        z.call("zkb_fr_partial_me", z._p(d_X_local), z.sz(B * I_local), z._p(fr_host_or_dummy(u_batch)), z.u32(u_batch.shape[0]),
+               z.sz(B), z.sz(I_local), z._p(x_red), z._p(0))
+    else:
+        z.call("zkb_memcpy_d2d", z._p(x_red), z._p(d_X_local), z.sz(32 * I_local), z._p(0))
+    if u_output.shape[0]:
+        z.call("zkb_fr_partial_me", z._p(d_W_local), z.sz(I_local * O), z._p(fr_host_or_dummy(u_output)), z.u32(u_output.shape[0]),
+               z.sz(O), z.sz(1), z._p(w_red), z._p(0))
+    else:
+        z.call("zkb_memcpy_d2d", z._p(w_red), z._p(d_W_local), z.sz(32 * I_local), z._p(0))
+    rounds = zkip_local_rounds(I_local)
+    sums = np.zeros((max(3 * rounds, 1), 8), dtype=np.uint32)
+    ta, tb = np.zeros((1, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_zkip_partial", z._p(x_red), z._p(w_red), z.sz(I_local), z._p(fr_host_or_dummy(u_input)), z.u32(kI), z.u32(rounds),
+           z._p(sums), z._p(ta), z._p(tb), z._p(0))
+    cx, cw = np.zeros((1, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_fr_mle_eval_2d", z._p(d_X_local), z.sz(B), z.sz(I_local), z._p(fr_host_or_dummy(u_batch)), z.u32(u_batch.shape[0]),
+           z._p(u_in_high), z.u32(kI - kP), z._p(cx), z._p(0))
+    z.call("zkb_fr_mle_eval_2d", z._p(d_W_local), z.sz(I_local), z.sz(O), z._p(u_in_high), z.u32(kI - kP),
+           z._p(fr_host_or_dummy(u_output)), z.u32(u_output.shape[0]), z._p(cw), z._p(0))
+    v = fr_limbs_to_ints(sums)
+    return ([v[3 * r:3 * r + 3] for r in range(rounds)], fr_limbs_to_ints(ta), fr_limbs_to_ints(tb),
+            fr_limbs_to_ints(cx)[0], fr_limbs_to_ints(cw)[0])
+
+
+def fr_host_or_dummy(limbs: np.ndarray) -> np.ndarray:
+    """a valid (k, 8) uint32 array for a challenge vector that may be empty"""
+    a = np.ascontiguousarray(limbs, dtype=np.uint32).reshape(-1, 8)
+    return a if a.shape[0] else np.zeros((1, 8), dtype=np.uint32)
+
+
+def zkfc_combine(parts, claim: int, u_input_ints):
+    """parts[p] = zkfc_local_part of rank p; claim = Y(u_batch, u_output).  Returns the dictionary zkFC::prove's
+    body produces: proof polynomials, final claim, claim_X, claim_W; raises "Claim does not match" like the
+    reference when claim_X * claim_W differs from the final claim."""
+    world = len(parts)
+    kP = world.bit_length() - 1
+    polys, final = zkip_combine([(s_, a_, b_) for s_, a_, b_, _, _ in parts], u_input_ints, claim)
+    u_rank = u_input_ints[:kP]
+    claim_x = sum(block_weight(u_rank, p) * parts[p][3] for p in range(world)) % R_MOD
+    claim_w = sum(block_weight(u_rank, p) * parts[p][4] for p in range(world)) % R_MOD
+    if claim_x * claim_w % R_MOD != final:
+        raise RuntimeError("Claim does not match")
+    return {"proof": polys, "claim": claim, "final_claim": final, "claim_x": claim_x, "claim_w": claim_w}
+
+
+def sharded_zkfc_prove(z, d_X_local, d_W_local, d_Y, B: int, I_local: int, O: int, u_batch, u_input, u_output, group=None):
+    """zkFC::prove's body over torch.distributed: local passes, ONE all-gather of a few hundred bytes, the shared
+    last rounds and the verifier replay on every rank."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    part = zkfc_local_part(z, d_X_local, d_W_local, B, I_local, O, u_batch, u_input, u_output, world)
+    claim = np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_fr_mle_eval_2d", z._p(d_Y), z.sz(B), z.sz(O), z._p(fr_host_or_dummy(u_batch)), z.u32(u_batch.shape[0]),
+           z._p(fr_host_or_dummy(u_output)), z.u32(u_output.shape[0]), z._p(claim), z._p(0))
+    rounds = len(part[0])
+    flat = [c for r_ in part[0] for c in r_] + part[1] + part[2] + [part[3], part[4]]
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    t = torch.from_numpy(fr_ints_to_limbs(flat).view(np.int32).copy()).to(dev)
+    bufs = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(bufs, t, group=group)
+    parts = []
+    for bfr in bufs:
+        v = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
+        parts.append(([v[3 * r:3 * r + 3] for r in range(rounds)], [v[3 * rounds]], [v[3 * rounds + 1]], v[3 * rounds + 2], v[3 * rounds + 3]))
+    return zkfc_combine(parts, fr_limbs_to_ints(claim)[0], fr_limbs_to_ints(u_input))
