@@ -150,11 +150,11 @@ __global__ void __launch_bounds__(kThreads) zkip_round_kernel(const Fr* __restri
     grid_sum_finish<3>(acc, partial, ticket, out, 0x7u, red);
 }
 
-// The last rounds of zkip in ONE launch of one CTA: from kZkipTailHalf pairs down,
+// The last rounds of zkip in ONE launch of one CTA: from kZkipTailHalf pairs down (above that one SM is too slow),
 // a round is a few microseconds of work and a separate launch each would cost
 // more than the arithmetic.  `vs` holds the challenges of these rounds in round
 // order (Montgomery form); wa/wb are two ping-pong buffers of `half` entries each.
-static constexpr size_t kZkipTailHalf = 2048;
+static constexpr size_t kZkipTailHalf = 512;
 __global__ void __launch_bounds__(1024) zkip_tail_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n_in, size_t half,
                                                           Challenges vs, unsigned rounds, Fr* __restrict__ wa, Fr* __restrict__ wb,
                                                           Fr* __restrict__ out) {
@@ -248,7 +248,7 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
         }
     }
     if (r < run) {
-        const unsigned rounds = run - r;   // at most 12: half <= 2048 here
+        const unsigned rounds = run - r;   // at most 10: half <= 512 here
         Challenges vs;
         memset(&vs, 0, sizeof(vs));
         for (unsigned t = 0; t < rounds; ++t) vs.u[t] = dev_fr_mont(h_u[k - 1 - (r + t)]);
@@ -324,6 +324,91 @@ __global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restric
     grid_sum_finish<5>(acc, partial, ticket, out, 0x7u, red);
 }
 
+// One pair (i, i + half) of a phase-2 round: the eq-weighted terms go to q[0..5], the
+// plain ones to acc[6..10]; the five folded values are stored.
+ZKB_DEV void tl_phase2_pair(const Fr* __restrict__ A, const Fr* __restrict__ S, const Fr* __restrict__ Bv, const Fr* __restrict__ T,
+                            const Fr* __restrict__ m, size_t i, size_t half, const Fr& beta, const Fr& v_mont, const Fr& e,
+                            Fr* __restrict__ nA, Fr* __restrict__ nS, Fr* __restrict__ nB, Fr* __restrict__ nT, Fr* __restrict__ nm,
+                            Fr (&q)[6], Fr (&acc)[11]) {
+    {
+        const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
+        const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
+        const Fr c01 = fr_sub(a1, a0), c10 = fr_add(s0, beta), c11 = fr_sub(s1, s0);
+        const Fr e00 = fr_mmul(a0, e), e01 = fr_mmul(c01, e);
+        const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+        const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+        q[0] = fr_add(q[0], t0); q[1] = fr_add(q[1], t1); q[2] = fr_add(q[2], t2);
+        acc[6] = fr_add(acc[6], a0);
+        acc[7] = fr_add(acc[7], c01);
+        fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
+        fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
+    }
+    {
+        const Fr b0 = fr_load(Bv + i), b1 = fr_load(Bv + i + half);
+        const Fr t0_ = fr_load(T + i), t1_ = fr_load(T + i + half);
+        const Fr m0 = fr_load(m + i), m1f = fr_load(m + i + half);
+        const Fr c01 = fr_sub(b1, b0), c10 = fr_add(t0_, beta), c11 = fr_sub(t1_, t0_);
+        const Fr e00 = fr_mmul(b0, e), e01 = fr_mmul(c01, e);
+        const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+        const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+        q[3] = fr_add(q[3], t0); q[4] = fr_add(q[4], t1); q[5] = fr_add(q[5], t2);
+        const Fr m1 = fr_sub(m1f, m0);
+        const Fr d0 = fr_mmul(m0, b0), d2 = fr_mmul(m1, c01);
+        const Fr d1 = fr_sub(fr_sub(fr_mmul(m1f, b1), d0), d2);
+        acc[8] = fr_add(acc[8], d0); acc[9] = fr_add(acc[9], d1); acc[10] = fr_add(acc[10], d2);
+        fr_store(nB + i, fr_add(b0, fr_mmul(v_mont, c01)));
+        fr_store(nT + i, fr_add(t0_, fr_mmul(v_mont, c11)));
+        fr_store(nm + i, fr_add(m0, fr_mmul(v_mont, m1)));
+    }
+}
+
+// The last phase-2 rounds (at most kTlTailHalf pairs) in ONE launch of one CTA of 128
+// threads, like zkip_tail_kernel.  Round t reads `cur`, writes the ping-pong set `nxt[t & 1]`
+// and uses the eq table lo[t] (these rounds have at most 7 variables: no high table).
+static constexpr size_t kTlTailHalf = 128;
+static constexpr unsigned kTlTailRounds = 8;
+struct TlTail {
+    const Fr* cur[5];                 // A, S, B, T, m as the first tail round finds them
+    Fr* nxt[2][5];                    // outputs of even / odd tail rounds
+    const Fr* lo[kTlTailRounds];      // eq tables per round (Montgomery form)
+    Fr v[kTlTailRounds];              // challenges per round (Montgomery form)
+};
+__global__ void __launch_bounds__(128) tl_phase2_tail_kernel(TlTail tt, size_t half, Fr beta, unsigned rounds, Fr* __restrict__ out) {
+    __shared__ Fr stage[11][4];
+    const Fr* in[5];
+#pragma unroll
+    for (int a = 0; a < 5; ++a) in[a] = tt.cur[a];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (unsigned t = 0; t < rounds; ++t) {
+        Fr acc[11], q[6];
+#pragma unroll
+        for (int i = 0; i < 11; ++i) acc[i] = fr_zero();
+#pragma unroll
+        for (int i = 0; i < 6; ++i) q[i] = fr_zero();
+        Fr* const* o = tt.nxt[t & 1];
+        for (size_t i = threadIdx.x; i < half; i += blockDim.x)
+            tl_phase2_pair(in[0], in[1], in[2], in[3], in[4], i, half, beta, tt.v[t], fr_load(tt.lo[t] + i), o[0], o[1], o[2], o[3], o[4],
+                           q, acc);
+#pragma unroll
+        for (int i = 0; i < 6; ++i) acc[i] = q[i];
+#pragma unroll
+        for (int i = 0; i < 11; ++i) {
+            acc[i] = warp_sum(acc[i]);
+            if (lane == 0) stage[i][warp] = acc[i];
+        }
+        __syncthreads();                 // also orders this round's stores before the next round's loads
+        if (threadIdx.x < 11) {
+            Fr v = fr_add(fr_add(stage[threadIdx.x][0], stage[threadIdx.x][1]), fr_add(stage[threadIdx.x][2], stage[threadIdx.x][3]));
+            if ((0x73Fu >> threadIdx.x) & 1u) v = fr_mmul(v, fe_r2<FrP>());   // sums of raw Montgomery products
+            fr_store(out + 11 * (size_t)t + threadIdx.x, v);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int a = 0; a < 5; ++a) in[a] = o[a];
+        half >>= 1;
+    }
+}
+
 // Phase-2 round on (A, S, B, T, m) of size 2*half (tlookup.cu:161-279).
 // sums: [0..2] eq-weighted (A,S) coefficients, [3..5] eq-weighted (B,T)
 // coefficients, [6] sum A0, [7] sum A1, [8..10] coefficients of (m0 + m1 t)(B0 + B1 t).
@@ -349,37 +434,7 @@ __global__ void __launch_bounds__(kThreads) tl_phase2_kernel(const Fr* __restric
         for (size_t jj = threadIdx.x; jj < piece && base + jj < half; jj += blockDim.x) {
             const size_t j = (base + jj) & lmask;
             const size_t i = base + jj;
-            const Fr e = fr_load(eq.lo + j);
-            {
-                const Fr a0 = fr_load(A + i), a1 = fr_load(A + i + half);
-                const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
-                const Fr c01 = fr_sub(a1, a0), c10 = fr_add(s0, beta), c11 = fr_sub(s1, s0);
-                const Fr e00 = fr_mmul(a0, e), e01 = fr_mmul(c01, e);
-                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
-                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
-                q[0] = fr_add(q[0], t0); q[1] = fr_add(q[1], t1); q[2] = fr_add(q[2], t2);
-                acc[6] = fr_add(acc[6], a0);
-                acc[7] = fr_add(acc[7], c01);
-                fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
-                fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
-            }
-            {
-                const Fr b0 = fr_load(Bv + i), b1 = fr_load(Bv + i + half);
-                const Fr t0_ = fr_load(T + i), t1_ = fr_load(T + i + half);
-                const Fr m0 = fr_load(m + i), m1f = fr_load(m + i + half);
-                const Fr c01 = fr_sub(b1, b0), c10 = fr_add(t0_, beta), c11 = fr_sub(t1_, t0_);
-                const Fr e00 = fr_mmul(b0, e), e01 = fr_mmul(c01, e);
-                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
-                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
-                q[3] = fr_add(q[3], t0); q[4] = fr_add(q[4], t1); q[5] = fr_add(q[5], t2);
-                const Fr m1 = fr_sub(m1f, m0);
-                const Fr d0 = fr_mmul(m0, b0), d2 = fr_mmul(m1, c01);
-                const Fr d1 = fr_sub(fr_sub(fr_mmul(m1f, b1), d0), d2);
-                acc[8] = fr_add(acc[8], d0); acc[9] = fr_add(acc[9], d1); acc[10] = fr_add(acc[10], d2);
-                fr_store(nB + i, fr_add(b0, fr_mmul(v_mont, c01)));
-                fr_store(nT + i, fr_add(t0_, fr_mmul(v_mont, c11)));
-                fr_store(nm + i, fr_add(m0, fr_mmul(v_mont, m1)));
-            }
+            tl_phase2_pair(A, S, Bv, T, m, i, half, beta, v_mont, fr_load(eq.lo + j), nA, nS, nB, nT, nm, q, acc);
         }
         if (eq.hi) {
             const Fr eh = fr_load(eq.hi + (base >> eq.kl));
@@ -772,6 +827,25 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
             ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq, R,
                        pp[pb][0], pp[pb][1], partial, ticket, out);
             cA = pp[pb][0]; cS = pp[pb][1];
+        } else if (half <= kTlTailHalf && kD - r <= kTlTailRounds) {
+            // the remaining phase-2 rounds in one launch
+            TlTail tt;
+            memset(&tt, 0, sizeof(tt));
+            const Fr* cur[5] = {cA, cS, cB, cT, cm};
+            const unsigned rounds = kD - r;
+            for (int a = 0; a < 5; ++a) {
+                tt.cur[a] = cur[a];
+                for (int par = 0; par < 2; ++par) {
+                    tt.nxt[par][a] = scratch.get_n<Fr>(half);
+                    if (!tt.nxt[par][a]) return ZKB_ERR_CUDA;
+                }
+            }
+            for (unsigned t = 0; t < rounds; ++t) {
+                tt.lo[t] = tabs[r + t].lo;
+                tt.v[t] = dev_fr_mont(h_v[kD - 1 - (r + t - k1)]);
+            }
+            ZKB_LAUNCH(tl_phase2_tail_kernel, 1, 128, 0, s, tt, half, beta, rounds, out);
+            break;
         } else {
             const Fr v = dev_fr_mont(h_v[kD - 1 - (r - k1)]);
             const int qb = (r - k1) & 1;   // B, T, m start shrinking at the first phase-2 round
