@@ -353,3 +353,45 @@ def test_sharded_zkfc_prove_equals_the_single_gpu_proof(dev, world):
     want_polys = S.fr_limbs_to_ints(polys)
     assert got["proof"] == [want_polys[3 * r:3 * r + 3] for r in range(9)]
     assert [got["claim"], got["final_claim"], got["claim_x"], got["claim_w"]] == want_claims
+
+
+def test_row_folds_of_mixed_tensors_match_the_field_matmul(dev):
+    """FrTensor::partial_me along the last axis of a [2400, 3000] tensor (one warp per part of a row, lazily reduced
+    small-integer products) against an independent path: the field matmul of the tensor with the eq table.  Entries mix
+    small integers of both signs, 64-bit integers, zeros and arbitrary field elements."""
+    z = dev.z
+    rows, J, k = 2400, 3000, 12
+    rng = np.random.Generator(np.random.PCG64(77))
+    vals = rng.integers(-(1 << 20), 1 << 20, size=rows * J, dtype=np.int64)
+    vals[::7] = rng.integers(-(1 << 62), 1 << 62, size=vals[::7].size, dtype=np.int64)
+    vals[::11] = 0
+    t = _fr_of_ints(vals)
+    t[5::13] = _rand_fr_limbs(rng, t[5::13].shape[0])           # not small in either sign
+    u = _rand_fr_limbs(rng, k)
+    uu = R.fr_unpack(u)
+    eq = [1]
+    for x in uu:                                                 # index bit j pairs with challenge j
+        eq = [e * (1 - x) % R.R_MOD for e in eq] + [e * x % R.R_MOD for e in eq]
+    d_t = z.DeviceBuffer.from_host(t)
+    got = z.DeviceBuffer(32 * rows)
+    dev.call("zkb_fr_partial_me", z._p(d_t), z.sz(rows * J), z._p(u), z.u32(k), z.sz(J), z.sz(1), z._p(got), z._p(0))
+    want = z.DeviceBuffer(32 * rows)
+    dev.call("zkb_fr_matmul", z._p(d_t), z._p(z.fr_buffer(R.fr_pack(eq[:J]))), z._p(want), z.sz(rows), z.sz(J), z.sz(1), z._p(0))
+    assert np.array_equal(got.to_host(np.uint32, (rows, 8)), want.to_host(np.uint32, (rows, 8)))
+    # and two rows against exact integer arithmetic
+    tv = R.fr_unpack(t[:2 * J])
+    for r_ in range(2):
+        assert R.fr_unpack(got.to_host(np.uint32, (rows, 8))[r_:r_ + 1])[0] == sum(a * e for a, e in zip(tv[r_ * J:(r_ + 1) * J], eq)) % R.R_MOD
+
+
+def test_mle_eval_of_small_integers(dev):
+    """the lazily reduced dot product inside the multilinear evaluation, on fixed-point values up to 64 bits"""
+    z = dev.z
+    n, k = 5000, 13
+    rng = np.random.Generator(np.random.PCG64(78))
+    vals = rng.integers(-(1 << 63), (1 << 63) - 1, size=n, dtype=np.int64)
+    vals[:8] = [0, 1, -1, (1 << 32) - 1, 1 << 32, -(1 << 32), (1 << 63) - 1, -(1 << 63)]
+    u = _rand_fr_limbs(rng, k)
+    out = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_fr_mle_eval", z._p(z.fr_buffer(_fr_of_ints(vals))), z.sz(n), z._p(u), z.u32(k), z._p(out), z._p(0))
+    assert R.fr_unpack(out)[0] == R.mle_eval([int(v) % R.R_MOD for v in vals], R.fr_unpack(u))
