@@ -204,6 +204,17 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
                       size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                       const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                       zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* The first `rounds` rounds of the same proof without the assembly of the round
+ * polynomials and the verifier replay (tlookup.cu:281-322; no counterpart in the reference:
+ * the building block of the multi-GPU split).  h_sums receives 1 + 11 * rounds values:
+ * sum B*m, then per round [0..2] the eq-weighted (A,S) coefficients, phase 1: [3] sum A0,
+ * [4] sum (A1 - A0); phase 2: [3..5] the eq-weighted (B,T) coefficients, [6] sum A0,
+ * [7] sum (A1 - A0), [8..10] the coefficients of (m0 + m1 t)(B0 + B1 t).  h_tails receives
+ * A, S (D >> rounds entries each) and B, T, m (N >> max(rounds - log2(D/N), 0) each) as the
+ * last of these rounds left them. */
+int zkb_tlookup_partial(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m, size_t D, size_t N,
+                        const zkb_fr_t* h_beta, const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned rounds,
+                        zkb_fr_t* h_sums, zkb_fr_t* h_tails, void* stream);
 /* multi_hadamard_sumchecks (proof.cu:190-241): K tensors of N (a power of two)
  * elements; h_polys receives (K+1) coefficients per round, log2 N rounds. */
 int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,

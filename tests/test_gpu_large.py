@@ -395,3 +395,44 @@ def test_mle_eval_of_small_integers(dev):
     out = np.zeros((1, 8), dtype=np.uint32)
     dev.call("zkb_fr_mle_eval", z._p(z.fr_buffer(_fr_of_ints(vals))), z.sz(n), z._p(u), z.u32(k), z._p(out), z._p(0))
     assert R.fr_unpack(out)[0] == R.mle_eval([int(v) % R.R_MOD for v in vals], R.fr_unpack(u))
+
+
+@pytest.mark.parametrize("world,logD,logN", [(2, 14, 8), (4, 16, 10), (8, 13, 13), (8, 18, 7)])
+def test_sharded_tlookup_equals_the_whole_proof(dev, world, logD, logN):
+    """The multi-GPU split of tLookup::prove with the ranks emulated in one process: values, table and multiplicities dealt
+    out round-robin, every rank's local rounds on the device (zkb_tlookup_partial), sharding.tlookup_combine for the
+    exchange, the shared last rounds and the replay; polynomials and final claim equal zkb_tlookup_prove's."""
+    from zkllm_ccs2024_b200 import sharding as S
+    z = dev.z
+    D, N, low = 1 << logD, 1 << logN, -(1 << (logN - 1))
+    rng = np.random.Generator(np.random.PCG64(world * 1000 + logD))
+    S_int = rng.integers(low, low + N, size=D, dtype=np.int64).astype(np.int32)
+    dS = z.DeviceBuffer(32 * D)
+    dev.call("zkb_fr_from_i32", z._p(z.DeviceBuffer.from_host(S_int)), z._p(dS), z.sz(D), z._p(0))
+    dT, dI, dM = z.DeviceBuffer(32 * N), z.DeviceBuffer(4 * D), z.DeviceBuffer(32 * N)
+    dev.call("zkb_tlookup_range_table", z.i32(low), z.sz(N), z.sz(N), z._p(dT), z._p(0))
+    dev.call("zkb_tlookup_range_indices", z._p(dS), z.i32(low), z._p(dI), z.sz(D), z._p(0))
+    dev.call("zkb_tlookup_prep", z._p(dI), z.sz(D), z.sz(N), z._p(dM), z._p(0))
+    hS, hT, hM = dS.to_host(np.uint32, (D, 8)), dT.to_host(np.uint32, (N, 8)), dM.to_host(np.uint32, (N, 8))
+    alpha, beta, u, v = _rand_fr(rng, 1), _rand_fr(rng, 1), _rand_fr(rng, logD), _rand_fr(rng, logD)
+    polys = np.zeros((4 * logD, 8), dtype=np.uint32)
+    final = np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(dM), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u), z._p(v),
+             z._p(polys), z._p(final), z._p(0))
+    ui, vi = S.fr_limbs_to_ints(u), S.fr_limbs_to_ints(v)
+    ul, vl = S.tlookup_local_challenges(ui, vi, D, N, world)
+    rounds = logD - (world.bit_length() - 1)
+    per_rank = []
+    for rank in range(world):
+        shares = [z.DeviceBuffer.from_host(np.ascontiguousarray(h[rank::world])) for h in (hS, hT, hM)]
+        sums = np.zeros((1 + 11 * rounds, 8), dtype=np.uint32)
+        tails = np.zeros((5, 8), dtype=np.uint32)
+        dev.call("zkb_tlookup_partial", z._p(shares[0]), z._p(shares[1]), z._p(shares[2]), z.sz(D // world), z.sz(N // world), z._p(beta),
+                 z._p(S.fr_host_or_dummy(S.fr_ints_to_limbs(ul))), z._p(S.fr_host_or_dummy(S.fr_ints_to_limbs(vl))), z.u32(rounds),
+                 z._p(sums), z._p(tails), z._p(0))
+        t = S.fr_limbs_to_ints(tails)
+        per_rank.append((S.fr_limbs_to_ints(sums), [t[0]], [t[1]], [t[2]], [t[3]], [t[4]]))
+    got_polys, got_final = S.tlookup_combine(per_rank, D, N, S.fr_limbs_to_ints(alpha)[0], S.fr_limbs_to_ints(beta)[0], ui, vi)
+    want = S.fr_limbs_to_ints(polys)
+    assert got_polys == [want[4 * r:4 * r + 4] for r in range(logD)]
+    assert got_final == S.fr_limbs_to_ints(final)[0]

@@ -772,22 +772,22 @@ int zkb_tlookup_range_table(int32_t low, size_t len, size_t table_size, zkb_fr_t
     return ZKB_OK;
 }
 
-int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
-                      size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
-                      const zkb_fr_t* h_u, const zkb_fr_t* h_v,
-                      zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
-    cudaStream_t s = as_stream(stream);
-    if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
-        return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
+}  // extern "C"
+
+// Queues the first `run` rounds of the lookup sumcheck (tlookup.cu:281-322) on `s`:
+// the inverses A = 1/(S + beta), B = 1/(T + beta), the sum of B * m into d_sums[0] and
+// 11 sums per round into d_sums[1 + 11 r].  fin[0..4] receive device pointers to
+// A, S, B, T, m as folded by the last round queued.
+static int tlookup_rounds_device(const Fr* d_S, const Fr* d_table, const Fr* d_m, size_t D, size_t N, const zkb_fr_t* h_beta,
+                                 const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned run, Fr* d_sums, const Fr* fin[5],
+                                 Scratch& scratch, cudaStream_t s) {
     const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN;
-    if (kD > 32) return fail(ZKB_ERR_LIMIT, "tLookup: D above 2^32");
-    Scratch scratch(s);
     // working arrays: A (D), then ping-pong halves
     Fr* A = scratch.get_n<Fr>(D);
     Fr* Bv = scratch.get_n<Fr>(N);
     if (!A || !Bv) return ZKB_ERR_CUDA;
-    ZKB_TRY(zkb_fr_inv_shifted(d_S, h_beta, reinterpret_cast<zkb_fr_t*>(A), D, stream));
-    ZKB_TRY(zkb_fr_inv_shifted(d_table, h_beta, reinterpret_cast<zkb_fr_t*>(Bv), N, stream));
+    ZKB_TRY(zkb_fr_inv_shifted(reinterpret_cast<const zkb_fr_t*>(d_S), h_beta, reinterpret_cast<zkb_fr_t*>(A), D, s));
+    ZKB_TRY(zkb_fr_inv_shifted(reinterpret_cast<const zkb_fr_t*>(d_table), h_beta, reinterpret_cast<zkb_fr_t*>(Bv), N, s));
     const size_t half0 = D > 1 ? D / 2 : 1;
     Fr* pp[2][5];
     for (int i = 0; i < 2; ++i)
@@ -800,22 +800,20 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
     const unsigned max_grid = (unsigned)sm_count() * 4;
     Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 11);
     unsigned* ticket = scratch.get_n<unsigned>(4);
-    Fr* d_sums = scratch.get_n<Fr>(1 + 11 * (size_t)kD);
-    if (!partial || !ticket || !d_sums) return ZKB_ERR_CUDA;
+    if (!partial || !ticket) return ZKB_ERR_CUDA;
     ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
     // sum B*m
-    ZKB_LAUNCH(fr_dot_kernel, grid_for(N, kThreads, 4), kThreads, 0, s, Bv, CFR(d_m), N, partial, ticket, d_sums, 1u);
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(N, kThreads, 4), kThreads, 0, s, Bv, d_m, N, partial, ticket, d_sums, 1u);
     const Fr beta = dev_fr(hfr::load(*h_beta));
     const Fr* cA = A;
-    const Fr* cS = CFR(d_S);
+    const Fr* cS = d_S;
     const Fr* cB = Bv;
-    const Fr* cT = CFR(d_table);
-    const Fr* cm = CFR(d_m);
+    const Fr* cT = d_table;
+    const Fr* cm = d_m;
     size_t M = D;
-    unsigned nu = kD;   // challenges of u still unbound
     EqTab tabs[33];
     if (kD) ZKB_TRY(make_eq_series(h_u, kD - 1, kD, 0, tabs, scratch, s));
-    for (unsigned r = 0; r < kD; ++r) {
+    for (unsigned r = 0; r < run; ++r) {
         const size_t half = M / 2;
         const EqTab eq = tabs[r];
         unsigned R, grid;
@@ -832,7 +830,7 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
             TlTail tt;
             memset(&tt, 0, sizeof(tt));
             const Fr* cur[5] = {cA, cS, cB, cT, cm};
-            const unsigned rounds = kD - r;
+            const unsigned rounds = run - r;
             for (int a = 0; a < 5; ++a) {
                 tt.cur[a] = cur[a];
                 for (int par = 0; par < 2; ++par) {
@@ -845,6 +843,8 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
                 tt.v[t] = dev_fr_mont(h_v[kD - 1 - (r + t - k1)]);
             }
             ZKB_LAUNCH(tl_phase2_tail_kernel, 1, 128, 0, s, tt, half, beta, rounds, out);
+            const int last = (rounds - 1) & 1;
+            cA = tt.nxt[last][0]; cS = tt.nxt[last][1]; cB = tt.nxt[last][2]; cT = tt.nxt[last][3]; cm = tt.nxt[last][4];
             break;
         } else {
             const Fr v = dev_fr_mont(h_v[kD - 1 - (r - k1)]);
@@ -854,8 +854,54 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
             cA = pp[pb][0]; cS = pp[pb][1]; cB = pp[qb][2]; cT = pp[qb][3]; cm = pp[qb][4];
         }
         M = half;
-        --nu;
     }
+    fin[0] = cA; fin[1] = cS; fin[2] = cB; fin[3] = cT; fin[4] = cm;
+    return ZKB_OK;
+}
+
+extern "C" {
+
+int zkb_tlookup_partial(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m, size_t D, size_t N,
+                        const zkb_fr_t* h_beta, const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned rounds,
+                        zkb_fr_t* h_sums, zkb_fr_t* h_tails, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
+        return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
+    const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN;
+    if (kD > 32) return fail(ZKB_ERR_LIMIT, "tLookup: D above 2^32");
+    if (rounds > kD) return fail(ZKB_ERR_ARG, "tLookup: more rounds than variables");
+    Scratch scratch(s);
+    Fr* d_sums = scratch.get_n<Fr>(1 + 11 * (size_t)rounds);
+    if (!d_sums) return ZKB_ERR_CUDA;
+    const Fr* fin[5];
+    ZKB_TRY(tlookup_rounds_device(CFR(d_S), CFR(d_table), CFR(d_m), D, N, h_beta, h_u, h_v, rounds, d_sums, fin, scratch, s));
+    const size_t nAS = D >> rounds, nBT = rounds > k1 ? N >> (rounds - k1) : N;
+    ZKB_CUDA(cudaMemcpyAsync(h_sums, d_sums, (1 + 11 * (size_t)rounds) * 32, cudaMemcpyDeviceToHost, s));
+    size_t off = 0;
+    for (int a = 0; a < 5; ++a) {
+        const size_t cnt = a < 2 ? nAS : nBT;
+        ZKB_CUDA(cudaMemcpyAsync(h_tails + off, fin[a], cnt * 32, cudaMemcpyDeviceToHost, s));
+        off += cnt;
+    }
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return ZKB_OK;
+}
+
+int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
+                      size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                      const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                      zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
+        return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
+    const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN;
+    if (kD > 32) return fail(ZKB_ERR_LIMIT, "tLookup: D above 2^32");
+    Scratch scratch(s);
+    Fr* d_sums = scratch.get_n<Fr>(1 + 11 * (size_t)kD);
+    if (!d_sums) return ZKB_ERR_CUDA;
+    const Fr* fin[5];
+    ZKB_TRY(tlookup_rounds_device(CFR(d_S), CFR(d_table), CFR(d_m), D, N, h_beta, h_u, h_v, kD, d_sums, fin, scratch, s));
+    unsigned nu = kD;   // challenges of u still unbound
     std::vector<zkb_fr_t> sums(1 + 11 * (size_t)kD);
     ZKB_CUDA(cudaMemcpyAsync(sums.data(), d_sums, sums.size() * 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));

@@ -255,3 +255,146 @@ def sharded_zkfc_prove(z, d_X_local, d_W_local, d_Y, B: int, I_local: int, O: in
         v = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
         parts.append(([v[3 * r:3 * r + 3] for r in range(rounds)], [v[3 * rounds]], [v[3 * rounds + 1]], v[3 * rounds + 2], v[3 * rounds + 3]))
     return zkfc_combine(parts, fr_limbs_to_ints(claim)[0], fr_limbs_to_ints(u_input))
+
+
+# ---- tLookup::prove (tlookup.cu:281-370) split the same way -------------------------------
+# S (D values), the table T and the multiplicities m (N each) are dealt out round-robin; a rank
+# runs its log2(D/P) local rounds (zkb_tlookup_partial) with the challenges of its own index
+# bits: u[log2 P:] for the eq weights, and v without the log2 P entries of the shared last rounds
+# (tlookup_local_challenges).  The eq weight of the rank's own low bits is one constant per rank.
+
+def tlookup_local_challenges(u, v, D: int, N: int, world: int):
+    """(u_local, v_local) to hand to zkb_tlookup_partial on a rank's share; u, v: sequences of the global challenges"""
+    kP = world.bit_length() - 1
+    k1 = (D // N).bit_length() - 1
+    return list(u[kP:]), list(v[:k1]) + list(v[k1 + kP:])
+
+
+def tlookup_combine(per_rank, D: int, N: int, alpha: int, beta: int, u, v):
+    """per_rank[p] = (sums, A, S, B, T, m) of rank p in integers: sums = what zkb_tlookup_partial returned for ALL the
+    rank's local rounds (1 + 11 per round), A..m its surviving entries (one each).  u, v: the global challenges.
+    Returns (polys, final_claim) - the log2(D) round polynomials [c0..c3] and the claim tLookup::prove returns; raises
+    RuntimeError with the reference's message when a round does not verify."""
+    world = len(per_rank)
+    kP = world.bit_length() - 1
+    kD, kN = D.bit_length() - 1, N.bit_length() - 1
+    k1 = kD - kN
+    if world & (world - 1) or kN < kP:
+        raise ValueError("the number of ranks must be a power of two and at most the table size")
+    n_local = kD - kP
+    w = [block_weight(u[:kP], p) for p in range(world)]
+    bm = sum(pr[0][0] for pr in per_rank) % R_MOD
+    rounds = []
+    for r in range(n_local):
+        weighted = 3 if r < k1 else 6
+        row = []
+        for c in range(11):
+            if c < weighted:
+                row.append(sum(w[p] * per_rank[p][0][1 + 11 * r + c] for p in range(world)) % R_MOD)
+            else:
+                row.append(sum(per_rank[p][0][1 + 11 * r + c] for p in range(world)) % R_MOD)
+        rounds.append(row)
+    # the last log2(world) rounds on the surviving entries: entry of rank p is index p
+    arr = [[per_rank[p][1 + a][0] for p in range(world)] for a in range(5)]
+    for r in range(n_local, kD):
+        A, S, B, T, m = arr
+        half = len(A) // 2
+        nbits = half.bit_length() - 1
+        vv = v[kD - 1 - (r - k1)]
+        q = [0] * 11
+        nxt = [[], [], [], [], []]
+        for g in range(half):
+            e = block_weight(u[:nbits], g)
+            a0, a1, s0, s1 = A[g], A[g + half], S[g], S[g + half]
+            c01, c10, c11 = a1 - a0, s0 + beta, s1 - s0
+            q[0] += e * a0 * c10
+            q[1] += e * (a0 * c11 + c01 * c10)
+            q[2] += e * c01 * c11
+            q[6] += a0
+            q[7] += c01
+            nxt[0].append((a0 + vv * c01) % R_MOD)
+            nxt[1].append((s0 + vv * c11) % R_MOD)
+            b0, b1, t0, t1, m0, m1f = B[g], B[g + half], T[g], T[g + half], m[g], m[g + half]
+            d01, d10, d11 = b1 - b0, t0 + beta, t1 - t0
+            q[3] += e * b0 * d10
+            q[4] += e * (b0 * d11 + d01 * d10)
+            q[5] += e * d01 * d11
+            m1 = m1f - m0
+            q[8] += m0 * b0
+            q[9] += m0 * d01 + m1 * b0
+            q[10] += m1 * d01
+            nxt[2].append((b0 + vv * d01) % R_MOD)
+            nxt[3].append((t0 + vv * d11) % R_MOD)
+            nxt[4].append((m0 + vv * m1) % R_MOD)
+        rounds.append([x % R_MOD for x in q])
+        arr = nxt
+    # assembly of the round polynomials and the verifier replay, as the single-GPU prover does on the host
+    inv = lambda x: pow(x, R_MOD - 2, R_MOD)
+    two_inv = inv(2)
+    al, al_sq = alpha, alpha * alpha % R_MOD
+    C = (al_sq - bm) % R_MOD
+    claim = (alpha + al_sq) % R_MOD
+    inv_ratio = N * inv(D) % R_MOD
+    polys = []
+    for r, q in enumerate(rounds):
+        ub = u[kD - 1 - r]
+        e0, e1 = (1 - ub) % R_MOD, (2 * ub - 1) % R_MOD
+        if r < k1:
+            p0 = [al * q[i] % R_MOD for i in range(3)]
+            vb = v[k1 - 1 - r]
+        else:
+            coef_b = inv_ratio * al_sq % R_MOD
+            p0 = [(al * q[i] + coef_b * q[3 + i]) % R_MOD for i in range(3)]
+            vb = v[kD - 1 - (r - k1)]
+        p = [p0[0] * e0, p0[1] * e0 + p0[0] * e1, p0[2] * e0 + p0[1] * e1, p0[2] * e1]
+        if r < k1:
+            p[0] += q[3] + C * two_inv
+            p[1] += q[4]
+        else:
+            p[0] += q[6] - q[8] * inv_ratio
+            p[1] += q[7] - q[9] * inv_ratio
+            p[2] -= q[10] * inv_ratio
+        p = [x % R_MOD for x in p]
+        polys.append(p)
+        if claim != (2 * p[0] + p[1] + p[2] + p[3]) % R_MOD:
+            raise RuntimeError("tLookup_phase1: claim != p(0) + p(1)" if r < k1 else "tLookup_phase2: claim != p(0) + p(1)")
+        claim = (p[0] + vb * (p[1] + vb * (p[2] + vb * p[3]))) % R_MOD
+        e = (ub * vb + (1 - ub) * (1 - vb)) % R_MOD
+        al = al * e % R_MOD
+        if r < k1:
+            C = C * two_inv % R_MOD
+        else:
+            al_sq = al_sq * e % R_MOD
+    return polys, claim
+
+
+def sharded_tlookup_prove(z, d_S_local, d_T_local, d_m_local, D: int, N: int, alpha: np.ndarray, beta: np.ndarray,
+                          u: np.ndarray, v: np.ndarray, group=None):
+    """tLookup::prove over torch.distributed: rank p holds S[p::P], T[p::P], m[p::P] on its GPU (device buffers of the
+    binding z); alpha, beta: (1, 8) uint32; u, v: (log2 D, 8) uint32, the global challenges.  Local rounds through
+    zkb_tlookup_partial, ONE all-gather, then tlookup_combine on every rank.  Returns (polys, final_claim)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    kP = world.bit_length() - 1
+    kD = D.bit_length() - 1
+    ui, vi = fr_limbs_to_ints(u), fr_limbs_to_ints(v)
+    ul, vl = tlookup_local_challenges(ui, vi, D, N, world)
+    rounds = kD - kP
+    sums = np.zeros((1 + 11 * rounds, 8), dtype=np.uint32)
+    tails = np.zeros((5, 8), dtype=np.uint32)
+    z.call("zkb_tlookup_partial", z._p(d_S_local), z._p(d_T_local), z._p(d_m_local), z.sz(D // world), z.sz(N // world),
+           z._p(np.ascontiguousarray(beta, dtype=np.uint32)), z._p(fr_host_or_dummy(fr_ints_to_limbs(ul))),
+           z._p(fr_host_or_dummy(fr_ints_to_limbs(vl))), z.u32(rounds), z._p(sums), z._p(tails), z._p(0))
+    payload = np.concatenate([sums, tails])
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    t = torch.from_numpy(payload.view(np.int32).copy()).to(dev)
+    bufs = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(bufs, t, group=group)
+    per_rank = []
+    for bfr in bufs:
+        vals = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
+        n_s = 1 + 11 * rounds
+        per_rank.append((vals[:n_s], [vals[n_s]], [vals[n_s + 1]], [vals[n_s + 2]], [vals[n_s + 3]], [vals[n_s + 4]]))
+    return tlookup_combine(per_rank, D, N, fr_limbs_to_ints(alpha)[0], fr_limbs_to_ints(beta)[0], ui, vi)
