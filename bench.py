@@ -229,7 +229,7 @@ def sumcheck_sharded(z, torch, dist, world: int, rank: int, steps: int) -> dict:
     t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     out["tlookup_prove"] = {"workload": f"tLookup prove (multiplicities given), 2^23 values in a 2^16 table dealt out over {world} GPUs",
-                            "seconds": float(t.item()), "final_claim": S.fr_ints_to_limbs([fin]).tobytes().hex()}
+                            "seconds": float(t.item()), "final_claim": np.ascontiguousarray(fin, dtype=np.uint32).tobytes().hex()}
     return out
 
 

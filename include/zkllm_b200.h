@@ -215,6 +215,21 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
 int zkb_tlookup_partial(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m, size_t D, size_t N,
                         const zkb_fr_t* h_beta, const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned rounds,
                         zkb_fr_t* h_sums, zkb_fr_t* h_tails, void* stream);
+/* The exchange step of the multi-GPU split (no counterpart in the reference; zkfc.cu:140-151 and
+ * tlookup.cu:281-322 are the checks replayed here).  The vectors are dealt out round-robin, rank p
+ * holding the indices p, p + world, ...; every rank has run all its local rounds and h_parts holds
+ * the `world` gathered blocks in rank order.  Pure host arithmetic.
+ * zkip: block = 3 * (k - log2 world) coefficient sums, then the rank's surviving pair (a, b);
+ *   h_polys receives 3 * k coefficients.
+ * tLookup: block = the 1 + 11 * (log2 D - log2 world) sums of zkb_tlookup_partial, then the rank's
+ *   surviving A, S, B, T, m; h_u, h_v are the challenges of the whole proof; h_polys receives
+ *   4 * log2 D coefficients.  Both return ZKB_ERR_VERIFY with the reference's message when a round
+ *   does not verify. */
+int zkb_zkip_combine(const zkb_fr_t* h_parts, unsigned world, unsigned k, const zkb_fr_t* h_u, const zkb_fr_t* h_claim,
+                     zkb_fr_t* h_polys, zkb_fr_t* h_final);
+int zkb_tlookup_combine(const zkb_fr_t* h_parts, unsigned world, size_t D, size_t N, const zkb_fr_t* h_alpha,
+                        const zkb_fr_t* h_beta, const zkb_fr_t* h_u, const zkb_fr_t* h_v, zkb_fr_t* h_polys,
+                        zkb_fr_t* h_final);
 /* multi_hadamard_sumchecks (proof.cu:190-241): K tensors of N (a power of two)
  * elements; h_polys receives (K+1) coefficients per round, log2 N rounds. */
 int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,

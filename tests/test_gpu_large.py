@@ -436,3 +436,11 @@ def test_sharded_tlookup_equals_the_whole_proof(dev, world, logD, logN):
     want = S.fr_limbs_to_ints(polys)
     assert got_polys == [want[4 * r:4 * r + 4] for r in range(logD)]
     assert got_final == S.fr_limbs_to_ints(final)[0]
+    # the C++ twin of the combine on the same gathered blocks
+    flat = []
+    for sums_p, a_, s_, b_, t_, m_ in per_rank:
+        flat += sums_p + a_ + s_ + b_ + t_ + m_
+    cpolys, cfinal = np.zeros((4 * logD, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_tlookup_combine", z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u),
+             z._p(v), z._p(cpolys), z._p(cfinal))
+    assert np.array_equal(cpolys, polys) and np.array_equal(cfinal, final)

@@ -96,3 +96,44 @@ def test_row_shard_covers_everything():
             assert spans[0][0] == 0 and spans[-1][1] == m
             assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
             assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
+
+
+def test_cpp_zkip_combine_matches_the_python_one():
+    """zkb_zkip_combine is pure host arithmetic: it runs without a GPU and must agree with sharding.zkip_combine"""
+    from tests.conftest import load_package
+    z = load_package()
+    from zkllm_ccs2024_b200 import sharding as S
+    from oracle import pyref as R
+    rng = random.Random(9)
+    for n, world in ((64, 2), (64, 4), (32, 8), (16, 1)):
+        k = n.bit_length() - 1
+        a = [rng.randrange(R.R_MOD) for _ in range(n)]
+        b = [rng.randrange(R.R_MOD) for _ in range(n)]
+        u = [rng.randrange(R.R_MOD) for _ in range(k)]
+        claim = sum(x * y for x, y in zip(a, b)) % R.R_MOD
+        per_rank, flat = [], []
+        for p in range(world):
+            la, lb, sums = a[p::world], b[p::world], []
+            for r in range(S.zkip_local_rounds(len(la))):
+                v, half = u[k - 1 - r], len(la) // 2
+                c = [0, 0, 0]
+                for g in range(half):
+                    da, db = la[g + half] - la[g], lb[g + half] - lb[g]
+                    c = [c[0] + la[g] * lb[g], c[1] + la[g] * db + lb[g] * da, c[2] + da * db]
+                sums.append([x % R.R_MOD for x in c])
+                la = [(la[g] + v * (la[g + half] - la[g])) % R.R_MOD for g in range(half)]
+                lb = [(lb[g] + v * (lb[g + half] - lb[g])) % R.R_MOD for g in range(half)]
+            per_rank.append((sums, la, lb))
+            flat += [c for row in sums for c in row] + la + lb
+        want_polys, want_final = S.zkip_combine(per_rank, u, claim)
+        polys, final = np.zeros((3 * k, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        z.call("zkb_zkip_combine", z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.u32(k), z._p(S.fr_ints_to_limbs(u)),
+               z._p(S.fr_ints_to_limbs([claim])), z._p(polys), z._p(final))
+        got = S.fr_limbs_to_ints(polys)
+        assert [got[3 * r:3 * r + 3] for r in range(k)] == want_polys
+        assert S.fr_limbs_to_ints(final)[0] == want_final
+        # a wrong claim is refused with the reference's message
+        with pytest.raises(z.ZkbError) as e:
+            z.call("zkb_zkip_combine", z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.u32(k), z._p(S.fr_ints_to_limbs(u)),
+                   z._p(S.fr_ints_to_limbs([claim + 1])), z._p(polys), z._p(final))
+        assert "claim != p(0) + p(1)" in str(e.value)

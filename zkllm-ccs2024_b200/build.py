@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "build"
 LIB = HERE / "lib" / "libzkllm_b200.so"
-SOURCES = ["common.cu", "fr_ops.cu", "sumcheck.cu", "g1_ops.cu", "msm.cu", "nn_ops.cu", "bench_kernels.cu", "hostapi.cu"]
+SOURCES = ["common.cu", "fr_ops.cu", "sumcheck.cu", "combine.cu", "g1_ops.cu", "msm.cu", "nn_ops.cu", "bench_kernels.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

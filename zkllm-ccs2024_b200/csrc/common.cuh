@@ -80,4 +80,9 @@ private:
 
 inline unsigned div_up(size_t a, size_t b) { return (unsigned)((a + b - 1) / b); }
 
+// Host: round polynomials of the lookup sumcheck from its per-round sums, with the
+// reference's checks (defined in combine.cu; used by the single- and the multi-GPU prover).
+int tlookup_assemble(const zkb_fr_t* sums, size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_u,
+                     const zkb_fr_t* h_v, zkb_fr_t* h_polys, zkb_fr_t* h_final);
+
 }  // namespace zkb

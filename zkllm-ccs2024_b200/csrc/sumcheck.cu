@@ -901,63 +901,12 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
     if (!d_sums) return ZKB_ERR_CUDA;
     const Fr* fin[5];
     ZKB_TRY(tlookup_rounds_device(CFR(d_S), CFR(d_table), CFR(d_m), D, N, h_beta, h_u, h_v, kD, d_sums, fin, scratch, s));
-    unsigned nu = kD;   // challenges of u still unbound
     std::vector<zkb_fr_t> sums(1 + 11 * (size_t)kD);
     ZKB_CUDA(cudaMemcpyAsync(sums.data(), d_sums, sums.size() * 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
 
-    // ---- host: assemble the round polynomials and replay the checks -------------
-    using hfr::H;
-    const H alpha0 = hfr::load(*h_alpha);
-    const H two_inv = hfr::inv(hfr::from_u64(2));
-    H alpha = alpha0;
-    H alpha_sq = hfr::mul(alpha0, alpha0);
-    H C = hfr::sub(alpha_sq, hfr::load(sums[0]));
-    H claim = hfr::add(alpha0, alpha_sq);
-    const H inv_ratio = hfr::mul(hfr::from_u64(N), hfr::inv(hfr::from_u64(D)));
-    nu = kD;
-    for (unsigned r = 0; r < kD; ++r) {
-        const zkb_fr_t* q = &sums[1 + 11 * (size_t)r];
-        const H ub = hfr::load(h_u[nu - 1]);
-        const H e0 = hfr::sub(hfr::from_u64(1), ub);                 // eq(u)(t) = e0 + e1 t
-        const H e1 = hfr::sub(hfr::add(ub, ub), hfr::from_u64(1));
-        H p0[3], p[4];
-        H vb;
-        if (r < k1) {
-            for (int i = 0; i < 3; ++i) p0[i] = hfr::mul(alpha, hfr::load(q[i]));
-            vb = hfr::load(h_v[k1 - 1 - r]);
-        } else {
-            const H coefB = hfr::mul(inv_ratio, alpha_sq);
-            for (int i = 0; i < 3; ++i)
-                p0[i] = hfr::add(hfr::mul(alpha, hfr::load(q[i])), hfr::mul(coefB, hfr::load(q[3 + i])));
-            vb = hfr::load(h_v[kD - 1 - (r - k1)]);
-        }
-        // p0 * eq
-        p[0] = hfr::mul(p0[0], e0);
-        p[1] = hfr::add(hfr::mul(p0[1], e0), hfr::mul(p0[0], e1));
-        p[2] = hfr::add(hfr::mul(p0[2], e0), hfr::mul(p0[1], e1));
-        p[3] = hfr::mul(p0[2], e1);
-        if (r < k1) {
-            p[0] = hfr::add(hfr::add(p[0], hfr::load(q[3])), hfr::mul(C, two_inv));
-            p[1] = hfr::add(p[1], hfr::load(q[4]));
-        } else {
-            p[0] = hfr::sub(hfr::add(p[0], hfr::load(q[6])), hfr::mul(hfr::load(q[8]), inv_ratio));
-            p[1] = hfr::sub(hfr::add(p[1], hfr::load(q[7])), hfr::mul(hfr::load(q[9]), inv_ratio));
-            p[2] = hfr::sub(p[2], hfr::mul(hfr::load(q[10]), inv_ratio));
-        }
-        for (int i = 0; i < 4; ++i) h_polys[4 * (size_t)r + i] = hfr::store(p[i]);
-        const H at1 = hfr::add(hfr::add(p[0], p[1]), hfr::add(p[2], p[3]));
-        if (!hfr::eq(claim, hfr::add(p[0], at1)))
-            return fail(ZKB_ERR_VERIFY, r < k1 ? "tLookup_phase1: claim != p(0) + p(1)" : "tLookup_phase2: claim != p(0) + p(1)");
-        claim = hfr::poly_eval(p, 4, vb);
-        const H e = hfr::eq_eval(ub, vb);
-        alpha = hfr::mul(alpha, e);
-        if (r < k1) C = hfr::mul(C, two_inv);
-        else alpha_sq = hfr::mul(alpha_sq, e);
-        --nu;
-    }
-    *h_final = hfr::store(claim);
-    return ZKB_OK;
+    // host: assemble the round polynomials and replay the checks
+    return tlookup_assemble(sums.data(), D, N, h_alpha, h_u, h_v, h_polys, h_final);
 }
 
 int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,

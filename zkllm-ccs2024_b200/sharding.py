@@ -235,11 +235,13 @@ def zkfc_combine(parts, claim: int, u_input_ints):
 
 def sharded_zkfc_prove(z, d_X_local, d_W_local, d_Y, B: int, I_local: int, O: int, u_batch, u_input, u_output, group=None):
     """zkFC::prove's body over torch.distributed: local passes, ONE all-gather of a few hundred bytes, the shared
-    last rounds and the verifier replay on every rank."""
+    last rounds and the verifier replay on every rank (zkb_zkip_combine, the C++ twin of zkip_combine).  Returns the
+    dictionary of zkfc_combine with the proof as a (3 k, 8) uint32 array."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
+    kP = world.bit_length() - 1
     part = zkfc_local_part(z, d_X_local, d_W_local, B, I_local, O, u_batch, u_input, u_output, world)
     claim = np.zeros((1, 8), dtype=np.uint32)
     z.call("zkb_fr_mle_eval_2d", z._p(d_Y), z.sz(B), z.sz(O), z._p(fr_host_or_dummy(u_batch)), z.u32(u_batch.shape[0]),
@@ -250,11 +252,20 @@ def sharded_zkfc_prove(z, d_X_local, d_W_local, d_Y, B: int, I_local: int, O: in
     t = torch.from_numpy(fr_ints_to_limbs(flat).view(np.int32).copy()).to(dev)
     bufs = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(bufs, t, group=group)
-    parts = []
-    for bfr in bufs:
-        v = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
-        parts.append(([v[3 * r:3 * r + 3] for r in range(rounds)], [v[3 * rounds]], [v[3 * rounds + 1]], v[3 * rounds + 2], v[3 * rounds + 3]))
-    return zkfc_combine(parts, fr_limbs_to_ints(claim)[0], fr_limbs_to_ints(u_input))
+    allp = torch.stack(bufs).cpu().numpy().view(np.uint32).reshape(world, 3 * rounds + 4, 8)
+    k = u_input.shape[0]
+    polys, final = np.zeros((max(3 * k, 1), 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_zkip_combine", z._p(np.ascontiguousarray(allp[:, :3 * rounds + 2])), z.u32(world), z.u32(k),
+           z._p(fr_host_or_dummy(u_input)), z._p(claim), z._p(polys), z._p(final))
+    u_rank = fr_limbs_to_ints(u_input[:kP])
+    cx = fr_limbs_to_ints(np.ascontiguousarray(allp[:, 3 * rounds + 2]))
+    cw = fr_limbs_to_ints(np.ascontiguousarray(allp[:, 3 * rounds + 3]))
+    claim_x = sum(block_weight(u_rank, p) * cx[p] for p in range(world)) % R_MOD
+    claim_w = sum(block_weight(u_rank, p) * cw[p] for p in range(world)) % R_MOD
+    fin = fr_limbs_to_ints(final)[0]
+    if claim_x * claim_w % R_MOD != fin:
+        raise RuntimeError("Claim does not match")
+    return {"proof": polys[:3 * k], "claim": fr_limbs_to_ints(claim)[0], "final_claim": fin, "claim_x": claim_x, "claim_w": claim_w}
 
 
 # ---- tLookup::prove (tlookup.cu:281-370) split the same way -------------------------------
@@ -372,29 +383,31 @@ def sharded_tlookup_prove(z, d_S_local, d_T_local, d_m_local, D: int, N: int, al
                           u: np.ndarray, v: np.ndarray, group=None):
     """tLookup::prove over torch.distributed: rank p holds S[p::P], T[p::P], m[p::P] on its GPU (device buffers of the
     binding z); alpha, beta: (1, 8) uint32; u, v: (log2 D, 8) uint32, the global challenges.  Local rounds through
-    zkb_tlookup_partial, ONE all-gather, then tlookup_combine on every rank.  Returns (polys, final_claim)."""
+    zkb_tlookup_partial, ONE all-gather, then zkb_tlookup_combine (the C++ twin of tlookup_combine) on every rank.
+    Returns (polys, final_claim) as (4 log2 D, 8) and (1, 8) uint32 arrays; raises z.ZkbError when a round fails."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     kP = world.bit_length() - 1
     kD = D.bit_length() - 1
-    ui, vi = fr_limbs_to_ints(u), fr_limbs_to_ints(v)
-    ul, vl = tlookup_local_challenges(ui, vi, D, N, world)
+    k1 = (D // N).bit_length() - 1
+    u = np.ascontiguousarray(u, dtype=np.uint32).reshape(-1, 8)
+    v = np.ascontiguousarray(v, dtype=np.uint32).reshape(-1, 8)
+    ul = fr_host_or_dummy(u[kP:])
+    vl = fr_host_or_dummy(np.concatenate([v[:k1], v[k1 + kP:]]))
     rounds = kD - kP
-    sums = np.zeros((1 + 11 * rounds, 8), dtype=np.uint32)
-    tails = np.zeros((5, 8), dtype=np.uint32)
+    part = np.zeros((1 + 11 * rounds + 5, 8), dtype=np.uint32)
     z.call("zkb_tlookup_partial", z._p(d_S_local), z._p(d_T_local), z._p(d_m_local), z.sz(D // world), z.sz(N // world),
-           z._p(np.ascontiguousarray(beta, dtype=np.uint32)), z._p(fr_host_or_dummy(fr_ints_to_limbs(ul))),
-           z._p(fr_host_or_dummy(fr_ints_to_limbs(vl))), z.u32(rounds), z._p(sums), z._p(tails), z._p(0))
-    payload = np.concatenate([sums, tails])
+           z._p(np.ascontiguousarray(beta, dtype=np.uint32)), z._p(ul), z._p(vl), z.u32(rounds), z._p(part),
+           z._p(part[1 + 11 * rounds:]), z._p(0))
     dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
-    t = torch.from_numpy(payload.view(np.int32).copy()).to(dev)
+    t = torch.from_numpy(part.view(np.int32)).to(dev)
     bufs = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(bufs, t, group=group)
-    per_rank = []
-    for bfr in bufs:
-        vals = fr_limbs_to_ints(bfr.cpu().numpy().view(np.uint32).reshape(-1, 8))
-        n_s = 1 + 11 * rounds
-        per_rank.append((vals[:n_s], [vals[n_s]], [vals[n_s + 1]], [vals[n_s + 2]], [vals[n_s + 3]], [vals[n_s + 4]]))
-    return tlookup_combine(per_rank, D, N, fr_limbs_to_ints(alpha)[0], fr_limbs_to_ints(beta)[0], ui, vi)
+    parts = np.ascontiguousarray(torch.stack(bufs).cpu().numpy().view(np.uint32))
+    polys, final = np.zeros((4 * kD, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_tlookup_combine", z._p(parts), z.u32(world), z.sz(D), z.sz(N), z._p(np.ascontiguousarray(alpha, dtype=np.uint32)),
+           z._p(np.ascontiguousarray(beta, dtype=np.uint32)), z._p(fr_host_or_dummy(u)), z._p(fr_host_or_dummy(v)), z._p(polys),
+           z._p(final))
+    return polys, final
