@@ -58,15 +58,26 @@ class ClockSampler(threading.Thread):
     def run(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-        while not self.stop_flag.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([t.strip() for t in out.split(",")])
-            except Exception:
-                pass
-            self.stop_flag.wait(0.2)
+        # one nvidia-smi process that prints a line every 100 ms (starting one per sample costs ~0.3 s each)
+        try:
+            proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            return
+        self.proc = proc
+        for line in proc.stdout:
+            if line.strip():
+                self.rows.append([t.strip() for t in line.strip().split(",")])
+            if self.stop_flag.is_set():
+                break
+        proc.terminate()
+
+    def stop(self):
+        self.stop_flag.set()
+        proc = getattr(self, "proc", None)
+        if proc is not None:
+            proc.terminate()      # the process this sampler started, by its own handle
+        self.join(timeout=5)
 
     def summary(self) -> dict:
         sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
@@ -348,8 +359,7 @@ def run_ours(args) -> dict:
     z.call("zkb_profile_enable", ctypes.c_int(0))
     buf = ctypes.create_string_buffer(1 << 16)
     z.call("zkb_profile_read", buf, z.sz(len(buf)))
-    sampler.stop_flag.set()
-    sampler.join()
+    sampler.stop()
     kernels = {}
     for line in buf.value.decode().splitlines():
         name, cnt, ms = line.rsplit(",", 2)
