@@ -444,3 +444,23 @@ def test_sharded_tlookup_equals_the_whole_proof(dev, world, logD, logN):
     dev.call("zkb_tlookup_combine", z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u),
              z._p(v), z._p(cpolys), z._p(cfinal))
     assert np.array_equal(cpolys, polys) and np.array_equal(cfinal, final)
+
+
+def test_host_buffer_commitment_equals_the_device_path(dev):
+    """zkb_commit_i32_host on a 1030 x 16384 matrix with 31-bit entries in some rows (five windows) against
+    zkb_commit_i32 on device buffers, and three rows against the C++ oracle."""
+    z = dev.z
+    m, n = 1030, 16384
+    d_g, h_g = gpu_generators(dev, n, 4242)
+    rng = np.random.Generator(np.random.PCG64(31))
+    sc = rng.integers(-8000, 8000, size=(m, n), dtype=np.int64).astype(np.int32)
+    sc[300:520] = rng.integers(-(1 << 30), 1 << 30, size=(220, n), dtype=np.int64).astype(np.int32)
+    sc[m - 1] = 0
+    h_out = np.zeros((m, 36), dtype=np.uint32)
+    dev.call("zkb_commit_i32_host", z._p(h_g), z.sz(n), z._p(sc.reshape(-1)), z.sz(m * n), z._p(h_out), z._p(0))
+    d_out = z.DeviceBuffer(144 * m)
+    dev.call("zkb_commit_i32", z._p(d_g), z.sz(n), z._p(z.DeviceBuffer.from_host(sc.reshape(-1))), z.sz(m * n), z._p(d_out), z._p(0))
+    assert np.array_equal(C.g1_normalise(h_out), normalised(dev, d_out, m))
+    rows = [0, 400, m - 1]
+    exp = C.commit_int(h_g, np.ascontiguousarray(sc[rows]).reshape(-1), "pippenger")
+    assert np.array_equal(C.g1_normalise(np.ascontiguousarray(h_out[rows])), C.g1_normalise(exp))
