@@ -298,6 +298,17 @@ int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scala
  * 8x larger Fr encoding. */
 int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
                    zkb_g1_t* d_out, void* stream);
+/* Same call with the algorithm prescribed instead of chosen by the library's cost estimate
+ * (commitment.cu:31-58 has one algorithm; both of these return the same group elements):
+ * ZKB_MSM_BUCKETS - bucket method, signed 7-bit windows, best for few rows or many generators;
+ * ZKB_MSM_TABLES  - per-call tables of all digit combinations of four generators, signed 3-bit
+ *                   windows, best for many rows over one generator set (96 bytes * 1024 per
+ *                   generator of scratch memory). */
+#define ZKB_MSM_AUTO 0
+#define ZKB_MSM_BUCKETS 1
+#define ZKB_MSM_TABLES 2
+int zkb_commit_i32_method(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
+                          zkb_g1_t* d_out, int method, void* stream);
 /* Host-buffer form of the same call - what commit-param.cu:12-28 does through files:
  * copies generators and int32 scalars in, commits, copies the m Jacobian results out. */
 int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_scalars, size_t n_scalars,

@@ -1,5 +1,6 @@
 """GPU parity: G1 tensors, commitments and openings against the big-integer
 oracle.  G1 results are compared on the affine point, Fr results bit for bit."""
+import ctypes
 import random
 
 import numpy as np
@@ -151,6 +152,12 @@ def test_commit_int(dev, m, n, bits):
     out = dev.read_g1(do, m)
     for r in range(m):
         assert affine_eq(out[r], exp[r]), r
+    # both algorithms by name: buckets (1) and combination tables (2)
+    for method in (1, 2):
+        dev.call("zkb_commit_i32_method", z._p(dg), z.sz(n), z._p(di), z.sz(m * n), z._p(do), ctypes.c_int(method), z._p(0))
+        out = dev.read_g1(do, m)
+        for r in range(m):
+            assert affine_eq(out[r], exp[r]) and R.g1_on_curve(out[r]), (method, r)
     hout = np.zeros((m, 36), dtype=np.uint32)
     dev.call("zkb_commit_i32_host", z._p(R.g1_pack(g)), z.sz(n), z._p(np.array(ints, dtype=np.int32)), z.sz(m * n), z._p(hout), z._p(0))
     out = R.g1_unpack(hout)
@@ -175,6 +182,44 @@ def test_commit_duplicate_and_identity_generators(dev, gens):
     dev.call("zkb_commit_int", z._p(dev.g1(g)), z.sz(6), z._p(dev.fr([R.int_to_fr(v) for v in ints])), z.sz(12), z._p(do), z._p(0))
     out = dev.read_g1(do, 2)
     assert affine_eq(out[0], exp[0]) and affine_eq(out[1], exp[1])
+    di = z.DeviceBuffer.from_host(np.array(ints, dtype=np.int32))
+    for method in (1, 2):
+        dev.call("zkb_commit_i32_method", z._p(dev.g1(g)), z.sz(6), z._p(di), z.sz(12), z._p(do), ctypes.c_int(method), z._p(0))
+        out = dev.read_g1(do, 2)
+        assert affine_eq(out[0], exp[0]) and affine_eq(out[1], exp[1]), method
+
+
+def test_commit_tables_special_points(dev, gens):
+    """combination tables whose entries meet P + P, P + (-P) and the identity while they are built:
+    equal, opposite and identity generators inside one group of four, every digit from -4 to 3"""
+    z = dev.z
+    P, Q = gens[0], gens[1]
+    g = [P, P, R.g1_neg(P), R.G1_ZERO, Q, R.g1_neg(Q), Q, P, R.G1_ZERO, R.G1_ZERO, R.G1_ZERO, R.G1_ZERO, Q]
+    n = len(g)
+    rng = random.Random(5)
+    rows = [[rng.randrange(-4, 4) for _ in range(n)] for _ in range(6)]
+    rows.append([3] * n)
+    rows.append([-4] * n)
+    rows.append([0] * n)
+    rows.append([rng.randrange(-14000, 14000) for _ in range(n)])
+    ints = [v for r in rows for v in r]
+    m = len(rows)
+    exp = R.commit_int(g, [R.int_to_fr(v) for v in ints])
+    do = z.DeviceBuffer(144 * m)
+    di = z.DeviceBuffer.from_host(np.array(ints, dtype=np.int32))
+    for method in (1, 2):
+        dev.call("zkb_commit_i32_method", z._p(dev.g1(g)), z.sz(n), z._p(di), z.sz(m * n), z._p(do), ctypes.c_int(method), z._p(0))
+        out = dev.read_g1(do, m)
+        for r in range(m):
+            assert affine_eq(out[r], exp[r]), (method, r)
+
+
+def test_commit_method_rejects_unknown(dev, gens):
+    z = dev.z
+    di = z.DeviceBuffer.from_host(np.array([1, 2, 3, 4], dtype=np.int32))
+    with pytest.raises(z.ZkbError) as e:
+        dev.call("zkb_commit_i32_method", z._p(dev.g1(gens[:4])), z.sz(4), z._p(di), z.sz(4), z._p(z.DeviceBuffer(144)), ctypes.c_int(7), z._p(0))
+    assert e.value.code == z.ERR_ARG
 
 
 @pytest.mark.parametrize("m,n", [(1, 3), (2, 8)])

@@ -42,9 +42,14 @@ def test_commit_against_cpp_oracle(dev, m, n, bits):
     rng = np.random.Generator(np.random.PCG64(m * n))
     sc = rng.integers(-(1 << bits), 1 << bits, size=m * n, dtype=np.int64).astype(np.int32)
     out = z.DeviceBuffer(144 * m)
-    dev.call("zkb_commit_i32", z._p(d_g), z.sz(n), z._p(z.DeviceBuffer.from_host(sc)), z.sz(m * n), z._p(out), z._p(0))
-    exp = C.commit_int(h_g, sc, "pippenger")
-    assert np.array_equal(normalised(dev, out, m), C.g1_normalise(exp))
+    d_sc = z.DeviceBuffer.from_host(sc)
+    dev.call("zkb_commit_i32", z._p(d_g), z.sz(n), z._p(d_sc), z.sz(m * n), z._p(out), z._p(0))
+    exp = C.g1_normalise(C.commit_int(h_g, sc, "pippenger"))
+    assert np.array_equal(normalised(dev, out, m), exp)
+    for method in (1, 2):       # buckets, combination tables
+        dev.call("zkb_memset0", z._p(out), z.sz(144 * m), z._p(0))
+        dev.call("zkb_commit_i32_method", z._p(d_g), z.sz(n), z._p(d_sc), z.sz(m * n), z._p(out), ctypes.c_int(method), z._p(0))
+        assert np.array_equal(normalised(dev, out, m), exp), method
 
 
 def test_commit_is_linear_in_the_scalars(dev):
@@ -63,6 +68,14 @@ def test_commit_is_linear_in_the_scalars(dev):
     summed = z.DeviceBuffer(144 * m)
     dev.call("zkb_g1_add", z._p(outs[0]), z._p(outs[1]), z._p(summed), z.sz(m), z._p(0))
     assert np.array_equal(normalised(dev, summed, m), normalised(dev, outs[2], m))
+    # both algorithms give the same 512 points
+    d_a = z.DeviceBuffer.from_host(a)
+    by_method = []
+    for method in (1, 2):
+        o = z.DeviceBuffer(144 * m)
+        dev.call("zkb_commit_i32_method", z._p(d_g), z.sz(n), z._p(d_a), z.sz(m * n), z._p(o), ctypes.c_int(method), z._p(0))
+        by_method.append(normalised(dev, o, m))
+    assert np.array_equal(by_method[0], by_method[1]) and np.array_equal(by_method[0], normalised(dev, outs[0], m))
     # and a sample of rows against the oracle
     _, h_g = gpu_generators(dev, n, 7)
     rows = [0, 255, 511]

@@ -121,6 +121,75 @@ ZKB_DEV G1Jac g1_add(const G1Jac& p, const G1Jac& q) {
     return r;
 }
 
+// ---------------------------------------------------------------------------
+// Extended Jacobian ("XYZZ") accumulator: x = X / ZZ, y = Y / ZZZ with
+// ZZ^3 == ZZZ^2; ZZZ == 0 is the identity.  Adding an affine point costs
+// 8M + 2S ("madd-2008-s") against 7M + 4S for Jacobian coordinates, and a
+// squaring costs a full product here, so a long chain of mixed additions is
+// one product per step cheaper.  Used only for running sums inside kernels;
+// results leave as Jacobian points.
+// ---------------------------------------------------------------------------
+struct __align__(16) G1Xyzz { Fq x, y, zz, zzz; };
+
+ZKB_DEV G1Xyzz xyzz_identity() {
+    G1Xyzz r;
+    r.x = fe_zero<FqParams>(); r.y = fe_zero<FqParams>(); r.zz = fe_zero<FqParams>(); r.zzz = fe_zero<FqParams>();
+    return r;
+}
+ZKB_DEV bool xyzz_is_identity(const G1Xyzz& p) { return fe_is_zero(p.zzz); }
+
+// 2 * q for an affine q that is not the identity ("mdbl-2008-s-1", a = 0)
+ZKB_DEV G1Xyzz xyzz_double_affine(const G1Aff& q) {
+    const Fq u = fq_dbl(q.y);
+    const Fq v = fq_sqr(u);
+    const Fq w = fq_mul(u, v);
+    const Fq s = fq_mul(q.x, v);
+    const Fq xx = fq_sqr(q.x);
+    const Fq m = fq_add(fq_dbl(xx), xx);
+    G1Xyzz r;
+    r.x = fq_sub(fq_sqr(m), fq_dbl(s));
+    r.y = fq_sub(fq_mul(m, fq_sub(s, r.x)), fq_mul(w, q.y));
+    r.zz = v;
+    r.zzz = w;
+    return r;
+}
+
+// XYZZ + affine.  Handles identity operands, P + P and P + (-P).
+ZKB_DEV G1Xyzz xyzz_add_mixed(const G1Xyzz& p, const G1Aff& q) {
+    if (g1_aff_is_identity(q)) return p;
+    if (xyzz_is_identity(p)) {
+        G1Xyzz r;
+        r.x = q.x; r.y = q.y; r.zz = fe_mont_one<FqParams>(); r.zzz = fe_mont_one<FqParams>();
+        return r;
+    }
+    const Fq u2 = fq_mul(q.x, p.zz);
+    const Fq s2 = fq_mul(q.y, p.zzz);
+    const Fq h = fq_sub(u2, p.x);
+    const Fq rr = fq_sub(s2, p.y);
+    if (fe_is_zero(h)) {
+        if (fe_is_zero(rr)) return xyzz_double_affine(q);
+        return xyzz_identity();
+    }
+    const Fq hh = fq_sqr(h);
+    const Fq hhh = fq_mul(h, hh);
+    const Fq v = fq_mul(p.x, hh);
+    G1Xyzz r;
+    r.x = fq_sub(fq_sub(fq_sqr(rr), hhh), fq_dbl(v));
+    r.y = fq_sub(fq_mul(rr, fq_sub(v, r.x)), fq_mul(p.y, hhh));
+    r.zz = fq_mul(p.zz, hh);
+    r.zzz = fq_mul(p.zzz, hhh);
+    return r;
+}
+
+// The same point in Jacobian coordinates with Z = ZZZ: Z^2 = ZZ^3, Z^3 = ZZZ^3.
+ZKB_DEV G1Jac xyzz_to_jac(const G1Xyzz& p) {
+    G1Jac r;
+    r.x = fq_mul(p.x, fq_sqr(p.zz));
+    r.y = fq_mul(p.y, fq_sqr(p.zzz));
+    r.z = p.zzz;
+    return r;
+}
+
 // k * p for a 256-bit scalar given as 8 raw little-endian limbs (the reference
 // reads the standard-form scalar bits directly, g1-tensor.cu:445-453).
 // Left-to-right double-and-add; the result is the same group element.

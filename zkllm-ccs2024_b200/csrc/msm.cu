@@ -499,10 +499,25 @@ static int windows_for_max(unsigned long long max_abs) {
     return 9;
 }
 
-// int32 path: find the largest magnitude (one small D2H), pick the window count.
+}  // namespace zkb
+#include "msm_comb.cuh"
+namespace zkb {
+
+// Field products of the bucket method for m rows (unit shared with comb_cost).
+static double bucket_cost(size_t m, size_t n, int W) {
+    return (double)m * W * ((double)n * 11.0 + 2.0 * kBuckets * 16.0);
+}
+
+// int32 path: find the largest magnitude (one small D2H), then either the bucket
+// method with 7-bit windows or, for many rows over one generator set, the
+// combination tables of msm_comb.cuh with 3-bit windows - whichever needs fewer field
+// products.  method: ZKB_MSM_AUTO, or one of the two by name.
+static constexpr size_t kCombTableLimit = (size_t)12 << 30;
 static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
-                             G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+                             G1Jac* d_out, Scratch& scratch, cudaStream_t s, int method = ZKB_MSM_AUTO) {
     if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
+    if (method != ZKB_MSM_AUTO && method != ZKB_MSM_BUCKETS && method != ZKB_MSM_TABLES)
+        return fail(ZKB_ERR_ARG, "commit: unknown method");
     const size_t m = n_scalars / n_gen;
     if (m == 0) return ZKB_OK;
     unsigned* d_max = scratch.get_n<unsigned>(4);
@@ -512,7 +527,15 @@ static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d
     unsigned h_max = 0;
     ZKB_CUDA(cudaMemcpyAsync(&h_max, d_max, 4, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
-    return msm_rows<false>(d_gens, n_gen, d_scalars, m, windows_for_max(h_max), d_out, scratch, s);
+    const int W7 = windows_for_max(h_max), W3 = comb_windows_for_max(h_max);
+    bool tables = method == ZKB_MSM_TABLES;
+    if (method == ZKB_MSM_AUTO)
+        tables = comb_table_bytes(n_gen) <= kCombTableLimit && comb_cost(m, n_gen, W3) < bucket_cost(m, n_gen, W7);
+    if (!tables) return msm_rows<false>(d_gens, n_gen, d_scalars, m, W7, d_out, scratch, s);
+    G1Aff* bases = scratch.get_n<G1Aff>(n_gen);
+    if (!bases) return ZKB_ERR_CUDA;
+    ZKB_TRY(to_affine_device(d_gens, bases, n_gen, s));
+    return msm_comb_rows(bases, n_gen, d_scalars, m, W3, d_out, scratch, s);
 }
 
 // ---- opening rounds (Commitment::me_open / me_open_step, commitment.cu:79-125) ----
@@ -770,6 +793,14 @@ int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalar
     Scratch scratch(s);
     return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
                              reinterpret_cast<G1Jac*>(d_out), scratch, s);
+}
+
+int zkb_commit_i32_method(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
+                          zkb_g1_t* d_out, int method, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    Scratch scratch(s);
+    return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
+                             reinterpret_cast<G1Jac*>(d_out), scratch, s, method);
 }
 
 int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
