@@ -196,51 +196,58 @@ def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
 
 def sumcheck_sharded(z, torch, dist, world: int, rank: int, steps: int) -> dict:
     """zkFC::prove's body (X 128x4096, W 4096x4096) with W dealt out by rows over the ranks (rank p holds rows
-    p, p + world, ...) and X by the matching columns: local passes on every GPU, one all-gather of a few hundred
-    bytes, the last log2(world) rounds and the verifier replay on every rank (zkllm-ccs2024_b200/sharding.py).
-    Wall seconds per proof, maximum over ranks, including the host-side exchange."""
-    from zkllm_ccs2024_b200 import sharding as S
+    p, p + world, ...) and X by the matching columns, and the 2^23-value lookup proof with values, table and
+    multiplicities dealt out round-robin: zkb_zkfc_prove_sharded / zkb_tlookup_prove_sharded - local passes on every
+    GPU, ONE ncclAllGather of a few hundred bytes inside the library, one device-to-host copy, the last log2(world)
+    rounds and the verifier replay on every rank.  Wall seconds per proof, maximum over ranks."""
     B, I, O = ZKFC_SHAPE
     X, W, Y, ub, ui, uo = zkfc_inputs()
     dXl = z.fr_buffer(ints_to_fr_limbs(np.ascontiguousarray(X[:, rank::world]).reshape(-1)))
     dWl = z.fr_buffer(ints_to_fr_limbs(np.ascontiguousarray(W[rank::world, :]).reshape(-1)))
     dY = z.fr_buffer(ints_to_fr_limbs(Y.reshape(-1)))
-    res = None
-    for _ in range(2):
-        res = S.sharded_zkfc_prove(z, dXl, dWl, dY, B, I // world, O, ub, ui, uo)
-    torch.cuda.synchronize()
-    dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        res = S.sharded_zkfc_prove(z, dXl, dWl, dY, B, I // world, O, ub, ui, uo)
-    torch.cuda.synchronize()
-    t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    polys, claims = np.zeros((36, 8), dtype=np.uint32), np.zeros((4, 8), dtype=np.uint32)
+
+    def zk():
+        z.call("zkb_zkfc_prove_sharded", z._p(dXl), z._p(dWl), z._p(dY), z.sz(B), z.sz(I // world), z.sz(O), z._p(ub), z._p(ui),
+               z._p(uo), z._p(polys), z._p(claims), z._p(0))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+        t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    s = timed(zk)
     out = {"zkfc_prove": {
-        "workload": f"zkFC::prove body, X 128x4096, W 4096x4096 dealt out by rows over {world} GPUs", "seconds": float(t.item()),
-        "weight_bytes_per_gpu": I // world * O * 32, "final_claim": S.fr_ints_to_limbs([res["final_claim"]]).tobytes().hex(),
-        "note": "one all-gather per proof; the time is dominated by the host-side exchange and replay, the split is for "
-                "capacity (weights sharded), a single GPU proves this size in under a millisecond"}}
+        "workload": f"zkFC::prove body, X 128x4096, W 4096x4096 dealt out by rows over {world} GPUs", "seconds": s,
+        "weight_bytes_per_gpu": I // world * O * 32, "final_claim": bytes(claims[1]).hex()}}
     del dXl, dWl, dY
-    # the lookup proof of the benchmark (2^23 values, 2^16 table) with values, table and multiplicities dealt out round-robin
     Sv, alpha, beta, u, v = tlookup_inputs()
     counts = np.bincount(Sv.astype(np.int64) - TL_LOW, minlength=TL_N)
     table = np.arange(TL_LOW, TL_LOW + TL_N, dtype=np.int64)
     dS = z.fr_buffer(ints_to_fr_limbs(np.ascontiguousarray(Sv[rank::world]).astype(np.int64)))
     dT = z.fr_buffer(ints_to_fr_limbs(np.ascontiguousarray(table[rank::world])))
     dM = z.fr_buffer(ints_to_fr_limbs(np.ascontiguousarray(counts[rank::world]).astype(np.int64)))
-    for _ in range(2):
-        polys, fin = S.sharded_tlookup_prove(z, dS, dT, dM, TL_D, TL_N, alpha, beta, u, v)
-    torch.cuda.synchronize()
-    dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        polys, fin = S.sharded_tlookup_prove(z, dS, dT, dM, TL_D, TL_N, alpha, beta, u, v)
-    torch.cuda.synchronize()
-    t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tpolys, tfinal = np.zeros((4 * 23, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+
+    def tl():
+        z.call("zkb_tlookup_prove_sharded", z._p(dS), z._p(dT), z._p(dM), z.sz(TL_D), z.sz(TL_N), z._p(alpha), z._p(beta), z._p(u),
+               z._p(v), z._p(tpolys), z._p(tfinal), z._p(0))
+
+    s = timed(tl)
     out["tlookup_prove"] = {"workload": f"tLookup prove (multiplicities given), 2^23 values in a 2^16 table dealt out over {world} GPUs",
-                            "seconds": float(t.item()), "final_claim": np.ascontiguousarray(fin, dtype=np.uint32).tobytes().hex()}
+                            "seconds": s, "final_claim": bytes(tfinal[0]).hex()}
+    gold = golden_fullsize()
+    for key, gk in (("zkfc_prove", "zkfc_prove_final_claim_be"), ("tlookup_prove", "tlookup_prove_final_claim_be")):
+        if gk in gold:      # the reference prints the claim big-endian, the library stores it little-endian
+            out[key]["equals_reference_claim"] = bytes.fromhex(out[key]["final_claim"])[::-1].hex() == gold[gk][2:]
     return out
 
 
@@ -284,13 +291,74 @@ def g1_equal(z_norm_a: np.ndarray, z_norm_b: np.ndarray) -> bool:
     return bool(np.array_equal(z_norm_a, z_norm_b))
 
 
-# DRAM bytes per (row, generator) pair of msm_accumulate_kernel, from an ncu capture of a 2048 x 11008 launch
-# (112.9 MB read + 47.7 MB written); the kernel's traffic is proportional to the number of pairs.
+def bench_config(m: int, n: int) -> dict:
+    """the workload, named the same way by both arms"""
+    return {"workload": f"commit_int {m}x{n}: row commitments of an int32 fixed-point matrix over {n} G1 generators (BLS12-381)",
+            "rows": m, "generators": n, "seed": SEED,
+            "l2": f"inputs ({m * n * 4 / 1e6:.0f} MB of scalars per step) larger than L2, no flush needed"}
+
+
+def table_method_windows(max_abs: int) -> int:
+    """3-bit windows of the combination-table method for scalars up to max_abs (msm_comb.cuh: comb_windows_for_max)"""
+    p = 8
+    for w in range(1, 11):
+        if max_abs * 7 + 3 <= 3 * p:
+            return w
+        p *= 8
+    return 11
+
+
+def table_method_additions(sc: np.ndarray, m: int, n: int, windows: int) -> int:
+    """mixed additions msm_comb_kernel performs for the matrix sc: one per (row, window, group of four generators)
+    whose four signed 3-bit digits are not all zero (groups of zeros are skipped by the kernel)"""
+    q = (n + 3) // 4
+    pad = np.zeros((m, 4 * q), dtype=np.int64)
+    pad[:, :n] = sc.reshape(m, n)
+    bias = sum(4 << (3 * w) for w in range(windows))
+    b = pad + bias
+    total = 0
+    for w in range(windows):
+        nz = ((b >> (3 * w)) & 7) != 4
+        total += int(nz.reshape(m, q, 4).any(axis=2).sum())
+    return total
+
+
+# DRAM bytes per launch of the dominant kernel come from one ncu capture each (profiles/), scaled by the work of this launch:
+# msm_accumulate_kernel (bucket method): 160.657 MB for 2048 x 11008 (row, generator) pairs;
+# msm_comb_kernel (combination tables): see NCU_COMB_DRAM_BYTES_PER_ADDITION (None until captured).
 NCU_DRAM_BYTES_PER_POINT = 160.657e6 / (2048 * 11008)
+NCU_COMB_DRAM_BYTES_PER_ADDITION = None
 CPU_BASELINE_SECONDS = 12.0
+LAYER_OUTPUTS = ["x1.bin", "temp_Q.bin", "temp_K.bin", "temp_V.bin", "temp_head_Y.bin", "temp_head_out.bin", "x2.bin", "x3.bin",
+                 "x4.bin", "x5.bin"]
+
+
+def g1_generator_limbs() -> np.ndarray:
+    """(1, 36) uint32: the G1 generator as a Jacobian point, Montgomery form, Z = R mod p"""
+    gen1 = np.zeros((1, 36), dtype=np.uint32)
+    gx = 0x120177419E0BFB75EDCE6ECC21DBF440F0AE6ACDF3D0E747154F95C7143BA1C17817FC679976FFF55CB38790FD530C16
+    gy = 0x0BBC3EFC5008A26A0E1C8C3FAD0059C051AC582950405194DD595F13570725CE8C22631A7918FD8EBAAC93D50CE72271
+    gz = 0x15F65EC3FA80E4935C071A97A256EC6D77CE5853705257455F48985753C758BAEBF4000BC40C0002760900000002FFFD
+    for k, v in enumerate((gx, gy, gz)):
+        for i in range(12):
+            gen1[0, 12 * k + i] = (v >> (32 * i)) & 0xFFFFFFFF
+    return gen1
+
+
+def row_shard(m: int, world: int, rank: int) -> tuple:
+    base, extra = divmod(m, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def golden_fullsize() -> dict:
+    path = ROOT / "tests" / "golden" / "ref_fullsize.json"
+    return json.loads(path.read_text()) if path.exists() else {}
 
 
 def run_ours(args) -> dict:
+    import hashlib
+
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
@@ -299,43 +367,51 @@ def run_ours(args) -> dict:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    z = load_package()
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    z = load_package()
+        # the library's own communicator (C++/NCCL): rank 0 makes the id, torch.distributed only carries it
+        idbuf = np.zeros(128, dtype=np.uint8)
+        if rank == 0:
+            z.call("zkb_comm_unique_id", z._p(idbuf))
+        t_id = torch.from_numpy(idbuf).cuda()
+        dist.broadcast(t_id, 0)
+        idbuf = t_id.cpu().numpy().copy()
+        z.call("zkb_comm_init", ctypes.c_int(rank), ctypes.c_int(world), z._p(idbuf))
     m, n = args.rows, args.cols
     stream = torch.cuda.current_stream().cuda_stream
     sp = z._p(stream)
 
     # ---- inputs, resident in HBM -------------------------------------------------------
+    # weak scaling (the headline): every rank commits its own m x n matrix; rank 0's is the N = 1 matrix
     h_sc = torch.from_numpy(weights(m, n, SEED + 2 + 7 * rank)).pin_memory()
     d_sc = h_sc.cuda(non_blocking=True)
     gs = generator_scalars(n)
     d_gs = torch.from_numpy(gs.view(np.int32)).cuda()
-    gen1 = np.zeros((1, 36), dtype=np.uint32)   # the G1 generator, Montgomery form, Z = R mod p
-    gx = 0x120177419E0BFB75EDCE6ECC21DBF440F0AE6ACDF3D0E747154F95C7143BA1C17817FC679976FFF55CB38790FD530C16
-    gy = 0x0BBC3EFC5008A26A0E1C8C3FAD0059C051AC582950405194DD595F13570725CE8C22631A7918FD8EBAAC93D50CE72271
-    gz = 0x15F65EC3FA80E4935C071A97A256EC6D77CE5853705257455F48985753C758BAEBF4000BC40C0002760900000002FFFD
-    for k, v in enumerate((gx, gy, gz)):
-        for i in range(12):
-            gen1[0, 12 * k + i] = (v >> (32 * i)) & 0xFFFFFFFF
-    d_gen1 = torch.from_numpy(gen1.view(np.int32)).cuda()
+    d_gen1 = torch.from_numpy(g1_generator_limbs().view(np.int32)).cuda()
     d_gens = torch.empty(n * 36, dtype=torch.int32, device="cuda")
     z.call("zkb_g1_mul", z._p(d_gen1.data_ptr()), z.sz(1), z._p(d_gs.data_ptr()), z.sz(n), z._p(d_gens.data_ptr()), sp)
-    d_out = torch.empty(m * 36, dtype=torch.int32, device="cuda")
-    if world > 1:
-        from zkllm_ccs2024_b200 import sharding
+    d_all = torch.empty(world * m * 36, dtype=torch.int32, device="cuda")     # every rank ends with all world * m points
+    d_out = d_all[rank * m * 36:(rank + 1) * m * 36]
     torch.cuda.synchronize()
 
     def step():
         z.call("zkb_commit_i32", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_sc.data_ptr()), z.sz(m * n), z._p(d_out.data_ptr()), sp)
         if world > 1:
-            # the exchange step of a row-sharded commitment: every rank ends with all world*m points
-            sharding.all_gather_rows(d_out, world * m, 36)
+            # the exchange step of a row-sharded commitment, in place in the preallocated result
+            z.call("zkb_comm_allgather", z._p(d_out.data_ptr()), z._p(d_all.data_ptr()), z.sz(m * 144), sp)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     for _ in range(args.warmup):
         step()
@@ -365,11 +441,7 @@ def run_ours(args) -> dict:
         name, cnt, ms = line.rsplit(",", 2)
         if not name.startswith("host:"):          # host-side allocator time is not a kernel
             kernels[name] = (int(cnt), float(ms))
-    if world > 1:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    ms_step = max_over_ranks(ms_total) / args.steps
     value = world * m * n / (ms_step * 1e-3) / 1e6
 
     # ---- end to end through the host-buffer call -------------------------------------------
@@ -389,13 +461,43 @@ def run_ours(args) -> dict:
         e2e_step()
     f1.record()
     barrier()
-    e2e_s = f0.elapsed_time(f1) * 1e-3 / args.steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks(f0.elapsed_time(f1) * 1e-3 / args.steps)
     e2e = {"value": world * m * n / e2e_s / 1e6, "unit": "Mpts/s", "h2d_bytes_per_step": int(n * 144 + m * n * 4),
            "d2h_bytes_per_step": int(m * 144)}
+    got_weak = d_out.cpu().numpy().view(np.uint32).reshape(m, 36).copy()
+
+    # ---- strong scaling: the ONE m x n matrix of the N = 1 run, rows dealt out over the ranks ------
+    strong = None
+    if world > 1:
+        b, e = row_shard(m, world, rank)
+        full = weights(m, n, SEED + 2).reshape(m, n)
+        d_loc = torch.from_numpy(np.ascontiguousarray(full[b:e])).cuda()
+        d_res = torch.empty(m * 36, dtype=torch.int32, device="cuda")
+
+        def strong_step():
+            z.call("zkb_commit_i32_sharded", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_loc.data_ptr()), z.sz(e - b), z.sz(m),
+                   z._p(d_res.data_ptr()), sp)
+
+        for _ in range(3):
+            strong_step()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            strong_step()
+        g1.record()
+        barrier()
+        strong_ms = max_over_ranks(g0.elapsed_time(g1) / args.steps)
+        strong = {"workload": f"one {m}x{n} matrix, rows dealt out in contiguous blocks over {world} GPUs, generators on every GPU, "
+                              "results all-gathered in row order (zkb_commit_i32_sharded)",
+                  "scaling": "strong", "ms": strong_ms, "Mpts_s": m * n / (strong_ms * 1e-3) / 1e6, "rows_per_gpu": e - b}
+        if rank == 0:
+            from oracle import cpporacle as C
+            sha = hashlib.sha256(C.g1_normalise(d_res.cpu().numpy().view(np.uint32).reshape(m, 36)).tobytes()).hexdigest()
+            strong["commit_sha256"] = sha
+            gold = golden_fullsize().get("commit_int_4096x11008_sha256") if (m, n) == (4096, 11008) else None
+            strong["matches_single_gpu_and_reference_sha"] = (sha == gold) if gold else None
+        del d_loc, d_res
 
     # ---- sumcheck with the weights split over the GPUs (every rank takes part) ----------------
     sharded = None
@@ -407,12 +509,13 @@ def run_ours(args) -> dict:
         # ---- correctness on a sample of rows (checker: CPU restatement) -------------------
         from oracle import cpporacle as C
         sample = sorted(set([0, 1, m // 2, m - 1]))
-        got = d_out.cpu().numpy().view(np.uint32).reshape(m, 36)
+        got = got_weak
         exp = C.commit_int(h_gens.numpy().view(np.uint32).reshape(n, 36), h_sc.numpy().reshape(m, n)[sample], "pippenger")
         parity = g1_equal(C.g1_normalise(got[sample]), C.g1_normalise(exp))
         e2e_ok = g1_equal(C.g1_normalise(h_out.numpy().view(np.uint32).reshape(m, 36)[sample]), C.g1_normalise(exp))
-        import hashlib
         commit_sha = hashlib.sha256(C.g1_normalise(got).tobytes()).hexdigest()   # all m points, affine-normalised
+        gold = golden_fullsize().get("commit_int_4096x11008_sha256") if (m, n) == (4096, 11008) else None
+        sha_parity = (commit_sha == gold) if gold else None
 
         # ---- CPU baseline: same algorithm on the host cores, bounded sample (N = 1 only) ---
         cpu_baseline = None
@@ -431,7 +534,7 @@ def run_ours(args) -> dict:
                             "sample": f"first {rows_cpu} of {m} rows ({cpu_s:.1f} s), signed-digit bucket MSM in C++ "
                                       "(oracle/zkoracle.cpp), OpenMP"}
 
-        # ---- roofline of the dominant kernel ------------------------------------------------
+        # ---- roofline of the dominant kernel: the integer pipe is what bounds it -------------
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
         hbm_peak, peak_src = 6650.0, "fallback"
@@ -446,44 +549,71 @@ def run_ours(args) -> dict:
         dom_name = max(kernels, key=lambda k: kernels[k][1]) if kernels else None
         dom_cnt, dom_ms = kernels.get(dom_name, (0, 0.0))
         dom_launch_ms = dom_ms / max(dom_cnt, 1)
-        windows = 2 if int(np.abs(h_sc.numpy()).max()) < 8128 else 3
-        algo_bytes = m * n * 4 + n * 96 + m * windows * 64 * 144     # scalars + affine bases in, bucket sums out
-        achieved = algo_bytes / (dom_launch_ms * 1e-3) / 1e9 if dom_launch_ms else 0.0
-        algo_mads = m * n * windows * FQ_MULS_PER_MIXED_ADD * MADS_PER_FQ_MUL
+        max_abs = int(np.abs(h_sc.numpy()).max())
+        if dom_name == "msm_comb_kernel":
+            windows = table_method_windows(max_abs)
+            additions = table_method_additions(h_sc.numpy(), m, n, windows)
+            fq_per_add, method = 10, f"combination tables of four generators, {windows} signed 3-bit windows, XYZZ running sums"
+            table_adds = ((n + 3) // 4) * 4096
+            algo_bytes = m * n * 4 + additions * 96 + m * windows * 144          # scalars, one table entry per addition, chain sums
+            traffic = int(additions * NCU_COMB_DRAM_BYTES_PER_ADDITION) if NCU_COMB_DRAM_BYTES_PER_ADDITION else None
+            traffic_src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one msm_comb_kernel launch (profiles/), scaled by the "
+                           "additions of this launch") if traffic else "not captured"
+            total_mads = (additions * fq_per_add + table_adds * 6) * MADS_PER_FQ_MUL
+        else:
+            windows = 2 if max_abs < 8128 else 3
+            additions = m * n * windows
+            fq_per_add, method = FQ_MULS_PER_MIXED_ADD, f"bucket method, {windows} signed 7-bit windows, Jacobian bucket sums"
+            algo_bytes = m * n * 4 + n * 96 + m * windows * 64 * 144     # scalars + affine bases in, bucket sums out
+            traffic = int(m * n * NCU_DRAM_BYTES_PER_POINT)
+            traffic_src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one 2048 x 11008 launch (160.7 MB), scaled by "
+                           "the points of this launch")
+            total_mads = additions * fq_per_add * MADS_PER_FQ_MUL
+        algo_mads = additions * fq_per_add * MADS_PER_FQ_MUL
         ach_gmad = algo_mads / (dom_launch_ms * 1e-3) / 1e9 if dom_launch_ms else 0.0
-        roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": achieved / hbm_peak, "traffic": int(m * n * NCU_DRAM_BYTES_PER_POINT), "peak_source": peak_src,
-                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one 2048 x 11008 launch "
-                                      "(160.7 MB), scaled by the points of this launch; algorithmic bytes "
-                                      f"{algo_bytes}",
-                    "note": "kernel is bound by 32-bit multiply-add issue, not HBM: see int_pipe"}
-        int_pipe = {"kernel": dom_name, "achieved": ach_gmad, "peak": imad["madc_chain"], "unit": "G mad/s",
+        ach_gbs = algo_bytes / (dom_launch_ms * 1e-3) / 1e9 if dom_launch_ms else 0.0
+        roofline = {"bound": "int_pipe", "kernel": dom_name, "achieved": ach_gmad, "peak": imad["madc_chain"], "unit": "G mad/s",
                     "frac": ach_gmad / imad["madc_chain"] if imad["madc_chain"] else None,
-                    "peaks_measured": imad, "algorithmic_mads_per_point": windows * FQ_MULS_PER_MIXED_ADD * MADS_PER_FQ_MUL,
-                    "launch_ms": dom_launch_ms}
+                    "peak_source": "32-bit multiply-add carry chains measured on this GPU in this run (zkb_bench_imad); "
+                                   "MEASURED_PEAKS.json has no integer figure",
+                    "peaks_measured": imad, "launch_ms": dom_launch_ms,
+                    "algorithmic": {"mixed_additions_per_launch": additions, "fq_products_per_addition": fq_per_add,
+                                    "mads_per_fq_product": MADS_PER_FQ_MUL, "mads_per_launch": algo_mads,
+                                    "mads_per_point_whole_step": total_mads / (m * n)},
+                    "traffic": traffic, "traffic_source": traffic_src,
+                    "hbm": {"achieved": ach_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": ach_gbs / hbm_peak,
+                            "peak_source": peak_src, "algorithmic_bytes": algo_bytes,
+                            "note": "not the binding resource of this kernel"}}
         shares = {k: round(v[1] / sum(x[1] for x in kernels.values()), 4) for k, v in kernels.items()} if kernels else {}
         sumcheck = None
         if not args.no_sumcheck:
-            del d_sc, d_out
+            del d_sc, d_out, d_all
             torch.cuda.empty_cache()
             sumcheck = sumcheck_ours(z, torch, max(2, min(args.steps, 5)), hbm_peak)
+        cfg = bench_config(m, n)
+        if world > 1:
+            cfg["rows_per_gpu"] = m
+            cfg["matrices"] = world
         result = {
             "metric": "G1 MSM throughput (Pedersen/Hyrax row commitment)", "value": value, "unit": "Mpts/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-            "config": {"workload": f"commit_int {m}x{n} int32 fixed-point weights over {n} G1 generators (BLS12-381), "
-                                   f"{windows} signed 7-bit windows", "rows_per_gpu": m, "generators": n,
-                       "l2": "inputs (172 MB of scalars per step) larger than L2, no flush needed"},
+            "config": cfg, "algorithm": method,
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roofline, "int_pipe": int_pipe, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
             "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "commit_sha256": commit_sha,
-            "sumcheck": sumcheck, "sumcheck_sharded": sharded,
+            "commit_sha256_equals_reference": sha_parity,
+            "sumcheck": sumcheck, "sumcheck_sharded": sharded, "strong": strong,
         }
-        if not (parity and e2e_ok):
-            result["error"] = "sampled rows differ from the CPU oracle"
+        if not (parity and e2e_ok) or sha_parity is False:
+            result["error"] = "commitments differ from the oracle / the reference's recorded SHA"
     if world > 1:
         dist.barrier()
+        z.call("zkb_comm_destroy")
         dist.destroy_process_group()
+    if rank == 0 and world == 1 and not args.no_layer:
+        del z
+        result["layer"] = layer_block(args)
     return result
 
 
@@ -526,11 +656,18 @@ def run_reference(args) -> dict:
         s = sum(times) / len(times)
         v = m * n / s / 1e6
         sumcheck = None if args.no_sumcheck else sumcheck_reference(harness, max(1, min(args.steps, 2)))
+        layer = None
+        if not args.no_layer and args.gpus == 1:
+            try:
+                layer = layer_workload("reference", [("process", 1)], args.seq, args.embed, args.hidden, args.tmpdir)
+            except Exception as ex:
+                layer = {"impl": "reference", "error": str(ex)[-600:]}
         return {**base, "value": v, "ms_per_step": s * 1e3, "sumcheck": sumcheck, "commit_sha256": commit_sha,
-                "config": {"workload": f"commit_int {m}x{n} (reference Commitment::commit_int, its own CUDA kernels, sm_100 build)"},
+                "config": bench_config(m, n),
+                "algorithm": "reference Commitment::commit_int (31-step double-and-add per pair, its own CUDA kernels, sm_100 -dlto build)",
                 "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": 0, "kind": "reference",
                                  "sample": "full workload, reference CUDA build on the same GPU (the reference has no CPU path)"},
-                "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+                "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "layer": layer}
     cores = C.threads()
     rows = min(m, max(cores, 16))
     best = None
@@ -540,31 +677,35 @@ def run_reference(args) -> dict:
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     v = rows * n / best / 1e6
-    return {**base, "value": v, "ms_per_step": best * 1e3 * m / rows,
-            "config": {"workload": f"commit_int {m}x{n}: the reference's double-and-add algorithm on host cores, {rows}-row sample"},
+    return {**base, "value": v, "ms_per_step": best * 1e3 * m / rows, "config": bench_config(m, n),
+            "algorithm": f"the reference's double-and-add algorithm on host cores, {rows}-row sample",
             "cpu_baseline": {"value": v, "unit": "Mpts/s", "cores": cores, "kind": "port",
                              "sample": f"first {rows} of {m} rows (per-point 31-step double-and-add + row sum, commitment.cu:31-58)"},
             "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
-def run_layer(args) -> dict:
+def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=None, log=None) -> dict:
     """One Llama-2-7B-shape decoder layer (seq 2048, hidden 4096, FFN 11008, random-init fixed-point weights) through the
-    stage drivers with the reference's command lines and files: parameter commitment, then rmsnorm, self-attn (linear +
-    attn), skip-connection, rmsnorm, ffn, skip-connection.  Wall seconds per stage process (each includes start-up and file
-    I/O).  --impl reference runs the reference's own driver executables (oracle/_ref/drivers, device-LTO build)."""
-    seq, embed, hidden = args.seq, args.embed, args.hidden
-    bindir = (ROOT / "oracle" / "_ref" / "drivers") if args.impl == "reference" else (ROOT / "zkllm-ccs2024_b200" / "bin")
+    stage drivers with the reference's command lines and files: parameter commitment once, then for every (mode, passes) of
+    `modes` the stages rmsnorm, self-attn (linear + attn), skip-connection, rmsnorm, ffn, skip-connection.  mode "process" =
+    one process per stage, as the reference's Python glue runs them; "batch" = all stages in one resident driver process
+    (this build only).  impl "reference" runs the reference's own driver executables (oracle/_ref/drivers, device-LTO build).
+    Wall seconds per stage (each includes file I/O, and start-up in process mode) and the SHA-256 of every integer output."""
+    import hashlib
+    bindir = (ROOT / "oracle" / "_ref" / "drivers") if impl == "reference" else (ROOT / "zkllm-ccs2024_b200" / "bin")
+    shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((embed, hidden), "decoder")
+    out = {"impl": impl, "workload": f"{shape} layer, seq {seq} hidden {embed} ffn {hidden}", "data": "synthetic"}
     if not (bindir / "ffn").exists():
-        return {"impl": args.impl, "workload": "layer", "unavailable": f"{bindir} has no driver executables"}
+        out["unavailable"] = f"{bindir.relative_to(ROOT)} has no driver executables"
+        return out
     env = dict(os.environ, ZKLLM_CHALLENGE_SEED="2024")
     stages = {}
-
-    batch = args.layer_mode == "batch" and args.impl == "ours"
     server = {"proc": None, "log": []}
+    state = {"batch": False}
 
     def run(stage, argv, cwd, label=None):
         t0 = time.perf_counter()
-        if batch:
+        if state["batch"]:
             # one resident driver process (zkllm-driver batch -): a command line in, its "[batch] ..." line back
             if server["proc"] is None:
                 server["proc"] = subprocess.Popen([str(bindir / "zkllm-driver"), "batch", "-"], cwd=cwd, env=env, text=True,
@@ -588,13 +729,25 @@ def run_layer(args) -> dict:
         dt = time.perf_counter() - t0
         stages[label or stage] = stages.get(label or stage, 0.0) + dt
 
-    with tempfile.TemporaryDirectory(dir=args.tmpdir) as tmp:
+    def close_server():
+        if server["proc"] is not None:
+            server["proc"].stdin.close()
+            server["log"].extend(server["proc"].stderr.readlines())
+            if log:
+                Path(log).write_text("".join(server["log"]))
+            rc = server["proc"].wait(timeout=120)
+            server["proc"] = None
+            if rc != 0:
+                raise RuntimeError("batch driver exited with an error")
+
+    with tempfile.TemporaryDirectory(dir=tmpdir) as tmp:
         w = Path(tmp)
         rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 64))
         params = [("input_layernorm.weight", 1, embed, embed), ("post_attention_layernorm.weight", 1, embed, embed),
                   ("self_attn.q_proj.weight", embed, embed, embed << 5), ("self_attn.k_proj.weight", embed, embed, embed << 5),
                   ("self_attn.v_proj.weight", embed, embed, embed << 5), ("mlp.up_proj.weight", embed, hidden, hidden << 5),
                   ("mlp.gate_proj.weight", embed, hidden, hidden << 5), ("mlp.down_proj.weight", hidden, embed, embed << 5)]
+        state["batch"] = modes[0][0] == "batch" and impl == "ours"
         for name, in_dim, out_dim, pp_size in params:
             if in_dim == 1:
                 wi = np.rint((1.0 + 0.1 * rng.standard_normal(out_dim)) * 65536).astype(np.int32)
@@ -624,31 +777,64 @@ def run_layer(args) -> dict:
             run("ffn", ["x3.bin", seq, embed, hidden, w, "layer-0", "x4.bin"], w, "ffn")
             run("skip-connection", ["x2.bin", "x4.bin", "x5.bin"], w, "skip-connection (x2)")
 
-        setup = dict(stages)
-        passes = []
-        for _ in range(max(1, args.layer_repeat)):
-            stages.clear()
-            prove_layer()
-            passes.append(dict(stages))
-        stages.clear()
-        stages.update(setup)
-        stages.update(passes[-1])
-        if server["proc"] is not None:
-            server["proc"].stdin.close()
-            server["log"].extend(server["proc"].stderr.readlines())
-            if args.layer_log:
-                Path(args.layer_log).write_text("".join(server["log"]))
-            if server["proc"].wait(timeout=60) != 0:
-                raise RuntimeError("batch driver exited with an error")
-        import hashlib
-        digest = hashlib.sha256((w / "x4.bin").read_bytes() + (w / "temp_head_out.bin").read_bytes()).hexdigest()
-    prove = sum(v for k, v in stages.items() if not k.startswith(("ppgen", "commit-param")))
-    shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((embed, hidden), "decoder")
-    return {"metric": f"{shape} layer prove time", "unit": "s", "value": prove, "higher_is_better": False,
-            "impl": args.impl, "workload": f"layer seq {seq} hidden {embed} ffn {hidden}", "stages_s": stages,
-            "mode": "one resident driver process" if batch else "one process per stage",
-            "passes_s": [sum(p.values()) for p in passes],
-            "commit_params_s": stages.get("commit-param (8 parameters)"), "outputs_sha256": digest, "data": "synthetic"}
+        def digest():
+            files = {}
+            h = hashlib.sha256()
+            for nm in LAYER_OUTPUTS:
+                data = (w / nm).read_bytes()
+                h.update(data)
+                files[nm] = hashlib.sha256(data).hexdigest()[:16]
+            return h.hexdigest(), files
+
+        out["setup_s"] = dict(stages)
+        out["setup_mode"] = "one resident driver process" if state["batch"] else "one process per stage"
+        for mode, passes in modes:
+            state["batch"] = mode == "batch" and impl == "ours"
+            if not state["batch"]:
+                close_server()
+            for nm in LAYER_OUTPUTS:            # every mode has to produce the outputs itself
+                if (w / nm).exists():
+                    (w / nm).unlink()
+            per_pass = []
+            for _ in range(max(1, passes)):
+                stages.clear()
+                prove_layer()
+                per_pass.append(dict(stages))
+            sha, files = digest()
+            out["one resident driver process" if state["batch"] else "one process per stage"] = {
+                "seconds": sum(per_pass[-1].values()), "stages_s": per_pass[-1], "passes_s": [sum(q.values()) for q in per_pass],
+                "outputs_sha256": sha, "output_files_sha256_16": files}
+        close_server()
+    return out
+
+
+def layer_block(args) -> dict:
+    """the layer workload as part of the default N = 1 line: this build in both driver modes (the reference arm reports its own)"""
+    try:
+        blk = layer_workload("ours", [("batch", 2), ("process", 1)], args.seq, args.embed, args.hidden, args.tmpdir, args.layer_log)
+    except Exception as ex:   # the headline line must still print
+        return {"impl": "ours", "error": str(ex)[-600:]}
+    gold = golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else None
+    shas = [v["outputs_sha256"] for v in blk.values() if isinstance(v, dict) and "outputs_sha256" in v]
+    blk["reference_outputs_sha256"] = gold
+    blk["parity"] = (all(x == gold for x in shas) and bool(shas)) if gold else None
+    blk["note"] = ("like for like with the reference is 'one process per stage' (every process pays CUDA start-up and reloads "
+                   "generators and weights); 'one resident driver process' is what this build adds; seconds are wall time")
+    return blk
+
+
+def run_layer(args) -> dict:
+    """--workload layer: the layer workload alone, one JSON line"""
+    if args.impl == "reference":
+        modes = [("process", max(1, args.layer_repeat))]
+    else:
+        modes = [(args.layer_mode, max(1, args.layer_repeat))]
+    blk = layer_workload(args.impl, modes, args.seq, args.embed, args.hidden, args.tmpdir, args.layer_log)
+    key = "one resident driver process" if (args.layer_mode == "batch" and args.impl == "ours") else "one process per stage"
+    inner = blk.get(key, {})
+    shape = blk["workload"].split(" layer")[0]
+    return {"metric": f"{shape} layer prove time", "unit": "s", "value": inner.get("seconds"), "higher_is_better": False,
+            "impl": args.impl, "mode": key, **blk}
 
 
 def main():
@@ -673,6 +859,7 @@ def main():
                     help="layer workload, our arm: all stages in one resident driver process, or one process per stage as the "
                          "reference's Python glue does (the reference arm always runs one process per stage)")
     ap.add_argument("--no-sumcheck", action="store_true", help="skip the zkFC / tLookup proof timings reported under 'sumcheck'")
+    ap.add_argument("--no-layer", action="store_true", help="skip the decoder-layer workload reported under 'layer' (N = 1 only)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

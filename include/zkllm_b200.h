@@ -322,6 +322,37 @@ int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, 
 int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
                 zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream);
 
+/* ---- multi-GPU: one process per GPU (no counterpart in the reference, which is single-GPU) ----
+ * The process's communicator is an NCCL communicator on the device that is current when
+ * zkb_comm_init runs; rank 0 makes the 128-byte id (zkb_comm_unique_id) and hands it to the other
+ * ranks by any means (a file, MPI, torch.distributed).  Every exchange is a plain all-gather
+ * on this GPU's own buffers.  The sharded provers below do all their local work first and
+ * exchange once; every rank returns the same result as the single-GPU call on the whole data. */
+int zkb_comm_unique_id(unsigned char* id128);
+int zkb_comm_init(int rank, int world, const unsigned char* id128);
+int zkb_comm_info(int* rank, int* world);               /* world == 0: not initialised */
+int zkb_comm_destroy(void);
+/* d_recv[p * bytes_per_rank ...] = rank p's d_send; queued on the stream, no host synchronisation */
+int zkb_comm_allgather(const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream);
+/* Commitment::commit_int (commitment.cu:31-58) with the rows dealt out in contiguous blocks: rank p
+ * holds rows [p*m/P ..) (the first m % P ranks one row more) as int32, the generators are on
+ * every rank, d_out_all receives all rows_total commitments in row order on every rank. */
+int zkb_commit_i32_sharded(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars_local, size_t rows_local,
+                           size_t rows_total, zkb_g1_t* d_out_all, void* stream);
+/* zkFC::prove's body (zkfc.cu:61-87) with W dealt out by rows round-robin and X by the matching
+ * columns: rank p holds X[:, p::P] (B x I_local) and W[p::P, :] (I_local x O), Y is on every rank.
+ * h_u_input has log2(I_local * P) entries.  Outputs as zkb_zkfc_prove. */
+int zkb_zkfc_prove_sharded(const zkb_fr_t* d_X_local, const zkb_fr_t* d_W_local, const zkb_fr_t* d_Y,
+                           size_t B, size_t I_local, size_t O,
+                           const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
+                           zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream);
+/* tLookup::prove (tlookup.cu:324-370) with S, the table and the multiplicities dealt out round-robin:
+ * rank p holds S[p::P], T[p::P], m[p::P]; D, N and the challenges are those of the whole proof. */
+int zkb_tlookup_prove_sharded(const zkb_fr_t* d_S_local, const zkb_fr_t* d_table_local, const zkb_fr_t* d_m_local,
+                              size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                              const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                              zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

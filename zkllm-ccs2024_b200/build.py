@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "build"
 LIB = HERE / "lib" / "libzkllm_b200.so"
-SOURCES = ["common.cu", "fr_ops.cu", "sumcheck.cu", "combine.cu", "g1_ops.cu", "msm.cu", "nn_ops.cu", "bench_kernels.cu"]
+SOURCES = ["common.cu", "fr_ops.cu", "sumcheck.cu", "combine.cu", "g1_ops.cu", "msm.cu", "nn_ops.cu", "bench_kernels.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objs = [str(BUILD / (s + ".o")) for s in srcs]
     newest = max(Path(o).stat().st_mtime for o in objs)
     if force or not LIB.exists() or LIB.stat().st_mtime < newest:
-        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *objs, "-lcudart"]
+        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *objs, "-lcudart", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

@@ -345,45 +345,34 @@ template <class P> ZKB_DEV Fe<P> mont_inv_fermat(const Fe<P>& a) {
     return res;
 }
 
-// Plain-integer helpers of the binary inversion below (values below 2^(32N)).
-template <class P> ZKB_DEV void fe_shr1(Fe<P>& a, uint32_t carry_in) {
+// x / 2^s mod p for x in [0, p) and 1 <= s <= 31: add the multiple m p that clears the low s bits
+// (m = -x / p mod 2^s), then shift; the sum is below 2^s p, which fits N + 1 limbs.
+template <class P> ZKB_DEV void fe_div_pow2(Fe<P>& x, uint32_t s) {
     constexpr int N = P::N;
+    const uint32_t m = (x.v[0] * P::M0) & ((1u << s) - 1u);
+    uint32_t t[N + 1];
 #pragma unroll
-    for (int i = 0; i < N - 1; ++i) a.v[i] = __funnelshift_r(a.v[i], a.v[i + 1], 1);
-    a.v[N - 1] = (a.v[N - 1] >> 1) | (carry_in << 31);
-}
-// x / 2 mod p for x in [0, p)
-template <class P> ZKB_DEV void fe_half(Fe<P>& x) {
-    constexpr int N = P::N;
-    const uint32_t odd = 0u - (x.v[0] & 1u);
-    x.v[0] = ptx_add_cc3(x.v[0], P::mod(0) & odd);
+    for (int i = 0; i < N; ++i) t[i] = x.v[i];
+    ptx_mad_lo_cc(t[0], P::mod(0), m);
 #pragma unroll
-    for (int i = 1; i < N; ++i) x.v[i] = ptx_addc_cc3(x.v[i], P::mod(i) & odd);
-    const uint32_t carry = ptx_addc3(0u, 0u);
-    fe_shr1(x, carry);
-}
-// a >= b as integers
-template <class P> ZKB_DEV bool fe_geq(const Fe<P>& a, const Fe<P>& b) {
-    constexpr int N = P::N;
-    (void)ptx_sub_cc3(a.v[0], b.v[0]);
+    for (int i = 1; i < N; ++i) ptx_madc_lo_cc(t[i], P::mod(i), m);
+    t[N] = ptx_addc3(0u, 0u);
+    ptx_mad_hi_cc(t[1], P::mod(0), m);
 #pragma unroll
-    for (int i = 1; i < N; ++i) (void)ptx_subc_cc3(a.v[i], b.v[i]);
-    return ptx_subc3(0u, 0u) == 0u;
-}
-// a -= b as integers, a >= b
-template <class P> ZKB_DEV void fe_sub_raw(Fe<P>& a, const Fe<P>& b) {
-    constexpr int N = P::N;
-    a.v[0] = ptx_sub_cc3(a.v[0], b.v[0]);
+    for (int i = 1; i < N; ++i) ptx_madc_hi_cc(t[i + 1], P::mod(i), m);
 #pragma unroll
-    for (int i = 1; i < N - 1; ++i) a.v[i] = ptx_subc_cc3(a.v[i], b.v[i]);
-    a.v[N - 1] = ptx_subc3(a.v[N - 1], b.v[N - 1]);
+    for (int i = 0; i < N; ++i) x.v[i] = __funnelshift_r(t[i], t[i + 1], s);
 }
+
 // 1/a in Montgomery form for a in Montgomery form; 0 maps to 0 like the
 // reference's Fermat inverse (bls12-381.cu:597-609), with the same value for
-// every other input.  Binary extended Euclid on plain integers: u, v shrink by
-// halving and subtracting while x1, x2 track u = x1 a, v = x2 a (mod p); at most
-// 2 * bits(p) short passes of shifts and additions instead of ~1.5 * bits(p) field
-// products.  The pass count is capped above that bound.
+// every other input.  Binary extended Euclid on plain integers with u, v both
+// odd: each pass replaces the larger of the two by their difference and strips all
+// its trailing zero bits at once (up to 31 per pass), while x1, x2 follow so
+// that u = x1 a, v = x2 a (mod p); the division of x1 by 2^s is one short
+// multiply-add pass (fe_div_pow2).  The order of u and v is handled with selects,
+// not branches, so the lanes of a warp stay together; about 0.7 * bits(p) passes,
+// capped above the worst case bits(u) + bits(v).
 template <class P> ZKB_DEV Fe<P> mont_inv(const Fe<P>& a) {
     constexpr int N = P::N;
     if (fe_is_zero(a)) return a;
@@ -391,29 +380,39 @@ template <class P> ZKB_DEV Fe<P> mont_inv(const Fe<P>& a) {
 #pragma unroll
     for (int i = 0; i < N; ++i) v.v[i] = P::mod(i);
     x1.v[0] = 1u;
-    // every pass halves u or v once, so at most bits(u) + bits(v) passes run
 #pragma unroll 1
     for (int it = 0; it < 64 * N + 64; ++it) {
-        if (!(u.v[0] & 1u)) {
-            fe_shr1(u, 0u);
-            fe_half(x1);
-        } else if (!(v.v[0] & 1u)) {
-            fe_shr1(v, 0u);
-            fe_half(x2);
-        } else {
-            if (fe_eq(u, v)) break;          // both equal the gcd, which is 1
-            if (fe_geq(u, v)) {
-                fe_sub_raw(u, v);            // odd - odd: even, halve at once
-                fe_shr1(u, 0u);
-                x1 = fe_sub(x1, x2);
-                fe_half(x1);
-            } else {
-                fe_sub_raw(v, u);
-                fe_shr1(v, 0u);
-                x2 = fe_sub(x2, x1);
-                fe_half(x2);
+        if (u.v[0] & 1u) {
+            // d = u - v; on a borrow the roles swap: v <- u, u <- v - u
+            Fe<P> d;
+            d.v[0] = ptx_sub_cc3(u.v[0], v.v[0]);
+#pragma unroll
+            for (int i = 1; i < N; ++i) d.v[i] = ptx_subc_cc3(u.v[i], v.v[i]);
+            const uint32_t borrow = ptx_subc3(0u, 0u);      // all-ones when u < v
+            if (fe_is_zero(d)) break;                        // u == v == gcd == 1
+            Fe<P> nd;
+            nd.v[0] = ptx_sub_cc3(0u, d.v[0]);
+#pragma unroll
+            for (int i = 1; i < N - 1; ++i) nd.v[i] = ptx_subc_cc3(0u, d.v[i]);
+            nd.v[N - 1] = ptx_subc3(0u, d.v[N - 1]);
+            Fe<P> xa, xc;
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                v.v[i] = borrow ? u.v[i] : v.v[i];
+                u.v[i] = borrow ? nd.v[i] : d.v[i];
+                xa.v[i] = borrow ? x2.v[i] : x1.v[i];
+                xc.v[i] = borrow ? x1.v[i] : x2.v[i];
             }
+            x1 = fe_sub(xa, xc);
+            x2 = xc;
         }
+        // u is even and not zero: strip up to 31 trailing zero bits
+        uint32_t s = u.v[0] ? (uint32_t)(__ffs((int)u.v[0]) - 1) : 31u;
+        if (s > 31u) s = 31u;
+#pragma unroll
+        for (int i = 0; i < N - 1; ++i) u.v[i] = __funnelshift_r(u.v[i], u.v[i + 1], s);
+        u.v[N - 1] >>= s;
+        fe_div_pow2(x1, s);
     }
     // u = v = 1 = x1 (a R): x1 is (a R)^-1 as a plain residue; the Montgomery form of 1/a is that times R^2
     return mont_mul(mont_mul(x1, fe_r2<P>()), fe_r2<P>());

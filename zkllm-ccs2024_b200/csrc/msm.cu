@@ -19,6 +19,7 @@
 //      of 8 buckets, then Horner over the windows.
 //
 // The m*n*144-byte product array of the reference is never formed.
+#include "comm.cuh"
 #include "frutil.cuh"
 #include "g1.cuh"
 #include "hostfr.hpp"
@@ -801,6 +802,48 @@ int zkb_commit_i32_method(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d
     Scratch scratch(s);
     return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
                              reinterpret_cast<G1Jac*>(d_out), scratch, s, method);
+}
+
+// Rows [begin, end) of rank `rank` when m rows are dealt out in contiguous blocks; the first m % world ranks take one more.
+static void row_block(size_t m, int world, int rank, size_t* begin, size_t* end) {
+    const size_t base = m / world, extra = m % world;
+    *begin = (size_t)rank * base + ((size_t)rank < extra ? (size_t)rank : extra);
+    *end = *begin + base + ((size_t)rank < extra ? 1 : 0);
+}
+
+int zkb_commit_i32_sharded(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars_local, size_t rows_local,
+                           size_t rows_total, zkb_g1_t* d_out_all, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    const int world = comm_world(), rank = comm_rank();
+    if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
+    if (n_gen == 0) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
+    size_t begin, end;
+    row_block(rows_total, world, rank, &begin, &end);
+    if (rows_local != end - begin) return fail(ZKB_ERR_DIM, "commit: this rank's row count does not match its block of the rows");
+    if (rows_total == 0) return ZKB_OK;
+    G1Jac* out = reinterpret_cast<G1Jac*>(d_out_all);
+    Scratch scratch(s);
+    if (rows_total % world == 0) {
+        // equal blocks: every rank commits into its slot of the result and the gather runs in place
+        if (rows_local)
+            ZKB_TRY(commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars_local, rows_local * n_gen,
+                                      out + begin, scratch, s));
+        return comm_allgather(out + begin, out, rows_local * sizeof(G1Jac), s);
+    }
+    const size_t max_rows = (rows_total + world - 1) / world;
+    G1Jac* send = scratch.get_n<G1Jac>(max_rows);
+    G1Jac* recv = scratch.get_n<G1Jac>(max_rows * world);
+    if (!send || !recv) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(send, 0, max_rows * sizeof(G1Jac), s));
+    if (rows_local)
+        ZKB_TRY(commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars_local, rows_local * n_gen, send, scratch, s));
+    ZKB_TRY(comm_allgather(send, recv, max_rows * sizeof(G1Jac), s));
+    for (int p = 0; p < world; ++p) {
+        size_t b, e;
+        row_block(rows_total, world, p, &b, &e);
+        if (e > b) ZKB_CUDA(cudaMemcpyAsync(out + b, recv + (size_t)p * max_rows, (e - b) * sizeof(G1Jac), cudaMemcpyDeviceToDevice, s));
+    }
+    return ZKB_OK;
 }
 
 int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,

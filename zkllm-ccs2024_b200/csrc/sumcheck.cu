@@ -8,6 +8,7 @@
 // finished by the last CTA of the same launch.  The host reads the sums once,
 // after the last round, assembles the polynomials and replays the verifier
 // checks (claim == p(0) + p(1)) that the reference makes between rounds.
+#include "comm.cuh"
 #include "frutil.cuh"
 #include "hostfr.hpp"
 
@@ -987,6 +988,117 @@ int zkb_inner_product_sumcheck(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t 
 int zkb_binary_sumcheck(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                         unsigned k, zkb_fr_t* h_proof, void* stream) {
     return legacy_sumcheck<2>(CFR(d_a), CFR(d_a), n, h_u, h_v, k, h_proof, as_stream(stream));
+}
+
+// ---- provers with the data dealt out over the ranks of the communicator (comm.cu) ----
+// eq(u[0..nbits); index): challenge j pairs with bit j of the index
+static hfr::H rank_weight(const zkb_fr_t* u, unsigned nbits, size_t index) {
+    hfr::H w = hfr::from_u64(1);
+    const hfr::H one = hfr::from_u64(1);
+    for (unsigned j = 0; j < nbits; ++j) {
+        const hfr::H uj = hfr::load(u[j]);
+        w = hfr::mul(w, ((index >> j) & 1) ? uj : hfr::sub(one, uj));
+    }
+    return w;
+}
+
+int zkb_zkfc_prove_sharded(const zkb_fr_t* d_X_local, const zkb_fr_t* d_W_local, const zkb_fr_t* d_Y,
+                           size_t B, size_t I_local, size_t O,
+                           const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
+                           zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    const int world = comm_world();
+    if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
+    if (world & (world - 1)) return fail(ZKB_ERR_ARG, "zkFC::prove: the number of ranks must be a power of two");
+    if (!B || !I_local || !O) return fail(ZKB_ERR_DIM, "zkFC::prove: empty dimension");
+    if (I_local & (I_local - 1)) return fail(ZKB_ERR_DIM, "zkFC::prove: a rank's share of the input dimension must be a power of two");
+    const unsigned kP = clog2((size_t)world), kL = clog2(I_local), kI = kL + kP, kB = clog2(B), kO = clog2(O);
+    const size_t block = 3 * (size_t)kL + 4;            // local round sums, surviving pair, X and W claims of the share
+    Scratch scratch(s);
+    Fr* d_part = scratch.get_n<Fr>(block + 1);          // + the claim on Y
+    Fr* d_all = scratch.get_n<Fr>(block * world);
+    Fr* y_rows = scratch.get_n<Fr>(B);
+    Fr* x_red = scratch.get_n<Fr>(I_local);
+    Fr* w_red = scratch.get_n<Fr>(I_local);
+    Fr* E_b = scratch.get_n<Fr>((size_t)1 << kB);
+    Fr* E_in = scratch.get_n<Fr>((size_t)1 << kL);
+    unsigned* ticket = scratch.get_n<unsigned>(4);
+    Fr* partial = scratch.get_n<Fr>((size_t)sm_count() * 4);
+    if (!d_part || !d_all || !y_rows || !x_red || !w_red || !E_b || !E_in || !ticket || !partial) return ZKB_ERR_CUDA;
+    ZKB_TRY(build_eq_table(h_u_batch, kB, E_b, s));
+    ZKB_TRY(build_eq_table(h_u_input + kP, kL, E_in, s));   // the challenges above the rank's own index bits
+    if (kO) ZKB_TRY(partial_me_device(CFR(d_Y), B * O, B, O, 1, h_u_output, kO, y_rows, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(y_rows, d_Y, B * 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(B, kThreads, 4), kThreads, 0, s, y_rows, E_b, B, partial, ticket, d_part + block, 0u);
+    if (kB) ZKB_TRY(partial_me_device(CFR(d_X_local), B * I_local, 1, B, I_local, h_u_batch, kB, x_red, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(x_red, d_X_local, I_local * 32, cudaMemcpyDeviceToDevice, s));
+    if (kO) ZKB_TRY(partial_me_device(CFR(d_W_local), I_local * O, I_local, O, 1, h_u_output, kO, w_red, scratch, s));
+    else ZKB_CUDA(cudaMemcpyAsync(w_red, d_W_local, I_local * 32, cudaMemcpyDeviceToDevice, s));
+    // local round r uses the challenge h_u_input[kI - 1 - r]
+    const Fr *fa = nullptr, *fb = nullptr;
+    ZKB_TRY(zkip_device(x_red, w_red, I_local, h_u_input + kP, kL, kL, d_part, scratch, s, &fa, &fb));
+    ZKB_CUDA(cudaMemcpyAsync(d_part + 3 * kL, fa, 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_CUDA(cudaMemcpyAsync(d_part + 3 * kL + 1, fb, 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(I_local, kThreads, 4), kThreads, 0, s, x_red, E_in, I_local, partial, ticket, d_part + 3 * kL + 2, 0u);
+    ZKB_LAUNCH(fr_dot_kernel, grid_for(I_local, kThreads, 4), kThreads, 0, s, w_red, E_in, I_local, partial, ticket, d_part + 3 * kL + 3, 0u);
+    ZKB_TRY(comm_allgather(d_part, d_all, block * 32, s));
+    std::vector<zkb_fr_t> all(block * world), claim(1);
+    ZKB_CUDA(cudaMemcpyAsync(all.data(), d_all, all.size() * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(claim.data(), d_part + block, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    // every rank: sums added, the last log2(world) rounds on the surviving pairs, the verifier's checks
+    const size_t zk_block = 3 * (size_t)kL + 2;
+    std::vector<zkb_fr_t> parts(zk_block * world);
+    for (int p = 0; p < world; ++p) memcpy(&parts[p * zk_block], &all[p * block], zk_block * 32);
+    ZKB_TRY(zkb_zkip_combine(parts.data(), (unsigned)world, kI, h_u_input, claim.data(), h_polys, &h_claims[1]));
+    hfr::H cx = hfr::zero(), cw = hfr::zero();
+    for (int p = 0; p < world; ++p) {
+        const hfr::H w = rank_weight(h_u_input, kP, (size_t)p);
+        cx = hfr::add(cx, hfr::mul(w, hfr::load(all[p * block + zk_block])));
+        cw = hfr::add(cw, hfr::mul(w, hfr::load(all[p * block + zk_block + 1])));
+    }
+    h_claims[0] = claim[0];
+    h_claims[2] = hfr::store(cx);
+    h_claims[3] = hfr::store(cw);
+    if (!hfr::eq(hfr::mul(cx, cw), hfr::load(h_claims[1]))) return fail(ZKB_ERR_VERIFY, "Claim does not match");
+    return ZKB_OK;
+}
+
+int zkb_tlookup_prove_sharded(const zkb_fr_t* d_S_local, const zkb_fr_t* d_table_local, const zkb_fr_t* d_m_local,
+                              size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                              const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                              zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    const int world = comm_world();
+    if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
+    if (world & (world - 1)) return fail(ZKB_ERR_ARG, "tLookup: the number of ranks must be a power of two");
+    if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
+        return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
+    if (N < (size_t)world) return fail(ZKB_ERR_DIM, "tLookup: more ranks than table entries");
+    const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN, kP = clog2((size_t)world);
+    if (kD > 32) return fail(ZKB_ERR_LIMIT, "tLookup: D above 2^32");
+    const unsigned rounds = kD - kP;
+    // a rank's challenges: u above its own index bits; v without the entries of the shared last rounds
+    std::vector<zkb_fr_t> vl;
+    for (unsigned i = 0; i < k1; ++i) vl.push_back(h_v[i]);
+    for (unsigned i = k1 + kP; i < kD; ++i) vl.push_back(h_v[i]);
+    if (vl.empty()) vl.resize(1);
+    const size_t block = 1 + 11 * (size_t)rounds + 5;
+    Scratch scratch(s);
+    Fr* d_part = scratch.get_n<Fr>(block);
+    Fr* d_all = scratch.get_n<Fr>(block * world);
+    if (!d_part || !d_all) return ZKB_ERR_CUDA;
+    const Fr* fin[5];
+    ZKB_TRY(tlookup_rounds_device(CFR(d_S_local), CFR(d_table_local), CFR(d_m_local), D / world, N / world, h_beta,
+                                  h_u + kP, vl.data(), rounds, d_part, fin, scratch, s));
+    for (int a = 0; a < 5; ++a)
+        ZKB_CUDA(cudaMemcpyAsync(d_part + 1 + 11 * (size_t)rounds + a, fin[a], 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_TRY(comm_allgather(d_part, d_all, block * 32, s));
+    std::vector<zkb_fr_t> all(block * world);
+    ZKB_CUDA(cudaMemcpyAsync(all.data(), d_all, all.size() * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return zkb_tlookup_combine(all.data(), (unsigned)world, D, N, h_alpha, h_beta, h_u, h_v, h_polys, h_final);
 }
 
 }  // extern "C"
