@@ -184,8 +184,8 @@ def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
     def tl():
         z.call("zkb_tlookup_range_indices", z._p(d_S.data_ptr()), z.i32(TL_LOW), z._p(d_idx.data_ptr()), z.sz(TL_D), sp)
         z.call("zkb_tlookup_prep", z._p(d_idx.data_ptr()), z.sz(TL_D), z.sz(TL_N), z._p(d_m.data_ptr()), sp)
-        z.call("zkb_tlookup_prove", z._p(d_S.data_ptr()), z._p(d_T.data_ptr()), z._p(d_m.data_ptr()), z.sz(TL_D), z.sz(TL_N),
-               z._p(alpha), z._p(beta), z._p(u), z._p(v), z._p(tpolys), z._p(tfinal), sp)
+        z.call("zkb_tlookup_prove_indexed", z._p(d_S.data_ptr()), z._p(d_idx.data_ptr()), z._p(d_T.data_ptr()), z._p(d_m.data_ptr()),
+               z.sz(TL_D), z.sz(TL_N), z._p(alpha), z._p(beta), z._p(u), z._p(v), z._p(tpolys), z._p(tfinal), sp)
 
     s = timed(tl)
     out["tlookup_prove"] = {"workload": "tLookupRange(-32768, 65536) prep + prove, 2^23 values", "seconds": s,

@@ -204,6 +204,15 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
                       size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                       const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                       zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* The same proof when the caller knows where each looked-up value sits in the table: d_indices[i]
+ * (may be NULL) claims table[d_indices[i]] == S[i], as tLookupRange::prep computes it
+ * (tlookup.cu:414-433).  A = 1/(S + beta) (tlookup.cu:50-62, 330) is then read from the N inverses
+ * of the table instead of D inversions, inside the first round; a value that is not at its
+ * claimed index is inverted on its own, so the transcript never depends on the indices. */
+int zkb_tlookup_prove_indexed(const zkb_fr_t* d_S, const uint32_t* d_indices, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
+                              size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                              const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                              zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
 /* The first `rounds` rounds of the same proof without the assembly of the round
  * polynomials and the verifier replay (tlookup.cu:281-322; no counterpart in the reference:
  * the building block of the multi-GPU split).  h_sums receives 1 + 11 * rounds values:
@@ -332,7 +341,8 @@ int zkb_comm_unique_id(unsigned char* id128);
 int zkb_comm_init(int rank, int world, const unsigned char* id128);
 int zkb_comm_info(int* rank, int* world);               /* world == 0: not initialised */
 int zkb_comm_destroy(void);
-/* d_recv[p * bytes_per_rank ...] = rank p's d_send; queued on the stream, no host synchronisation */
+/* d_recv[p * bytes_per_rank ...] = rank p's d_send; queued on the stream, no host synchronisation
+ * (no counterpart in the reference) */
 int zkb_comm_allgather(const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream);
 /* Commitment::commit_int (commitment.cu:31-58) with the rows dealt out in contiguous blocks: rank p
  * holds rows [p*m/P ..) (the first m % P ranks one row more) as int32, the generators are on

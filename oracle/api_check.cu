@@ -6,16 +6,17 @@
 // Inputs and challenges come from a fixed integer generator, so the two builds
 // print the same lines when the implementations agree.  Covered here are the
 // parts of the API that no stage driver reaches: zkip_stacked / zkFCStacked
-// (zkfc.cu:153-307), zkAttn / zkAttnStacked (zksoftmax.cu:222-320) and zkReLU
-// (zkrelu.cu:3-66).  Every
+// (zkfc.cu:153-307), zkAttn / zkAttnStacked (zksoftmax.cu:222-320), zkReLU
+// (zkrelu.cu:3-66), and FrTensor::split, Commitment::commit_int_multi, FrTensor::random*.  Every
 // prove() below throws if one of its verifier equations fails.
 //
-// usage: api_check <fcstacked|attn|attnstacked|relu>
+// usage: api_check <fcstacked|attn|attnstacked|relu|misc>
 // output: "poly<i> <coefficients>" per round polynomial, "final <Fr>", "ok 1".
 #include <iostream>
 #include <string>
 #include <vector>
 
+#include "commitment.cuh"
 #include "fr-tensor.cuh"
 #include "polynomial.cuh"
 #include "zkfc.cuh"
@@ -154,6 +155,59 @@ static int relu() {
     return 0;
 }
 
+// FrTensor::split with ragged windows (fr-tensor.cu:562-585), Commitment::commit_int_multi against
+// commit_int of each tensor (commitment.cu:60-77), FrTensor::random / random_int value ranges
+// (fr-tensor.cu:444-510).  The random draws differ from run to run, so only their ranges are printed.
+static int misc() {
+    Gen g(0x5EED0005);
+    FrTensor t = g.ints(37, 1 << 20);
+    for (uint window : {5u, 1u, 36u, 16u}) {
+        auto halves = t.split(window);
+        print_tensor(("out_split" + to_string(window) + "_0").c_str(), halves.first);
+        print_tensor(("out_split" + to_string(window) + "_1").c_str(), halves.second);
+    }
+    Commitment gens(8, G1Jacobian_generator);
+    gens *= g.ints(8, 1 << 30);
+    vector<FrTensor> ts;
+    ts.push_back(g.ints(16, 8000));
+    ts.push_back(g.ints(8, 8000));
+    ts.push_back(g.ints(24, 1 << 30));
+    G1TensorJacobian all = gens.commit_int_multi(ts);
+    cout << "out_multi_rows " << all.size << endl;
+    bool same = true;
+    uint row = 0;
+    for (auto& x : ts) {
+        G1TensorJacobian c = gens.commit_int(x);
+        for (uint i = 0; i < c.size; ++i, ++row) {
+            G1TensorJacobian diff = G1TensorJacobian(1, all(row)) - G1TensorJacobian(1, c(i));
+            const G1Jacobian_t d = diff(0u);
+            for (int k = 0; k < 12; ++k) same = same && d.z.val[k] == 0;   // the identity has Z = 0
+        }
+    }
+    cout << "ok_multi " << (same && row == all.size) << endl;
+    const uint bits = 12, n = 4096;
+    FrTensor ri = FrTensor::random_int(n, bits);
+    FrTensor shifted = ri + Fr_t{{1u << (bits - 1), 0, 0, 0, 0, 0, 0, 0}};
+    bool in_range = true, varied = false;
+    for (uint i = 0; i < n; ++i) {
+        const Fr_t x = shifted(i);
+        for (int k = 1; k < 8; ++k) in_range = in_range && x.val[k] == 0;
+        in_range = in_range && x.val[0] < (1u << bits);
+        varied = varied || x.val[0] != shifted(0u).val[0];
+    }
+    cout << "ok_random_int " << (in_range && varied) << endl;
+    FrTensor rf = FrTensor::random(n);
+    bool canonical = true, wide = false;
+    for (uint i = 0; i < n; ++i) {
+        const Fr_t x = rf(i);
+        canonical = canonical && x.val[7] < 1944954707u;
+        wide = wide || x.val[7] != 0;
+    }
+    cout << "ok_random " << (canonical && wide) << endl;
+    cout << "ok 1" << endl;
+    return 0;
+}
+
 int main(int argc, char** argv) {
     const string cmd = argc > 1 ? argv[1] : "";
     try {
@@ -161,7 +215,8 @@ int main(int argc, char** argv) {
         if (cmd == "attn") return attn();
         if (cmd == "attnstacked") return attn_stacked();
         if (cmd == "relu") return relu();
-        cerr << "usage: api_check <fcstacked|attn|attnstacked|relu>" << endl;
+        if (cmd == "misc") return misc();
+        cerr << "usage: api_check <fcstacked|attn|attnstacked|relu|misc>" << endl;
         return 2;
     } catch (const std::exception& e) {
         cout << "exception " << e.what() << endl;

@@ -214,15 +214,46 @@ def build(ctx: Ctx) -> list:
     return cases
 
 
+def fr_digest(hex_vals) -> str:
+    """SHA-256 of the values' canonical 32-byte little-endian encodings, concatenated"""
+    return hashlib.sha256(b"".join(int(h, 16).to_bytes(32, "little") for h in hex_vals)).hexdigest()
+
+
+def softmax_large_inputs(m: int, n: int, d: int) -> np.ndarray:
+    nrng = np.random.Generator(np.random.PCG64(78))
+    return np.rint(nrng.standard_normal(m * n) * (2.0 ** 32) * math.sqrt(d) * 1.5).astype(np.int64)
+
+
+def fullsize(ctx: Ctx) -> dict:
+    """Cases at the layer's own sizes, recorded as digests: the softmax row shift over 2048 columns with d = 4096
+    (zksoftmax.cu:20-32: a 2048-term left-to-right double-precision sum per row), its digits and table outputs."""
+    m, n, d = 16, 2048, 4096
+    X = softmax_large_inputs(m, n, d)
+    out = ctx.run("softmax", ctx.fr_file([R.int_to_fr(int(x)) for x in X]), m, n, d)
+    rec = {"m": m, "n": n, "d": d, "inputs": "tests/golden/make_golden.py: softmax_large_inputs (PCG64 seed 78)", "shift": out["shift"]}
+    for key in ("y", "xseg0", "xseg1", "xseg2", "yseg0", "yseg1"):
+        rec[key + "_sha256"] = fr_digest(out[key])
+    return {"softmax_16x2048_d4096": rec}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--harness", default=str(ROOT / "oracle" / "_ref" / "ref_harness"))
     ap.add_argument("--out", default=str(ROOT / "tests" / "golden" / "ref_golden.json"))
     ap.add_argument("--api-check", action="store_true", help="also record the output of oracle/_ref/api_check_ref")
+    ap.add_argument("--fullsize", action="store_true", help="only add the full-size digests to tests/golden/ref_fullsize.json")
     args = ap.parse_args()
+    if args.fullsize:
+        path = ROOT / "tests" / "golden" / "ref_fullsize.json"
+        gold = json.loads(path.read_text())
+        with tempfile.TemporaryDirectory() as tmp:
+            gold.update(fullsize(Ctx(args.harness, Path(tmp))))
+        path.write_text(json.dumps(gold, indent=1) + "\n")
+        print(f"updated {path}")
+        return
     if args.api_check:
         exe = ROOT / "oracle" / "_ref" / "api_check_ref"
-        for case in ("fcstacked", "attn", "attnstacked", "relu"):
+        for case in ("fcstacked", "attn", "attnstacked", "relu", "misc"):
             res = subprocess.run([str(exe), case], capture_output=True, text=True, check=True)
             keep = [ln for ln in res.stdout.splitlines() if ln.split(" ")[0].startswith(("poly", "final", "out", "ok"))]
             # a long line (a whole tensor) is kept as its key and the SHA-256 of its text

@@ -33,7 +33,7 @@ def run(exe: Path, case: str) -> list:
     return [squeeze(ln) for ln in res.stdout.splitlines() if ln.split(" ")[0].startswith(("poly", "final", "out", "ok"))]
 
 
-@pytest.mark.parametrize("case", ["fcstacked", "attn", "attnstacked", "relu"])
+@pytest.mark.parametrize("case", ["fcstacked", "attn", "attnstacked", "relu", "misc"])
 def test_class_api_matches_the_reference_build(case):
     assert OURS.exists(), "oracle/_build/api_check is missing: run make -C oracle api"
     ours = run(OURS, case)

@@ -135,6 +135,11 @@ def test_tlookup_against_cpp_oracle(dev, logD, logN):
     dev.call("zkb_tlookup_prove", z._p(dS), z._p(dT), z._p(dM), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u), z._p(v),
              z._p(polys), z._p(final), z._p(0))
     assert np.array_equal(polys, epolys) and np.array_equal(final, efinal)
+    # table positions given: the inverses come from the table's, same transcript
+    polys2, final2 = np.zeros_like(polys), np.zeros_like(final)
+    dev.call("zkb_tlookup_prove_indexed", z._p(dS), z._p(dI), z._p(dT), z._p(dM), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u),
+             z._p(v), z._p(polys2), z._p(final2), z._p(0))
+    assert np.array_equal(polys2, epolys) and np.array_equal(final2, efinal)
 
 
 def test_tlookup_full_size_verifies(dev):

@@ -90,14 +90,20 @@ def test_zkfc_prove_rejects_wrong_output(dev):
     assert e.value.code == z.ERR_VERIFY
 
 
-def _tlookup(dev, S, table, m, alpha, beta, u, v):
+def _tlookup(dev, S, table, m, alpha, beta, u, v, indices=None):
+    """indices: None = zkb_tlookup_prove; a list = zkb_tlookup_prove_indexed with those claimed table positions"""
     z = dev.z
     D, N = len(S), len(table)
     kD = R.ceil_log2(D)
     polys = np.zeros((max(4 * kD, 1), 8), dtype=np.uint32)
     final = np.zeros((1, 8), dtype=np.uint32)
-    dev.call("zkb_tlookup_prove", z._p(dev.fr(S)), z._p(dev.fr(table)), z._p(dev.fr(m)), z.sz(D), z.sz(N),
-             z._p(dev.hfr([alpha])), z._p(dev.hfr([beta])), z._p(dev.hfr(u)), z._p(dev.hfr(v)), z._p(polys), z._p(final), z._p(0))
+    if indices is None:
+        dev.call("zkb_tlookup_prove", z._p(dev.fr(S)), z._p(dev.fr(table)), z._p(dev.fr(m)), z.sz(D), z.sz(N),
+                 z._p(dev.hfr([alpha])), z._p(dev.hfr([beta])), z._p(dev.hfr(u)), z._p(dev.hfr(v)), z._p(polys), z._p(final), z._p(0))
+    else:
+        d_idx = z.DeviceBuffer.from_host(np.array(indices, dtype=np.uint32))
+        dev.call("zkb_tlookup_prove_indexed", z._p(dev.fr(S)), z._p(d_idx), z._p(dev.fr(table)), z._p(dev.fr(m)), z.sz(D), z.sz(N),
+                 z._p(dev.hfr([alpha])), z._p(dev.hfr([beta])), z._p(dev.hfr(u)), z._p(dev.hfr(v)), z._p(polys), z._p(final), z._p(0))
     p = R.fr_unpack(polys)[:4 * kD]
     return [p[4 * i:4 * i + 4] for i in range(kD)], R.fr_unpack(final)[0]
 
@@ -117,6 +123,43 @@ def test_tlookup_prove(dev, D, N, low):
     polys, final = _tlookup(dev, vals, table, m, alpha, beta, u, v)
     assert [[c % R.R_MOD for c in (p + [0, 0, 0, 0])[:4]] for p in exp_polys] == polys
     assert final == exp
+    # with the table positions given (inverses read from the table's), and with positions that are
+    # wrong, out of range or all the same (every value then inverted on its own): the same transcript
+    wrong = [rng.randrange(0, 2 * N) for _ in range(D)]
+    for indices in (idx, wrong, [0] * D, [i if k % 3 else 0xFFFFFFFF for k, i in enumerate(idx)]):
+        p2, f2 = _tlookup(dev, vals, table, m, alpha, beta, u, v, indices)
+        assert p2 == polys and f2 == final
+
+
+def test_tlookup_value_equal_to_minus_beta(dev):
+    """S + beta = 0 for some entries: the inverse is taken as 0 (tlookup.cu:50-62) on every path, so the
+    plain and the indexed prover agree with each other and with the oracle - whether the proof passes or not"""
+    z = dev.z
+    rng = random.Random(77)
+    D, N, low = 256, 16, -8
+    table = R.range_table(low, N)
+    vals = [R.int_to_fr(rng.randrange(low, low + N)) for _ in range(D)]
+    idx = R.range_indices(vals, low)
+    m = R.tlookup_prep(idx, N)
+    alpha, beta = rng.randrange(R.R_MOD), (-vals[5]) % R.R_MOD
+    u, v = rand_fr(rng, 8), rand_fr(rng, 8)
+    outcomes = []
+    for indices in (None, idx):
+        try:
+            outcomes.append(_tlookup(dev, vals, table, m, alpha, beta, u, v, indices))
+        except z.ZkbError as e:
+            outcomes.append(("error", e.msg))
+    try:
+        exp_polys = []
+        exp = R.tlookup_prove(vals, table, m, alpha, beta, u, v, exp_polys)
+        oracle = ([[c % R.R_MOD for c in (p + [0, 0, 0, 0])[:4]] for p in exp_polys], exp)
+    except Exception as e:      # the oracle raises the reference's message
+        oracle = ("error", str(e))
+    assert outcomes[0] == outcomes[1]
+    if oracle[0] == "error":
+        assert outcomes[0][0] == "error" and oracle[1] in outcomes[0][1]
+    else:
+        assert outcomes[0] == oracle
 
 
 def test_tlookup_bad_multiplicities_fail(dev):

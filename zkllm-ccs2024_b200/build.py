@@ -25,15 +25,23 @@ NVCC_FLAGS = [
 ]
 
 
-def _headers_mtime() -> float:
-    hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.hpp")) + [HERE.parent / "include" / "zkllm_b200.h"]
-    return max(h.stat().st_mtime for h in hdrs)
+def _deps_mtime(path: Path, seen=None) -> float:
+    """newest modification time among a source file and the local headers it includes, directly or not"""
+    import re
+    seen = set() if seen is None else seen
+    if path in seen or not path.exists():
+        return 0.0
+    seen.add(path)
+    newest = path.stat().st_mtime
+    for inc in re.findall(r'^\s*#\s*include\s+"([^"]+)"', path.read_text(), flags=re.M):
+        newest = max(newest, _deps_mtime((path.parent / inc).resolve(), seen))
+    return newest
 
 
 def _compile(src: str, force: bool, verbose: bool) -> str:
     obj = BUILD / (src + ".o")
     srcp = CSRC / src
-    if not force and obj.exists() and obj.stat().st_mtime > max(srcp.stat().st_mtime, _headers_mtime()):
+    if not force and obj.exists() and obj.stat().st_mtime > _deps_mtime(srcp):
         return f"up to date: {src}"
     cmd = ["nvcc", *NVCC_FLAGS, "-c", str(srcp), "-o", str(obj)]
     if verbose:

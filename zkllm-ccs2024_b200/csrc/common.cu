@@ -37,13 +37,20 @@ void profile_begin(const char* name, cudaStream_t s) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
     ProfRec r;
     r.name = name;
-    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+    r.e0 = r.e1 = nullptr;
+    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) {
+        // keep begin/end paired: a record without events is skipped by profile_end and the reader
+        if (r.e0) cudaEventDestroy(r.e0);
+        r.e0 = r.e1 = nullptr;
+        g_prof.push_back(r);
+        return;
+    }
     cudaEventRecord(r.e0, s);
     g_prof.push_back(r);
 }
 void profile_end(cudaStream_t s) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
-    if (!g_prof.empty()) cudaEventRecord(g_prof.back().e1, s);
+    if (!g_prof.empty() && g_prof.back().e1) cudaEventRecord(g_prof.back().e1, s);
 }
 
 int sm_count() {
@@ -56,6 +63,26 @@ int sm_count() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+SideStream* side_stream() {
+    static SideStream table[64];
+    static bool made[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { fail(ZKB_ERR_CUDA, "side stream: no current device"); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!made[dev]) {
+        SideStream& t = table[dev];
+        if (cudaStreamCreateWithFlags(&t.st, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) {
+            fail(ZKB_ERR_CUDA, "side stream: cannot create stream or events");
+            return nullptr;
+        }
+        made[dev] = true;
+    }
+    return &table[dev];
 }
 
 // Keep freed scratch blocks cached in the device's stream-ordered pool: with the
@@ -127,7 +154,7 @@ int zkb_profile_enable(int on) {
 }
 int zkb_profile_reset(void) {
     std::lock_guard<std::mutex> lk(g_prof_mu);
-    for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    for (auto& r : g_prof) { if (r.e0) cudaEventDestroy(r.e0); if (r.e1) cudaEventDestroy(r.e1); }
     g_prof.clear();
     for (int i = 0; i < 3; ++i) { g_alloc_ns[i] = 0; g_alloc_calls[i] = 0; }
     return ZKB_OK;
@@ -139,7 +166,7 @@ int zkb_profile_read(char* buf, size_t cap) {
     std::map<std::string, std::pair<unsigned long long, double>> agg;
     for (auto& r : g_prof) {
         float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
+        if (r.e0 && r.e1 && cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
             auto& a = agg[r.name];
             a.first += 1;
             a.second += ms;

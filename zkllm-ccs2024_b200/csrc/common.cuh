@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <string>
 
 #include "../../include/zkllm_b200.h"
@@ -77,6 +78,19 @@ private:
     void* blocks_[kMax];
     int n_ = 0;
 };
+
+// A second stream per device for work that may run beside the caller's stream,
+// with the two events that fork from and join back into it.  Created on first use.
+// `busy` is held for the length of a call that uses the stream, so two host threads
+// on one device take turns.  Drain waits for the stream when a call leaves early.
+// Memory that work on the side stream touches is allocated from a Scratch bound to
+// that stream (stream-ordered allocations are only ordered on their own stream).
+struct SideStream { cudaStream_t st; cudaEvent_t fork, join; std::mutex busy; };
+struct Drain {
+    cudaStream_t st;
+    ~Drain() { cudaStreamSynchronize(st); }
+};
+SideStream* side_stream();   // nullptr (and the error text set) on failure
 
 inline unsigned div_up(size_t a, size_t b) { return (unsigned)((a + b - 1) / b); }
 

@@ -154,6 +154,23 @@ ZKB_DEV G1Xyzz xyzz_double_affine(const G1Aff& q) {
     return r;
 }
 
+// 2 * p ("dbl-2008-s-1", a = 0): 6M + 3S
+ZKB_DEV G1Xyzz xyzz_double(const G1Xyzz& p) {
+    if (xyzz_is_identity(p)) return p;
+    const Fq u = fq_dbl(p.y);
+    const Fq v = fq_sqr(u);
+    const Fq w = fq_mul(u, v);
+    const Fq s = fq_mul(p.x, v);
+    const Fq xx = fq_sqr(p.x);
+    const Fq m = fq_add(fq_dbl(xx), xx);
+    G1Xyzz r;
+    r.x = fq_sub(fq_sqr(m), fq_dbl(s));
+    r.y = fq_sub(fq_mul(m, fq_sub(s, r.x)), fq_mul(w, p.y));
+    r.zz = fq_mul(v, p.zz);
+    r.zzz = fq_mul(w, p.zzz);
+    return r;
+}
+
 // XYZZ + affine.  Handles identity operands, P + P and P + (-P).
 ZKB_DEV G1Xyzz xyzz_add_mixed(const G1Xyzz& p, const G1Aff& q) {
     if (g1_aff_is_identity(q)) return p;

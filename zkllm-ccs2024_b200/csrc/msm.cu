@@ -24,7 +24,6 @@
 #include "g1.cuh"
 #include "hostfr.hpp"
 
-#include <mutex>
 #include <vector>
 
 namespace zkb {
@@ -751,35 +750,6 @@ __global__ void me_open_tail_rows_kernel(const Fr* __restrict__ S, const Fr* __r
         else { if (!(j & 1) && j + 1 < len) sc = fr_load(St + j + 1); else live = false; }
         fr_store(rows + x, live ? fr_mmul(sc, fr_load(Wt + (size_t)t * c + b)) : fr_zero());
     }
-}
-
-// A second stream per device for work that may run beside the caller's stream,
-// with the two events that fork from and join back into it.  Created on first use.
-// `busy` is held for the length of a call that uses the stream, so two host threads
-// on one device take turns.  Drain waits for the stream when a call leaves early.
-struct SideStream { cudaStream_t st; cudaEvent_t fork, join; std::mutex busy; };
-struct Drain {
-    cudaStream_t st;
-    ~Drain() { cudaStreamSynchronize(st); }
-};
-static SideStream* side_stream() {
-    static SideStream table[64];
-    static bool made[64] = {};
-    static std::mutex mu;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { fail(ZKB_ERR_CUDA, "side stream: no current device"); return nullptr; }
-    std::lock_guard<std::mutex> lk(mu);
-    if (!made[dev]) {
-        SideStream& t = table[dev];
-        if (cudaStreamCreateWithFlags(&t.st, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) {
-            fail(ZKB_ERR_CUDA, "side stream: cannot create stream or events");
-            return nullptr;
-        }
-        made[dev] = true;
-    }
-    return &table[dev];
 }
 
 }  // namespace zkb

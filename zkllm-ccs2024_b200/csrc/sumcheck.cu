@@ -156,47 +156,91 @@ __global__ void __launch_bounds__(kThreads) zkip_round_kernel(const Fr* __restri
 // more than the arithmetic.  `vs` holds the challenges of these rounds in round
 // order (Montgomery form); wa/wb are two ping-pong buffers of `half` entries each.
 static constexpr size_t kZkipTailHalf = 512;
-__global__ void __launch_bounds__(1024) zkip_tail_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n_in, size_t half,
-                                                          Challenges vs, unsigned rounds, Fr* __restrict__ wa, Fr* __restrict__ wb,
-                                                          Fr* __restrict__ out) {
-    __shared__ Fr red3[3][32];
+static constexpr unsigned kZkipTailThreads = 512;
+
+// A sum of up to 2^32 field elements as a plain 288-bit integer: adding is one carry chain, the
+// reduction modulo r happens once per sum instead of once per addition.
+struct Wide9 { uint32_t l[9]; };
+ZKB_DEV void wide_zero(Wide9& w) {
+#pragma unroll
+    for (int i = 0; i < 9; ++i) w.l[i] = 0u;
+}
+ZKB_DEV void wide_add_fr(Wide9& w, const Fr& a) {
+    ptx_add_cc(w.l[0], a.v[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) ptx_addc_cc(w.l[i], a.v[i]);
+    ptx_addc(w.l[8], 0u);
+}
+ZKB_DEV void wide_add(Wide9& w, const Wide9& o) {
+    ptx_add_cc(w.l[0], o.l[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) ptx_addc_cc(w.l[i], o.l[i]);
+    ptx_addc(w.l[8], o.l[8]);
+}
+ZKB_DEV Wide9 wide_shfl_down(const Wide9& w, int off) {
+    Wide9 o;
+#pragma unroll
+    for (int i = 0; i < 9; ++i) o.l[i] = __shfl_down_sync(0xffffffffu, w.l[i], off);
+    return o;
+}
+// (w * R) mod r for w = lo + hi 2^256: the sum of raw Montgomery products (each carrying 1/R) as the
+// true field element.  mont_mul takes a first operand up to 2^256 when the second is below r.
+ZKB_DEV Fr wide_fix(const Wide9& w) {
+    Fr lo, hi = fr_zero();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo.v[i] = w.l[i];
+    hi.v[0] = w.l[8];
+    const Fr r2 = fe_r2<FrP>();
+    // lo R + hi 2^256 R = lo R + hi R^2
+    return fr_add(fr_mmul(lo, r2), fr_mmul(fr_mmul(hi, r2), r2));
+}
+
+__global__ void __launch_bounds__(kZkipTailThreads) zkip_tail_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n_in,
+                                                                      size_t half, Challenges vs, unsigned rounds,
+                                                                      Fr* __restrict__ wa, Fr* __restrict__ wb, Fr* __restrict__ out) {
+    __shared__ Wide9 stage[3][kZkipTailThreads / 32];
     const size_t stride = half;
     const Fr* ca = a;
     const Fr* cb = b;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (unsigned r = 0; r < rounds; ++r) {
         Fr* oa = wa + (r & 1) * stride;
         Fr* ob = wb + (r & 1) * stride;
         const Fr v_mont = vs.u[r];
-        Fr acc[3];
-        acc[0] = acc[1] = acc[2] = fr_zero();
-        for (size_t g = threadIdx.x; g < half; g += blockDim.x) {
-            const Fr a0 = g < n_in ? fr_load(ca + g) : fr_zero();
-            const Fr b0 = g < n_in ? fr_load(cb + g) : fr_zero();
-            const Fr a1 = g + half < n_in ? fr_load(ca + g + half) : fr_zero();
-            const Fr b1 = g + half < n_in ? fr_load(cb + g + half) : fr_zero();
-            const Fr da = fr_sub(a1, a0), db = fr_sub(b1, b0);
-            const Fr t0 = fr_mmul(a0, b0), t2 = fr_mmul(da, db);
-            const Fr t1 = fr_sub(fr_sub(fr_mmul(a1, b1), t0), t2);
-            acc[0] = fr_add(acc[0], t0);
-            acc[1] = fr_add(acc[1], t1);
-            acc[2] = fr_add(acc[2], t2);
-            fr_store(oa + g, fr_add(a0, fr_mmul(v_mont, da)));
-            fr_store(ob + g, fr_add(b0, fr_mmul(v_mont, db)));
-        }
-        // the three sums in one pass over the block (raw Montgomery sums; fixed up after the last round)
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        // warps that hold a pair of this round; the others only meet the barriers
+        const unsigned active_warps = (unsigned)((half + 31) / 32 < kZkipTailThreads / 32 ? (half + 31) / 32 : kZkipTailThreads / 32);
+        if ((unsigned)warp < active_warps) {
+            Wide9 acc[3];
+            wide_zero(acc[0]); wide_zero(acc[1]); wide_zero(acc[2]);
+            for (size_t g = threadIdx.x; g < half; g += (size_t)active_warps * 32) {
+                const Fr a0 = g < n_in ? fr_load(ca + g) : fr_zero();
+                const Fr b0 = g < n_in ? fr_load(cb + g) : fr_zero();
+                const Fr a1 = g + half < n_in ? fr_load(ca + g + half) : fr_zero();
+                const Fr b1 = g + half < n_in ? fr_load(cb + g + half) : fr_zero();
+                const Fr da = fr_sub(a1, a0), db = fr_sub(b1, b0);
+                const Fr t0 = fr_mmul(a0, b0), t2 = fr_mmul(da, db);
+                const Fr t1 = fr_sub(fr_sub(fr_mmul(a1, b1), t0), t2);
+                wide_add_fr(acc[0], t0);
+                wide_add_fr(acc[1], t1);
+                wide_add_fr(acc[2], t2);
+                fr_store(oa + g, fr_add(a0, fr_mmul(v_mont, da)));
+                fr_store(ob + g, fr_add(b0, fr_mmul(v_mont, db)));
+            }
 #pragma unroll
-        for (int q = 0; q < 3; ++q) {
-            acc[q] = warp_sum(acc[q]);
-            if (lane == 0) red3[q][warp] = acc[q];
+            for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+                for (int q = 0; q < 3; ++q) wide_add(acc[q], wide_shfl_down(acc[q], off));
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int q = 0; q < 3; ++q) stage[q][warp] = acc[q];
+            }
         }
         __syncthreads();                       // also orders this round's stores before the next round's loads
-        if (warp == 0) {
-#pragma unroll
-            for (int q = 0; q < 3; ++q) {
-                const Fr v = warp_sum(red3[q][lane]);
-                if (lane == 0) fr_store(out + 3 * r + q, v);
-            }
+        if (threadIdx.x < 3) {
+            Wide9 tot = stage[threadIdx.x][0];
+            for (unsigned w = 1; w < active_warps; ++w) wide_add(tot, stage[threadIdx.x][w]);
+            fr_store(out + 3 * r + threadIdx.x, wide_fix(tot));
         }
         __syncthreads();
         ca = oa;
@@ -204,8 +248,6 @@ __global__ void __launch_bounds__(1024) zkip_tail_kernel(const Fr* __restrict__ 
         n_in = half;
         half >>= 1;
     }
-    // sums of raw Montgomery products carry 1/R: one multiplication by R^2 each, all in parallel
-    if (threadIdx.x < 3 * rounds) fr_store(out + threadIdx.x, fr_mmul(fr_load(out + threadIdx.x), fe_r2<FrP>()));
 }
 
 // Queues the first `run` of the k rounds of zkip on `s` (round r uses h_u[k - 1 - r]).
@@ -256,7 +298,7 @@ static int zkip_device(const Fr* d_a, const Fr* d_b, size_t n, const zkb_fr_t* h
         Fr* wa = scratch.get_n<Fr>(2 * half);
         Fr* wb = scratch.get_n<Fr>(2 * half);
         if (!wa || !wb) return ZKB_ERR_CUDA;
-        ZKB_LAUNCH(zkip_tail_kernel, 1, 1024, 0, s, ca, cb, n_in, half, vs, rounds, wa, wb, d_polys + 3 * r);
+        ZKB_LAUNCH(zkip_tail_kernel, 1, kZkipTailThreads, 0, s, ca, cb, n_in, half, vs, rounds, wa, wb, d_polys + 3 * r);
         // the tail's round t writes to the half of the ping-pong pair with index t & 1
         ca = wa + ((rounds - 1) & 1) * half;
         cb = wb + ((rounds - 1) & 1) * half;
@@ -316,6 +358,84 @@ __global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restric
             fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
             fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
         }
+        if (eq.hi) {
+            const Fr eh = fr_load(eq.hi + (base >> eq.kl));
+            q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
+        }
+        acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
+    }
+    grid_sum_finish<5>(acc, partial, ticket, out, 0x7u, red);
+}
+
+// 1 / (s + beta) for a value the caller says sits at table index k: B[k] when T[k] == s (B holds the
+// inverses of the table), else the value's own inversion - the same field element either way, zero
+// mapped to zero (tlookup_inv_kernel, tlookup.cu:50-62).
+ZKB_DEV Fr tl_inverse_at(const Fr& s, uint32_t k, const Fr* __restrict__ T, const Fr* __restrict__ Bv, size_t N, const Fr& beta) {
+    if (k < N && fe_eq(fr_load(T + k), s)) return fr_load(Bv + k);
+    const Fr x = fr_add(s, beta);
+    if (fe_is_zero(x)) return x;
+    Fr one = fr_zero();
+    one.v[0] = 1u;
+    // x read as the Montgomery form of x / R: the inverse comes back as R^2 / x
+    return fr_mmul(fr_mmul(mont_inv<FrP>(x), one), one);
+}
+
+// First phase-1 round with A = 1 / (S + beta) formed on the fly from the table's inverses, so the
+// D-element array A is neither computed by D inversions nor written and read back.  Same five
+// sums and the same folded arrays as tl_phase1_kernel on (A, S).  Where both inverses of a pair
+// are non-zero, A0 (S0 + beta) = A1 (S1 + beta) = 1 exactly, which turns the three weighted
+// coefficients into
+//     t0 = e,    t2 = e (A1 - A0)(S1 - S0),    t1 = -t2,
+// one field product and one product by the difference S1 - S0 - a small integer for fixed-point
+// data, accumulated unreduced (LazyDot).  A pair with a zero inverse takes the general formulas.
+__global__ void __launch_bounds__(kThreads) tl_phase1_first_kernel(const Fr* __restrict__ S, const uint32_t* __restrict__ idx,
+                                                                    const Fr* __restrict__ T, const Fr* __restrict__ Bv, size_t N,
+                                                                    size_t half, Fr beta, Fr v_mont, EqTab eq, unsigned R,
+                                                                    Fr* __restrict__ nA, Fr* __restrict__ nS,
+                                                                    Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[5];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) acc[i] = fr_zero();
+    Fr one = fr_zero();
+    one.v[0] = 1u;
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    const size_t piece = (size_t)blockDim.x * R;          // never straddles a chunk of the low table
+    const size_t npieces = (half + piece - 1) / piece;
+    for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
+        Fr esum = fr_zero();                               // sum of the weights e R of the regular pairs
+        Fr g0 = fr_zero(), g1 = fr_zero(), g2 = fr_zero(); // general-formula pairs (each term carries 1/R)
+        LazyDot lazy;                                      // sum of (S1 - S0) * e (A1 - A0), carries 1/R after finish()
+        lazy.init();
+        const size_t base = c * piece;
+        for (size_t jj = threadIdx.x; jj < piece && base + jj < half; jj += blockDim.x) {
+            const size_t j = (base + jj) & lmask;
+            const size_t i = base + jj;
+            const Fr s0 = fr_load(S + i), s1 = fr_load(S + i + half);
+            const Fr a0 = tl_inverse_at(s0, idx[i], T, Bv, N, beta);
+            const Fr a1 = tl_inverse_at(s1, idx[i + half], T, Bv, N, beta);
+            const Fr e = fr_load(eq.lo + j);
+            const Fr c01 = fr_sub(a1, a0), c11 = fr_sub(s1, s0);
+            const Fr e01 = fr_mmul(c01, e);
+            if (!fe_is_zero(a0) && !fe_is_zero(a1)) {
+                esum = fr_add(esum, e);
+                lazy.add(c11, e01);
+            } else {
+                const Fr c10 = fr_add(s0, beta);
+                const Fr e00 = fr_mmul(a0, e);
+                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+                g0 = fr_add(g0, t0); g1 = fr_add(g1, t1); g2 = fr_add(g2, t2);
+            }
+            acc[3] = fr_add(acc[3], a0);
+            acc[4] = fr_add(acc[4], c01);
+            fr_store(nA + i, fr_add(a0, fr_mmul(v_mont, c01)));
+            fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
+        }
+        // e R -> e / R, the scale of the other weighted terms (fixed by R^2 after the grid sum)
+        Fr q0 = fr_add(fr_mmul(fr_mmul(esum, one), one), g0);
+        const Fr lz = lazy.finish();
+        Fr q1 = fr_sub(g1, lz), q2 = fr_add(g2, lz);
         if (eq.hi) {
             const Fr eh = fr_load(eq.hi + (base >> eq.kl));
             q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
@@ -710,30 +830,52 @@ int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y
     cudaStream_t s = as_stream(stream);
     if (!B || !I || !O) return fail(ZKB_ERR_DIM, "zkFC::prove: empty dimension");
     const unsigned kB = clog2(B), kI = clog2(I), kO = clog2(O);
+    // The pass over W (every weight once) runs on the caller's stream; the passes over X and Y and
+    // the eq tables, which are much smaller, run beside it on the second stream and join before the
+    // rounds.  What the second stream touches is allocated on that stream.
+    SideStream* side = side_stream();
+    if (!side) return ZKB_ERR_CUDA;
+    std::lock_guard<std::mutex> turn(side->busy);
     Scratch scratch(s);
+    Scratch side_mem(side->st);
+    Drain drain{side->st};   // destroyed first: nothing of the second stream outlives the buffers
     // results gathered on the device: [claim, claim_X, claim_W, polys...]
     Fr* d_res = scratch.get_n<Fr>(3 + 3 * (size_t)kI);
-    Fr* y_rows = scratch.get_n<Fr>(B);
-    Fr* x_red = scratch.get_n<Fr>(I);
     Fr* w_red = scratch.get_n<Fr>(I);
-    Fr* E_b = scratch.get_n<Fr>((size_t)1 << kB);
-    Fr* E_in = scratch.get_n<Fr>((size_t)1 << kI);
-    if (!d_res || !y_rows || !x_red || !w_red || !E_b || !E_in) return ZKB_ERR_CUDA;
-    ZKB_TRY(build_eq_table(h_u_batch, kB, E_b, s));
-    ZKB_TRY(build_eq_table(h_u_input, kI, E_in, s));
-    // claim = Y(u_batch, u_output): row dots with eq(u_output), then eq(u_batch)
-    if (kO) ZKB_TRY(partial_me_device(CFR(d_Y), B * O, B, O, 1, h_u_output, kO, y_rows, scratch, s));
-    else ZKB_CUDA(cudaMemcpyAsync(y_rows, d_Y, B * 32, cudaMemcpyDeviceToDevice, s));
     unsigned* ticket = scratch.get_n<unsigned>(4);
     Fr* partial = scratch.get_n<Fr>((size_t)sm_count() * 4);
-    if (!ticket || !partial) return ZKB_ERR_CUDA;
+    Fr* y_rows = side_mem.get_n<Fr>(B);
+    Fr* x_red = side_mem.get_n<Fr>(I);
+    Fr* E_b = side_mem.get_n<Fr>((size_t)1 << kB);
+    Fr* E_in = side_mem.get_n<Fr>((size_t)1 << kI);
+    Fr* d_claim = side_mem.get_n<Fr>(1);
+    unsigned* side_ticket = side_mem.get_n<unsigned>(4);
+    Fr* side_partial = side_mem.get_n<Fr>((size_t)sm_count() * 4);
+    if (!d_res || !w_red || !ticket || !partial || !y_rows || !x_red || !E_b || !E_in || !d_claim || !side_ticket || !side_partial)
+        return ZKB_ERR_CUDA;
+    // the caller's inputs are ready at this point of the caller's stream
+    ZKB_CUDA(cudaEventRecord(side->fork, s));
+    ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
+    {
+        cudaStream_t t = side->st;
+        ZKB_TRY(build_eq_table(h_u_batch, kB, E_b, t));
+        ZKB_TRY(build_eq_table(h_u_input, kI, E_in, t));
+        // claim = Y(u_batch, u_output): row dots with eq(u_output), then eq(u_batch)
+        if (kO) ZKB_TRY(partial_me_device(CFR(d_Y), B * O, B, O, 1, h_u_output, kO, y_rows, side_mem, t));
+        else ZKB_CUDA(cudaMemcpyAsync(y_rows, d_Y, B * 32, cudaMemcpyDeviceToDevice, t));
+        ZKB_CUDA(cudaMemsetAsync(side_ticket, 0, 16, t));
+        ZKB_LAUNCH(fr_dot_kernel, grid_for(B, kThreads, 4), kThreads, 0, t, y_rows, E_b, B, side_partial, side_ticket, d_claim, 0u);
+        // X_red = eq(u_batch)^T X
+        if (kB) ZKB_TRY(partial_me_device(CFR(d_X), B * I, 1, B, I, h_u_batch, kB, x_red, side_mem, t));
+        else ZKB_CUDA(cudaMemcpyAsync(x_red, d_X, I * 32, cudaMemcpyDeviceToDevice, t));
+        ZKB_CUDA(cudaEventRecord(side->join, t));
+    }
+    // W_red = W eq(u_output)
     ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
-    ZKB_LAUNCH(fr_dot_kernel, grid_for(B, kThreads, 4), kThreads, 0, s, y_rows, E_b, B, partial, ticket, d_res + 0, 0u);
-    // X_red = eq(u_batch)^T X ; W_red = W eq(u_output)
-    if (kB) ZKB_TRY(partial_me_device(CFR(d_X), B * I, 1, B, I, h_u_batch, kB, x_red, scratch, s));
-    else ZKB_CUDA(cudaMemcpyAsync(x_red, d_X, I * 32, cudaMemcpyDeviceToDevice, s));
     if (kO) ZKB_TRY(partial_me_device(CFR(d_W), I * O, I, O, 1, h_u_output, kO, w_red, scratch, s));
     else ZKB_CUDA(cudaMemcpyAsync(w_red, d_W, I * 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_CUDA(cudaStreamWaitEvent(s, side->join, 0));
+    ZKB_CUDA(cudaMemcpyAsync(d_res, d_claim, 32, cudaMemcpyDeviceToDevice, s));
     ZKB_TRY(zkip_device(x_red, w_red, I, h_u_input, kI, kI, d_res + 3, scratch, s));
     ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, x_red, E_in, I, partial, ticket, d_res + 1, 0u);
     ZKB_LAUNCH(fr_dot_kernel, grid_for(I, kThreads, 4), kThreads, 0, s, w_red, E_in, I, partial, ticket, d_res + 2, 0u);
@@ -779,15 +921,18 @@ int zkb_tlookup_range_table(int32_t low, size_t len, size_t table_size, zkb_fr_t
 // the inverses A = 1/(S + beta), B = 1/(T + beta), the sum of B * m into d_sums[0] and
 // 11 sums per round into d_sums[1 + 11 r].  fin[0..4] receive device pointers to
 // A, S, B, T, m as folded by the last round queued.
+// d_idx (optional): for every S[i] the table index the caller says holds it; with it the first
+// phase-1 round forms A from the N inverses of the table (tl_phase1_first_kernel).
 static int tlookup_rounds_device(const Fr* d_S, const Fr* d_table, const Fr* d_m, size_t D, size_t N, const zkb_fr_t* h_beta,
                                  const zkb_fr_t* h_u, const zkb_fr_t* h_v, unsigned run, Fr* d_sums, const Fr* fin[5],
-                                 Scratch& scratch, cudaStream_t s) {
+                                 Scratch& scratch, cudaStream_t s, const uint32_t* d_idx = nullptr) {
     const unsigned kD = clog2(D), kN = clog2(N), k1 = kD - kN;
-    // working arrays: A (D), then ping-pong halves
-    Fr* A = scratch.get_n<Fr>(D);
+    const bool fused_first = d_idx != nullptr && k1 >= 1 && run >= 1;
+    // working arrays: A (D) unless the first round forms it, then ping-pong halves
+    Fr* A = fused_first ? nullptr : scratch.get_n<Fr>(D);
     Fr* Bv = scratch.get_n<Fr>(N);
-    if (!A || !Bv) return ZKB_ERR_CUDA;
-    ZKB_TRY(zkb_fr_inv_shifted(reinterpret_cast<const zkb_fr_t*>(d_S), h_beta, reinterpret_cast<zkb_fr_t*>(A), D, s));
+    if ((!fused_first && !A) || !Bv) return ZKB_ERR_CUDA;
+    if (!fused_first) ZKB_TRY(zkb_fr_inv_shifted(reinterpret_cast<const zkb_fr_t*>(d_S), h_beta, reinterpret_cast<zkb_fr_t*>(A), D, s));
     ZKB_TRY(zkb_fr_inv_shifted(reinterpret_cast<const zkb_fr_t*>(d_table), h_beta, reinterpret_cast<zkb_fr_t*>(Bv), N, s));
     const size_t half0 = D > 1 ? D / 2 : 1;
     Fr* pp[2][5];
@@ -823,8 +968,13 @@ static int tlookup_rounds_device(const Fr* d_S, const Fr* d_table, const Fr* d_m
         const int pb = r & 1;
         if (r < k1) {
             const Fr v = dev_fr_mont(h_v[k1 - 1 - r]);
-            ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq, R,
-                       pp[pb][0], pp[pb][1], partial, ticket, out);
+            if (r == 0 && fused_first) {
+                ZKB_LAUNCH(tl_phase1_first_kernel, grid, kThreads, 0, s, cS, d_idx, d_table, Bv, N, half, beta, v, eq, R,
+                           pp[pb][0], pp[pb][1], partial, ticket, out);
+            } else {
+                ZKB_LAUNCH(tl_phase1_kernel, grid, kThreads, 0, s, cA, cS, half, beta, v, eq, R,
+                           pp[pb][0], pp[pb][1], partial, ticket, out);
+            }
             cA = pp[pb][0]; cS = pp[pb][1];
         } else if (half <= kTlTailHalf && kD - r <= kTlTailRounds) {
             // the remaining phase-2 rounds in one launch
@@ -892,6 +1042,13 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
                       size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                       const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                       zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    return zkb_tlookup_prove_indexed(d_S, nullptr, d_table, d_m, D, N, h_alpha, h_beta, h_u, h_v, h_polys, h_final, stream);
+}
+
+int zkb_tlookup_prove_indexed(const zkb_fr_t* d_S, const uint32_t* d_indices, const zkb_fr_t* d_table, const zkb_fr_t* d_m,
+                              size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
+                              const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                              zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
     cudaStream_t s = as_stream(stream);
     if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
         return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
@@ -901,7 +1058,7 @@ int zkb_tlookup_prove(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr
     Fr* d_sums = scratch.get_n<Fr>(1 + 11 * (size_t)kD);
     if (!d_sums) return ZKB_ERR_CUDA;
     const Fr* fin[5];
-    ZKB_TRY(tlookup_rounds_device(CFR(d_S), CFR(d_table), CFR(d_m), D, N, h_beta, h_u, h_v, kD, d_sums, fin, scratch, s));
+    ZKB_TRY(tlookup_rounds_device(CFR(d_S), CFR(d_table), CFR(d_m), D, N, h_beta, h_u, h_v, kD, d_sums, fin, scratch, s, d_indices));
     std::vector<zkb_fr_t> sums(1 + 11 * (size_t)kD);
     ZKB_CUDA(cudaMemcpyAsync(sums.data(), d_sums, sums.size() * 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));

@@ -32,15 +32,23 @@ FrTensor tLookup::prep(const uint* indices, const uint D) {
 // Runs the whole argument; the reference never appends to `proof` on this path
 // (tlookup.cu:324-370), so neither does this, but the round polynomials go to
 // the transcript sink when one is installed.
+// `indexed_by` (optional): a tensor of D range values whose offsets from `first` are the table indices of S.
 static Fr_t lookup_prove(const FrTensor& S, const FrTensor& T, const FrTensor& m, const Fr_t& alpha, const Fr_t& beta,
-                         const vector<Fr_t>& u, const vector<Fr_t>& v) {
+                         const vector<Fr_t>& u, const vector<Fr_t>& v, const FrTensor* indexed_by = nullptr, int first = 0) {
     const uint D = S.size, N = m.size;
     if (u.size() != ceilLog2(D)) throw std::runtime_error("u.size() != ceilLog2(D)");
     if (v.size() != ceilLog2(D)) throw std::runtime_error("v.size() != ceilLog2(D)");
     vector<Fr_t> polys(4 * u.size() + 1);
     Fr_t final_claim;
-    check(zkb_tlookup_prove(S.gpu_data, T.gpu_data, m.gpu_data, D, N, &alpha, &beta, u.empty() ? &kZero : u.data(),
-                            v.empty() ? &kZero : v.data(), polys.data(), &final_claim, nullptr));
+    if (indexed_by && D > N) {
+        DevU32 idx(D);
+        check(zkb_tlookup_range_indices(indexed_by->gpu_data, first, idx.p, D, nullptr));
+        check(zkb_tlookup_prove_indexed(S.gpu_data, idx.p, T.gpu_data, m.gpu_data, D, N, &alpha, &beta, u.empty() ? &kZero : u.data(),
+                                        v.empty() ? &kZero : v.data(), polys.data(), &final_claim, nullptr));
+    } else {
+        check(zkb_tlookup_prove(S.gpu_data, T.gpu_data, m.gpu_data, D, N, &alpha, &beta, u.empty() ? &kZero : u.data(),
+                                v.empty() ? &kZero : v.data(), polys.data(), &final_claim, nullptr));
+    }
     if (auto* sink = zkllm::transcript_sink()) {
         zkllm::Transcript::Entry e;
         e.label = "tLookup";
@@ -59,7 +67,7 @@ Fr_t tLookup::prove(const FrTensor& S, const FrTensor& m, const Fr_t& alpha, con
     const uint N = m.size;
     if (D != 1u << ceilLog2(D) || N != 1u << ceilLog2(N) || D % N != 0)
         throw std::runtime_error("D or N is not power of 2, or D is not divisible by N");
-    return lookup_prove(S, table, m, alpha, beta, u, v);
+    return lookup_prove(S, table, m, alpha, beta, u, v, is_range ? &S : nullptr, range_first);
 }
 
 static FrTensor range_table(int low, uint len) {
@@ -69,7 +77,10 @@ static FrTensor range_table(int low, uint len) {
     return t;
 }
 
-tLookupRange::tLookupRange(int low, uint len) : tLookup(range_table(low, len)), low(low) {}
+tLookupRange::tLookupRange(int low, uint len) : tLookup(range_table(low, len)), low(low) {
+    is_range = true;
+    range_first = low;
+}
 
 // vals[i] - low as a table index, for device ints
 static void int_indices(const int* d_vals, int low, uint* d_idx, uint D) {
@@ -141,5 +152,5 @@ Fr_t tLookupRangeMapping::prove(const FrTensor& S_in, const FrTensor& S_out, con
     if (N != 1u << ceilLog2(N) || D % N != 0) throw std::runtime_error("N is not power of 2, or D is not divisible by N");
     auto S_com = S_in + S_out * r;
     auto T_com = table + mapped_vals * r;
-    return lookup_prove(S_com, T_com, m, alpha, beta, u, v);
+    return lookup_prove(S_com, T_com, m, alpha, beta, u, v, &S_in, low);
 }

@@ -19,6 +19,12 @@ public:
     // S: looked-up values (D, a power of two, a multiple of the table size), m: multiplicities
     Fr_t prove(const FrTensor& S, const FrTensor& m, const Fr_t& alpha, const Fr_t& beta,
                const vector<Fr_t>& u, const vector<Fr_t>& v, vector<Polynomial>& transcript);
+
+protected:
+    // set by tLookupRange: entry j of the table is range_first + j, so the index of a looked-up
+    // value is known without a search (the prover then reads 1/(S + beta) from the table's inverses)
+    bool is_range = false;
+    int range_first = 0;
 };
 
 class tLookupRange : public tLookup {
