@@ -69,7 +69,12 @@ int zkb_bench_imad(int mode, unsigned iters, double* h_gops, void* stream);
 /* ---- device memory (FrTensor/G1Tensor ctors, dtors, copies:
  *      fr-tensor.cu:158-179, g1-tensor.cu:40-60,123-152) ------------------------- */
 int zkb_malloc(void** d_ptr, size_t bytes);   /* usable at once on any stream */
-int zkb_free(void* d_ptr);                    /* waits for the device first, like cudaFree */
+int zkb_free(void* d_ptr);                     /* waits for the device first, like cudaFree */
+/* Device memory of this library (zkb_malloc and the scratch memory of every call) comes from a
+ * stream-ordered pool the library owns, which keeps freed blocks for reuse (no counterpart in the reference,
+ * which calls cudaMalloc / cudaFree per tensor, fr-tensor.cu:158-179).  zkb_pool_trim waits for the device and
+ * returns cached memory to the driver down to keep_bytes. */
+int zkb_pool_trim(size_t keep_bytes);
 /* Page-locked host memory and copies that do not wait (no counterpart in the
  * reference, whose ioutils.cu:3-45 stages files through pageable memory): the host
  * buffer must stay untouched until zkb_sync on the same stream. */
@@ -349,6 +354,13 @@ int zkb_comm_allgather(const void* d_send, void* d_recv, size_t bytes_per_rank, 
  * every rank, d_out_all receives all rows_total commitments in row order on every rank. */
 int zkb_commit_i32_sharded(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars_local, size_t rows_local,
                            size_t rows_total, zkb_g1_t* d_out_all, void* stream);
+/* The same commitments with the COLUMNS dealt out instead: rank p holds a contiguous block of the
+ * generators and, for all `rows` rows, the scalars of those columns (rows x n_gen_local, int32).  Every rank
+ * commits its block (the per-call tables of the generators are then built for n / P generators only),
+ * the P partial commitments of each row are all-gathered and added in rank order; d_out receives the
+ * `rows` commitments on every rank - the same group elements as commitment.cu:31-58 on the whole matrix. */
+int zkb_commit_i32_colsharded(const zkb_g1_t* d_gens_local, size_t n_gen_local, const int32_t* d_scalars_local, size_t rows,
+                              zkb_g1_t* d_out, void* stream);
 /* zkFC::prove's body (zkfc.cu:61-87) with W dealt out by rows round-robin and X by the matching
  * columns: rank p holds X[:, p::P] (B x I_local) and W[p::P, :] (I_local x O), Y is on every rank.
  * h_u_input has log2(I_local * P) entries.  Outputs as zkb_zkfc_prove. */

@@ -43,6 +43,23 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(zkb):
         assert ref.any()
 
 
+def test_the_largest_sizes_fill_the_fixed_array_exactly(zkb):
+    """k = 24 uses all 4096 entries of the high table: one element more than half the limit (ragged), then the limit itself"""
+    z = zkb
+    rng = np.random.Generator(np.random.PCG64(24))
+    u = _rand_fr(rng, 24)
+    # small signed values as field elements: cheap to make on the host at this size
+    vals = rng.integers(-(1 << 30), 1 << 30, size=1 << 24, dtype=np.int64)
+    d_int = z.DeviceBuffer.from_host(vals)
+    d_a = z.DeviceBuffer(32 << 24)
+    z.call("zkb_fr_from_i64", z._p(d_int), z._p(d_a), z.sz(1 << 24), z._p(0))
+    for n in ((1 << 23) + 1, 1 << 24):
+        ref, got = np.zeros((1, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        z.call("zkb_fr_mle_eval", z._p(d_a), z.sz(n), z._p(u), z.u32(24), z._p(ref), z._p(0))
+        z.call("zkb_fr_mle_eval_noalloc", z._p(d_a), z.sz(n), z._p(u), z.u32(24), z._p(got), z._p(0))
+        assert np.array_equal(ref, got) and ref.any(), n
+
+
 def test_sizes_beyond_the_limit_are_refused(zkb):
     z = zkb
     rng = np.random.Generator(np.random.PCG64(1))

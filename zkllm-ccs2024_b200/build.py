@@ -114,6 +114,19 @@ def build_host(force: bool = False) -> Path:
     return HOST_LIB
 
 
+def reference_dir():
+    """Where the reference's sources are, or None: $ZKLLM_REFERENCE_DIR, else a directory named `reference` next to
+    this repository.  Only the drop-in check (build_reference_drivers) and the test checkers use it."""
+    cands = []
+    if os.environ.get("ZKLLM_REFERENCE_DIR"):
+        cands.append(Path(os.environ["ZKLLM_REFERENCE_DIR"]))
+    cands.append(HERE.parent.parent / "reference")
+    for c in cands:
+        if (c / "commitment.cu").exists():
+            return c
+    return None
+
+
 def build_reference_drivers(ref_dir: Path) -> bool:
     """Drop-in check: the reference's six driver sources, unmodified, compiled against
     host/ and linked with the two libraries, into bin/ref-drivers/.  Each source is
@@ -139,4 +152,5 @@ def build_reference_drivers(ref_dir: Path) -> bool:
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="--verbose-ptxas" in sys.argv)
     build_host(force="--force" in sys.argv)
-    build_reference_drivers(Path(os.environ.get("ZKLLM_REFERENCE_DIR", "/root/reference")))
+    if reference_dir() is not None:
+        build_reference_drivers(reference_dir())

@@ -1,7 +1,10 @@
 // Library plumbing: error text, device memory entry points, scratch pool.
 #include "common.cuh"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <chrono>
 #include <map>
@@ -65,6 +68,20 @@ int sm_count() {
     return cached[dev];
 }
 
+static bool nvtx_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("ZKLLM_NVTX");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+ApiRange::ApiRange(const char* name) : on(nvtx_enabled()) {
+    if (on) nvtxRangePushA(name);
+}
+ApiRange::~ApiRange() {
+    if (on) nvtxRangePop();
+}
+
 SideStream* side_stream() {
     static SideStream table[64];
     static bool made[64] = {};
@@ -85,19 +102,40 @@ SideStream* side_stream() {
     return &table[dev];
 }
 
-// Keep freed scratch blocks cached in the device's stream-ordered pool: with the
-// default release threshold (0) the pool returns memory to the driver at every
-// synchronisation and the next call pays for mapping it again.
-static void ensure_pool_keeps_memory() {
-    static bool done[64];
+// The library's own stream-ordered memory pool, one per device, created on first use.  Its release
+// threshold is unlimited, so freed blocks stay cached (with the default threshold of 0 a pool hands
+// its memory back to the driver at every synchronisation and the next call pays for mapping it again);
+// zkb_pool_trim gives cached memory back.  The device's default pool, which other users of
+// cudaMallocAsync in the same process share, is left as it is.
+static cudaMemPool_t library_pool() {
+    static cudaMemPool_t pools[64];
+    static bool made[64];
+    static std::mutex mu;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
-    cudaMemPool_t pool;
-    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!made[dev]) {
+        cudaMemPoolProps props;
+        memset(&props, 0, sizeof(props));
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
         unsigned long long thresh = ~0ull;
         cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh);
+        pools[dev] = pool;
+        made[dev] = true;
     }
-    done[dev] = true;
+    return pools[dev];
+}
+static cudaError_t pool_alloc(void** p, size_t bytes, cudaStream_t s) {
+    cudaMemPool_t pool = library_pool();
+    return pool ? cudaMallocFromPoolAsync(p, bytes, pool, s) : cudaMallocAsync(p, bytes, s);
 }
 
 // Host time spent inside the allocator calls, reported by zkb_profile_read as
@@ -126,10 +164,9 @@ void* Scratch::get(size_t bytes) {
         return nullptr;
     }
     if (bytes == 0) bytes = 16;
-    ensure_pool_keeps_memory();
     AllocClock clock(0);
     void* p = nullptr;
-    cudaError_t e = cudaMallocAsync(&p, bytes, stream_);
+    cudaError_t e = pool_alloc(&p, bytes, stream_);
     if (e != cudaSuccess) {
         cuda_fail(e, "cudaMallocAsync(scratch)");
         return nullptr;
@@ -189,15 +226,14 @@ int zkb_profile_read(char* buf, size_t cap) {
     return ZKB_OK;
 }
 
-// Device buffers come from the device's stream-ordered pool (which keeps freed
+// Device buffers come from the library's stream-ordered pool (which keeps freed
 // memory for reuse), allocated and released on the null stream.  zkb_malloc
 // returns memory that is usable at once on any stream; zkb_free first waits for
 // the whole device, like cudaFree, so work still running on any stream is safe.
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");
-    ensure_pool_keeps_memory();
     AllocClock clock(1);
-    ZKB_CUDA(cudaMallocAsync(d_ptr, bytes ? bytes : 16, (cudaStream_t)0));
+    ZKB_CUDA(pool_alloc(d_ptr, bytes ? bytes : 16, (cudaStream_t)0));
     ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     return ZKB_OK;
 }
@@ -206,6 +242,13 @@ int zkb_free(void* d_ptr) {
     AllocClock clock(2);
     ZKB_CUDA(cudaDeviceSynchronize());
     ZKB_CUDA(cudaFreeAsync(d_ptr, (cudaStream_t)0));
+    return ZKB_OK;
+}
+int zkb_pool_trim(size_t keep_bytes) {
+    cudaMemPool_t pool = library_pool();
+    if (!pool) return ZKB_OK;
+    ZKB_CUDA(cudaDeviceSynchronize());
+    ZKB_CUDA(cudaMemPoolTrimTo(pool, keep_bytes));
     return ZKB_OK;
 }
 int zkb_host_alloc(void** h_ptr, size_t bytes) {

@@ -54,13 +54,22 @@ void profile_end(cudaStream_t s);
         ZKB_LAUNCH_CHECK(#kernel);                                        \
     } while (0)
 
+// A named range around an entry point for timeline tools (NVTX push/pop), active only when the
+// environment variable ZKLLM_NVTX is 1 at the first call; otherwise one branch.
+struct ApiRange {
+    bool on;
+    explicit ApiRange(const char* name);
+    ~ApiRange();
+};
+#define ZKB_API_RANGE() ::zkb::ApiRange api_range__(__func__)
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
 // Scratch memory that lives for one entry-point call.  Blocks come from the
-// device's stream-ordered pool (cudaMallocAsync), so a call neither blocks the
+// library's stream-ordered pool (cudaMallocFromPoolAsync), so a call neither blocks the
 // device nor pays a cudaMalloc; every block is released in the destructor in
 // stream order.
 class Scratch {

@@ -771,6 +771,7 @@ int zkb_fr_unmont(const zkb_fr_t* d_a, zkb_fr_t* d_out, size_t n, void* stream) 
     return ZKB_OK;
 }
 int zkb_fr_inv_shifted(const zkb_fr_t* d_a, const zkb_fr_t* h_beta, zkb_fr_t* d_out, size_t n, void* stream) {
+    ZKB_API_RANGE();
     if (!n) return ZKB_OK;
     if (static_cast<const void*>(d_a) != static_cast<const void*>(d_out) && n >= (size_t)kThreads * kInvLong) {
         ZKB_LAUNCH(fr_inv_shifted_long_kernel, grid_for(n, kThreads * kInvLong, 8), kThreads, 0, as_stream(stream),
@@ -797,6 +798,7 @@ int zkb_fr_sum(const zkb_fr_t* d_a, size_t n, zkb_fr_t* h_out, void* stream) {
 }
 
 int zkb_fr_mle_eval(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (k > 32 || n == 0) return fail(ZKB_ERR_DIM, "Incompatible dimensions");
     const size_t full = (size_t)1 << k;
@@ -812,6 +814,7 @@ int zkb_fr_mle_eval(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned
 
 int zkb_fr_partial_me(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u, unsigned k,
                       size_t cur_dim, size_t window, zkb_fr_t* d_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (k > 31) return fail(ZKB_ERR_LIMIT, "partial_me: too many variables");
     if (cur_dim <= (((size_t)1 << k) >> 1)) return fail(ZKB_ERR_DIM, "cur_dim <= ((1<<u.size()) >> 1)");
@@ -847,6 +850,7 @@ int zkb_fr_partial_me_window(const zkb_fr_t* d_a, size_t n, const zkb_fr_t* h_u,
 int zkb_fr_mle_eval_2d(const zkb_fr_t* d_a, size_t d0, size_t d1,
                        const zkb_fr_t* h_u0, unsigned k0, const zkb_fr_t* h_u1, unsigned k1,
                        zkb_fr_t* h_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (k0 > 31 || k1 > 31) return fail(ZKB_ERR_LIMIT, "multi_dim_me: too many variables");
     if (d1 <= (((size_t)1 << k1) >> 1)) return fail(ZKB_ERR_DIM, "cur_dim <= ((1<<u.size()) >> 1)");
@@ -883,6 +887,7 @@ int zkb_fr_transpose(const zkb_fr_t* d_a, size_t M, size_t N, zkb_fr_t* d_out, v
     return ZKB_OK;
 }
 int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_t M, size_t N, size_t P, void* stream) {
+    ZKB_API_RANGE();
     if (!M || !P) return ZKB_OK;
     cudaStream_t s = as_stream(stream);
     if (N && M * N * P >= ((size_t)1 << 22)) {
@@ -969,19 +974,23 @@ static constexpr size_t kNoAllocElems = kNoAllocLo + kNoAllocHi + kNoAllocGrid +
 static __device__ __align__(256) zkb::Fr g_noalloc_scratch[kNoAllocElems];
 
 // The array's name is a host-side stand-in in host code, not a device address:
-// the address the kernels need is looked up once per device.
-static zkb::Fr* g_noalloc_addr[64];
+// the address the kernels need is looked up once per device and kept (atomically:
+// two host threads may make their first call at the same time; both look up the
+// same address).  A cudaDeviceReset in the same process invalidates the kept address.
+static std::atomic<zkb::Fr*> g_noalloc_addr[64];
 
 static int noalloc_scratch(zkb::Fr** out) {
     int dev = 0;
     ZKB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(ZKB_ERR_LIMIT, "zkb_fr_mle_eval_noalloc: device index above 63");
-    if (!g_noalloc_addr[dev]) {
+    zkb::Fr* addr = g_noalloc_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void* p = nullptr;
         ZKB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-        g_noalloc_addr[dev] = static_cast<zkb::Fr*>(p);
+        addr = static_cast<zkb::Fr*>(p);
+        g_noalloc_addr[dev].store(addr, std::memory_order_release);
     }
-    *out = g_noalloc_addr[dev];
+    *out = addr;
     return ZKB_OK;
 }
 

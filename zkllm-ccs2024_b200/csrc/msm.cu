@@ -547,24 +547,27 @@ static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d
 // are the pair-swapped scalars with every other entry zero), which leaves one
 // scalar product per pair, for g'.  Scalars are used by their raw limbs, as the
 // reference's G1Jacobian_mul reads them.  A lone last element pairs with nothing.
-__global__ void me_open_rows_kernel(const Fr* __restrict__ sc, size_t old_size, size_t new_size, Fr u_mont,
+// with_T = 0 leaves the T row out: rows = [T0, T1] (the caller derives T from the round before).
+__global__ void me_open_rows_kernel(const Fr* __restrict__ sc, size_t old_size, size_t new_size, Fr u_mont, unsigned with_T,
                                     Fr* __restrict__ rows, Fr* __restrict__ nsc) {
     const Fr zero = fr_zero();
+    Fr* row_T0 = rows + (with_T ? old_size : 0);
+    Fr* row_T1 = row_T0 + old_size;
     for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
         const size_t i0 = 2 * g, i1 = 2 * g + 1;
         const Fr s0 = fr_load(sc + i0);
-        fr_store(rows + i0, s0);
-        fr_store(rows + old_size + i0, zero);
+        if (with_T) fr_store(rows + i0, s0);
+        fr_store(row_T0 + i0, zero);
         if (i1 >= old_size) {
-            fr_store(rows + 2 * old_size + i0, zero);
+            fr_store(row_T1 + i0, zero);
             fr_store(nsc + g, fr_sub(s0, fr_mmul(u_mont, s0)));
             continue;
         }
         const Fr s1 = fr_load(sc + i1);
-        fr_store(rows + i1, s1);
-        fr_store(rows + old_size + i1, s0);        // T0: s_2j on g_2j+1
-        fr_store(rows + 2 * old_size + i0, s1);    // T1: s_2j+1 on g_2j
-        fr_store(rows + 2 * old_size + i1, zero);
+        if (with_T) fr_store(rows + i1, s1);
+        fr_store(row_T0 + i1, s0);        // T0: s_2j on g_2j+1
+        fr_store(row_T1 + i0, s1);        // T1: s_2j+1 on g_2j
+        fr_store(row_T1 + i1, zero);
         fr_store(nsc + g, fr_add(s0, fr_mmul(u_mont, fr_sub(s1, s0))));
     }
 }
@@ -752,6 +755,15 @@ __global__ void me_open_tail_rows_kernel(const Fr* __restrict__ S, const Fr* __r
     }
 }
 
+// out[row] = sum over the ranks p of part[p * rows + row], added in rank order
+__global__ void __launch_bounds__(128) g1_sum_ranks_kernel(const G1Jac* __restrict__ part, size_t rows, unsigned world, G1Jac* __restrict__ out) {
+    for (size_t row = blockIdx.x * (size_t)blockDim.x + threadIdx.x; row < rows; row += (size_t)gridDim.x * blockDim.x) {
+        G1Jac acc = g1_load(part + row);
+        for (unsigned p = 1; p < world; ++p) acc = g1_add_call(acc, g1_load(part + (size_t)p * rows + row));
+        g1_store(out + row, acc);
+    }
+}
+
 }  // namespace zkb
 
 using namespace zkb;
@@ -760,6 +772,7 @@ extern "C" {
 
 int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
                    zkb_g1_t* d_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     Scratch scratch(s);
     return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
@@ -768,6 +781,7 @@ int zkb_commit_i32(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalar
 
 int zkb_commit_i32_method(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
                           zkb_g1_t* d_out, int method, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     Scratch scratch(s);
     return commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens), n_gen, d_scalars, n_scalars,
@@ -783,6 +797,7 @@ static void row_block(size_t m, int world, int rank, size_t* begin, size_t* end)
 
 int zkb_commit_i32_sharded(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* d_scalars_local, size_t rows_local,
                            size_t rows_total, zkb_g1_t* d_out_all, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     const int world = comm_world(), rank = comm_rank();
     if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
@@ -816,8 +831,32 @@ int zkb_commit_i32_sharded(const zkb_g1_t* d_gens, size_t n_gen, const int32_t* 
     return ZKB_OK;
 }
 
+int zkb_commit_i32_colsharded(const zkb_g1_t* d_gens_local, size_t n_gen_local, const int32_t* d_scalars_local, size_t rows,
+                              zkb_g1_t* d_out, void* stream) {
+    ZKB_API_RANGE();
+    cudaStream_t s = as_stream(stream);
+    const int world = comm_world();
+    if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
+    if (rows == 0) return ZKB_OK;
+    if (rows > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many rows");
+    Scratch scratch(s);
+    G1Jac* mine = scratch.get_n<G1Jac>(rows);
+    G1Jac* all = scratch.get_n<G1Jac>(rows * (size_t)world);
+    if (!mine || !all) return ZKB_ERR_CUDA;
+    if (n_gen_local) {
+        ZKB_TRY(commit_i32_device(reinterpret_cast<const G1Jac*>(d_gens_local), n_gen_local, d_scalars_local, rows * n_gen_local, mine,
+                                  scratch, s));
+    } else {
+        ZKB_CUDA(cudaMemsetAsync(mine, 0, rows * sizeof(G1Jac), s));      // no columns here: the identity for every row
+    }
+    ZKB_TRY(comm_allgather(mine, all, rows * sizeof(G1Jac), s));
+    ZKB_LAUNCH(g1_sum_ranks_kernel, grid_for(rows, 128), 128, 0, s, all, rows, (unsigned)world, reinterpret_cast<G1Jac*>(d_out));
+    return ZKB_OK;
+}
+
 int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
                    zkb_g1_t* d_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
     if (n_scalars == 0) return ZKB_OK;
@@ -831,6 +870,7 @@ int zkb_commit_int(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scala
 
 int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_scalars, size_t n_scalars,
                         zkb_g1_t* h_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
     const size_t m = n_scalars / n_gen;
@@ -850,6 +890,7 @@ int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_s
 
 int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, size_t n_scalars,
                zkb_g1_t* d_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit - Incompatible dimensions");
     if (n_scalars == 0) return ZKB_OK;
@@ -860,6 +901,7 @@ int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, 
 
 int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
                 zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
     if (k > 62) return fail(ZKB_ERR_LIMIT, "Commitment::me_open - more than 62 rounds");
@@ -891,42 +933,91 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // (the Horner chain over 37 windows is latency-bound: once, not once per round).
     unsigned n_big = 0;
     for (size_t c = n; n_big < k && c > kTailLen; c = (c + 1) / 2) ++n_big;
+    // Only the first big round forms T = sum s_i g_i by an MSM.  With a = u (1 - u), b = (1 - u)^2, c = u^2 of a
+    // round, the next round's T is  a T + b T0 + c T1  (expand sum s'_j g'_j with the two folds above), so
+    // every later T is a fixed combination of the first T and the T0, T1 of the rounds before it: rounds
+    // after the first need two MSM rows instead of three, and all derived T come from one small MSM over
+    // those proof points at the end.  Like the fold and the tail this uses scalars modulo r.
     MsmShape big0;
     G1Jac* big_buckets = nullptr;
-    size_t per_round = 0;
+    G1Jac* big_points = nullptr;                 // T, T0, T1 of round 0, then T0, T1 of every later big round
+    size_t per_row = 0;
+    const size_t big_rows = n_big ? 3 + 2 * (size_t)(n_big - 1) : 0;
     if (n_big) {
         ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
-        per_round = msm_bucket_count(big0);
-        big_buckets = keep.get_n<G1Jac>(per_round * n_big);
-        if (!big_buckets) return ZKB_ERR_CUDA;
+        per_row = msm_bucket_count(big0) / 3;
+        big_buckets = keep.get_n<G1Jac>(per_row * big_rows);
+        big_points = keep.get_n<G1Jac>(big_rows);
+        if (!big_buckets || !big_points) return ZKB_ERR_CUDA;
     }
+    std::vector<zkb_fr_t> coef;                  // host copy of the combination scalars, alive until the last synchronisation
     unsigned r = 0;
+    size_t rows_done = 0;
     for (; r < n_big && rc == ZKB_OK; ++r) {
         const size_t nn = (cur + 1) / 2;
+        const unsigned n_rows = r == 0 ? 3u : 2u;
         const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
         Fr* rows_r = rows + 3 * used;
         G1Aff* bases_r = bases + used;
-        ZKB_LAUNCH(me_open_rows_kernel, grid_for(nn, 128), 128, 0, s, cs, cur, nn, u_mont, rows_r, sc[r & 1]);
+        ZKB_LAUNCH(me_open_rows_kernel, grid_for(nn, 128), 128, 0, s, cs, cur, nn, u_mont, r == 0 ? 1u : 0u, rows_r, sc[r & 1]);
         ZKB_TRY(to_affine_device(cg, bases_r, cur, s));
         ZKB_CUDA(cudaEventRecord(side->fork, s));
         ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
         {
             Scratch round(side->st);   // sorted lists of this round, released in the side stream's order
             MsmShape sh;
-            rc = msm_shape(cur, 3, kMaxWindows, true, big0.nseg, &sh);
-            if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_round * r, round, side->st);
+            rc = msm_shape(cur, n_rows, kMaxWindows, true, big0.nseg, &sh);
+            if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_row * rows_done, round, side->st);
         }
         ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
         cs = sc[r & 1];
         cg = gn[r & 1];
         used += cur;
         cur = nn;
+        rows_done += n_rows;
     }
     if (rc == ZKB_OK && n_big) {
         MsmShape all = big0;
-        all.m = 3 * (size_t)n_big;
+        all.m = big_rows;
         Scratch fin(side->st);
-        rc = msm_reduce_phase(big_buckets, all, d_proof, fin, side->st);
+        rc = msm_reduce_phase(big_buckets, all, big_points, fin, side->st);
+        if (rc == ZKB_OK) ZKB_CUDA(cudaMemcpyAsync(d_proof, big_points, 3 * sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
+        for (unsigned t = 1; t < n_big && rc == ZKB_OK; ++t)
+            ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t + 1, big_points + 3 + 2 * (size_t)(t - 1), 2 * sizeof(G1Jac),
+                                     cudaMemcpyDeviceToDevice, side->st));
+        if (rc == ZKB_OK && n_big > 1) {
+            // coefficient of every point of big_points[0 .. 2 n_big - 1) in T of round t = 1 .. n_big - 1
+            const size_t n_pts = 2 * (size_t)n_big - 1, n_der = n_big - 1;
+            std::vector<hfr::H> a(n_big), b(n_big), c(n_big);
+            for (unsigned i = 0; i < n_big; ++i) {
+                hfr::H u = hfr::load(h_u[i]);
+                for (int pass = 0; pass < 2; ++pass)      // a raw value of r or more names the same multiple as its residue
+                    if (hfr::geq(u, hfr::kMod)) { uint64_t bo; u = hfr::raw_sub(u, hfr::kMod, &bo); }
+                const hfr::H v = hfr::sub(hfr::from_u64(1), u);
+                a[i] = hfr::mul(u, v);
+                b[i] = hfr::mul(v, v);
+                c[i] = hfr::mul(u, u);
+            }
+            coef.assign(n_der * n_pts, hfr::store(hfr::zero()));
+            for (unsigned t = 1; t < n_big; ++t) {
+                zkb_fr_t* row = &coef[(size_t)(t - 1) * n_pts];
+                hfr::H run = hfr::from_u64(1);            // product of a_i for i in (j, t)
+                for (int j = (int)t - 1; j >= 0; --j) {
+                    row[1 + 2 * (size_t)j] = hfr::store(hfr::mul(b[j], run));
+                    row[2 + 2 * (size_t)j] = hfr::store(hfr::mul(c[j], run));
+                    run = hfr::mul(run, a[j]);
+                }
+                row[0] = hfr::store(run);
+            }
+            // everything of this step lives on the side stream, after its reduction
+            Fr* d_coef = fin.get_n<Fr>(coef.size());
+            G1Jac* d_der = fin.get_n<G1Jac>(n_der);
+            if (!d_coef || !d_der) return ZKB_ERR_CUDA;
+            ZKB_CUDA(cudaMemcpyAsync(d_coef, coef.data(), coef.size() * sizeof(Fr), cudaMemcpyHostToDevice, side->st));
+            rc = msm_rows<true>(big_points, n_pts, d_coef, n_der, kMaxWindows, d_der, fin, side->st);
+            for (unsigned t = 1; t < n_big && rc == ZKB_OK; ++t)
+                ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t, d_der + (t - 1), sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
+        }
     }
     // the remaining K rounds and the final generator as one MSM over this round's generators
     const unsigned K = k - r;

@@ -13,8 +13,8 @@
 //     addition per entry (Montgomery's trick: one inversion per 64 entries);
 //   * a row then needs ONE mixed addition per (window, group of four
 //     generators): W/4 additions per (scalar, generator) pair instead of one
-//     per 7-bit window, and no sorting, buckets or bucket reduction.  A running
-//     sum takes the windows from the top down with three doublings in between.
+//     per 7-bit window, and no sorting, buckets or bucket reduction.  The 3-bit
+//     windows are combined by doublings at the end.
 //
 // The tables cost ceil(n/4) * 4096 affine additions and 96 bytes per entry, so the
 // caller chooses this path only when the rows outweigh that (see commit_i32_device).
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(128) comb_quads_kernel(const G1Aff* __restrict
 struct CombShape {
     size_t m, n;          // rows, generators
     size_t n_quads;       // ceil(n / 4)
-    unsigned nseg;        // chains per row
+    unsigned nseg;        // chains per (row, window)
     unsigned qps;         // groups of four per chain
     int W;                // 3-bit windows
 };
@@ -214,58 +214,49 @@ ZKB_DEV unsigned comb_index(const int32_t* __restrict__ row, size_t n, size_t q,
     return f0 | (f1 << 3) | (f2 << 6) | (f3 << 9);
 }
 
-// Thread per (chain, row), rows fastest.  A chain is a run of `qps` groups of four generators; the
-// thread walks it once per window, from the top window down, with three doublings of
-// the running sum between windows (Horner), so what it leaves is the chain's whole
-// contribution to the row: sum_w 8^w sum_q table[q][digits_w(q)].  Groups whose four digits
-// are all zero (common in the top window) are skipped; the table entry of the next
-// step is requested from memory before the current addition starts.
+// Thread per (window, chain, row), rows fastest: one running sum over the chain's groups of four,
+// skipping groups whose four digits are all zero (common in the top windows).  The table
+// entry of the next step is requested from memory before the current addition starts.
 #ifndef ZKB_COMB_MINBLOCKS
 #define ZKB_COMB_MINBLOCKS 3
 #endif
-__device__ __noinline__ static G1Xyzz xyzz_double_call(const G1Xyzz& p) { return xyzz_double(p); }
-
 __global__ void __launch_bounds__(128, ZKB_COMB_MINBLOCKS) msm_comb_kernel(const G1Aff* __restrict__ table,
                                                                             const int32_t* __restrict__ scalars, CombShape sh,
                                                                             G1Jac* __restrict__ part) {
     const size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    const size_t total = (size_t)sh.nseg * sh.m;
+    const size_t total = (size_t)sh.W * sh.nseg * sh.m;
     if (t >= total) return;
     const size_t row = t % sh.m;
-    const unsigned seg = (unsigned)(t / sh.m);
+    const unsigned seg = (unsigned)((t / sh.m) % sh.nseg);
+    // dense low windows first, the sparse top windows fill the tail of the launch
+    const int w = (int)(t / (sh.m * sh.nseg));
     const unsigned long long bias = comb_bias(sh.W);
     const int32_t* srow = scalars + row * sh.n;
     // 16-byte loads of four scalars need n % 4 == 0 and an aligned matrix
     const bool vec = (sh.n & 3) == 0 && (reinterpret_cast<size_t>(scalars) & 15) == 0;
-    const size_t q_begin = (size_t)seg * sh.qps;
-    size_t q_end = q_begin + sh.qps;
+    size_t q = (size_t)seg * sh.qps;
+    size_t q_end = q + sh.qps;
     if (q_end > sh.n_quads) q_end = sh.n_quads;
+    // full groups can use the vector load; the ragged last group (n % 4 != 0) cannot
+    unsigned idx = kCombZeroIdx;
+    while (q < q_end && (idx = comb_index(srow, sh.n, q, w, bias, vec)) == kCombZeroIdx) ++q;
     G1Xyzz acc = xyzz_identity();
-#pragma unroll 1
-    for (int w = sh.W - 1; w >= 0; --w) {
-        if (w != sh.W - 1 && !xyzz_is_identity(acc)) {
-#pragma unroll 1
-            for (int d = 0; d < kCombBits; ++d) acc = xyzz_double_call(acc);
-        }
-        size_t q = q_begin;
-        unsigned idx = kCombZeroIdx;
+    while (q < q_end) {
+        const G1Aff p = g1_aff_load(table + q * kCombEntries + idx);
+        ++q;
         while (q < q_end && (idx = comb_index(srow, sh.n, q, w, bias, vec)) == kCombZeroIdx) ++q;
-        while (q < q_end) {
-            const G1Aff p = g1_aff_load(table + q * kCombEntries + idx);
-            ++q;
-            while (q < q_end && (idx = comb_index(srow, sh.n, q, w, bias, vec)) == kCombZeroIdx) ++q;
-            if (q < q_end) {
-                const char* nxt = reinterpret_cast<const char*>(table + q * kCombEntries + idx);
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt + 64));
-            }
-            acc = xyzz_add_mixed(acc, p);
+        if (q < q_end) {
+            const char* nxt = reinterpret_cast<const char*>(table + q * kCombEntries + idx);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt + 64));
         }
+        acc = xyzz_add_mixed(acc, p);
     }
     g1_store(part + t, xyzz_to_jac(acc));
 }
 
-// Sixteen lanes per row: the chains of the row added up (each lane a few, then a tree over the lanes).
+// Sixteen lanes per (row, window): the chains of the window added up (each lane a few, then a tree
+// over the lanes), times 8^w.
 ZKB_DEV G1Jac g1_shfl_down16(const G1Jac& p, int off) {
     G1Jac r;
 #pragma unroll
@@ -277,20 +268,37 @@ ZKB_DEV G1Jac g1_shfl_down16(const G1Jac& p, int off) {
     return r;
 }
 __device__ __noinline__ static G1Jac g1_add_comb_call(const G1Jac& p, const G1Jac& q) { return g1_add(p, q); }
+__device__ __noinline__ static G1Jac g1_double_comb_call(const G1Jac& p) { return g1_double(p); }
 
-__global__ void __launch_bounds__(128) msm_comb_reduce_kernel(const G1Jac* __restrict__ part, CombShape sh, G1Jac* __restrict__ out) {
+__global__ void __launch_bounds__(128) msm_comb_window_kernel(const G1Jac* __restrict__ part, CombShape sh, G1Jac* __restrict__ win) {
     const size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    const size_t row = t >> 4;
+    const size_t grp = t >> 4;
     const unsigned lane = (unsigned)(t & 15);
+    const bool valid = grp < sh.m * (size_t)sh.W;
+    const size_t row = valid ? grp % sh.m : 0;
+    const int w = valid ? (int)(grp / sh.m) : 0;
     G1Jac acc = g1_identity();
-    if (row < sh.m)
-        for (unsigned sg = lane; sg < sh.nseg; sg += 16) acc = g1_add_comb_call(acc, g1_load(part + (size_t)sg * sh.m + row));
+    if (valid)
+        for (unsigned sg = lane; sg < sh.nseg; sg += 16)
+            acc = g1_add_comb_call(acc, g1_load(part + ((size_t)w * sh.nseg + sg) * sh.m + row));
 #pragma unroll 1
     for (int off = 8; off > 0; off >>= 1) {
         const G1Jac other = g1_shfl_down16(acc, off);      // every lane of the warp takes part
         acc = g1_add_comb_call(acc, other);
     }
-    if (lane == 0 && row < sh.m) g1_store(out + row, acc);
+    if (lane == 0 && valid) {
+#pragma unroll 1
+        for (int d = 0; d < kCombBits * w; ++d) acc = g1_double_comb_call(acc);
+        g1_store(win + grp, acc);
+    }
+}
+
+__global__ void __launch_bounds__(128) msm_comb_sum_kernel(const G1Jac* __restrict__ win, CombShape sh, G1Jac* __restrict__ out) {
+    const size_t row = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (row >= sh.m) return;
+    G1Jac acc = g1_load(win + row);
+    for (int w = 1; w < sh.W; ++w) acc = g1_add(acc, g1_load(win + (size_t)w * sh.m + row));
+    g1_store(out + row, acc);
 }
 
 // Products of field elements (unit of the two cost estimates below).
@@ -300,20 +308,19 @@ static double comb_cost(size_t m, size_t n, int W) {
 }
 static size_t comb_table_bytes(size_t n) { return ((n + 3) / 4) * (size_t)kCombEntries * sizeof(G1Aff); }
 
-// Chains per row: all chains cost the same, so the launch should be a whole number of waves
-// (threads the device holds at once), with at least two of them and chains of at least 16 groups.
-static unsigned comb_segments(size_t m, size_t n_quads) {
+// Chains per (row, window): enough threads to fill the device, a whole number of waves
+// when the chains are long enough to choose.
+static unsigned comb_segments(size_t m, size_t n_quads, int W) {
     const size_t wave = (size_t)sm_count() * ZKB_COMB_MINBLOCKS * 128;
     unsigned best = 1;
-    double best_score = 0.0;
-    for (unsigned nseg = 1; nseg <= 512; ++nseg) {
-        if (nseg > 1 && n_quads / nseg < 16) break;
-        const size_t qps = (n_quads + nseg - 1) / nseg;
-        if ((n_quads + qps - 1) / qps != nseg) continue;          // this count leaves an empty last chain
-        const double waves = (double)(m * (size_t)nseg) / (double)wave;
+    double best_eff = 0.0;
+    for (unsigned nseg = 1; nseg <= 64; ++nseg) {
+        if (nseg > 1 && n_quads / nseg < 48) break;
+        const double waves = (double)(m * (size_t)W * nseg) / (double)wave;
         const double eff = waves / (double)(size_t)(waves + 0.999999);
+        // prefer at least two waves worth of threads; among those, the fullest last wave
         const double score = (waves >= 2.0 ? 1.0 : waves / 2.0) * eff;
-        if (score > best_score + 0.01) { best_score = score; best = nseg; }
+        if (score > best_eff + 1e-9) { best_eff = score; best = nseg; }
     }
     return best;
 }
@@ -326,22 +333,24 @@ static int msm_comb_rows(const G1Aff* bases, size_t n, const int32_t* d_scalars,
     CombShape sh;
     sh.m = m; sh.n = n; sh.W = W;
     sh.n_quads = (n + 3) / 4;
-    sh.nseg = comb_segments(m, sh.n_quads);
+    sh.nseg = comb_segments(m, sh.n_quads, W);
     sh.qps = (unsigned)((sh.n_quads + sh.nseg - 1) / sh.nseg);
     sh.nseg = (unsigned)((sh.n_quads + sh.qps - 1) / sh.qps);
     const size_t n_pad = sh.n_quads * 4, n_pairs = sh.n_quads * 2;
     G1Aff* singles = scratch.get_n<G1Aff>(n_pad * 8);
     G1Aff* pairs = scratch.get_n<G1Aff>(n_pairs * 64);
     G1Aff* table = scratch.get_n<G1Aff>(sh.n_quads * (size_t)kCombEntries);
-    const size_t n_chains = (size_t)sh.nseg * m;
+    const size_t n_chains = (size_t)W * sh.nseg * m;
     G1Jac* part = scratch.get_n<G1Jac>(n_chains);
-    if (!singles || !pairs || !table || !part) return ZKB_ERR_CUDA;
-    if ((n_chains + 127) / 128 > 0x7fffffffull || m > ((size_t)0x7fffffff << 3)) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
+    G1Jac* win = scratch.get_n<G1Jac>((size_t)W * m);
+    if (!singles || !pairs || !table || !part || !win) return ZKB_ERR_CUDA;
+    if ((n_chains + 127) / 128 > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
     ZKB_LAUNCH(comb_singles_kernel, div_up(n_pad, 128), 128, 0, s, bases, n, n_pad, singles);
     ZKB_LAUNCH(comb_pairs_kernel, div_up(n_pairs * 8, 128), 128, 0, s, singles, n_pairs, pairs);
     ZKB_LAUNCH(comb_quads_kernel, div_up(sh.n_quads * 64, 128), 128, 0, s, pairs, sh.n_quads, table);
     ZKB_LAUNCH(msm_comb_kernel, div_up(n_chains, 128), 128, 0, s, table, d_scalars, sh, part);
-    ZKB_LAUNCH(msm_comb_reduce_kernel, div_up(m * 16, 128), 128, 0, s, part, sh, d_out);
+    ZKB_LAUNCH(msm_comb_window_kernel, div_up(m * (size_t)W * 16, 128), 128, 0, s, part, sh, win);
+    ZKB_LAUNCH(msm_comb_sum_kernel, div_up(m, 128), 128, 0, s, win, sh, d_out);
     return ZKB_OK;
 }
 

@@ -184,11 +184,13 @@ ZKB_DEV Wide9 wide_shfl_down(const Wide9& w, int off) {
     return o;
 }
 // (w * R) mod r for w = lo + hi 2^256: the sum of raw Montgomery products (each carrying 1/R) as the
-// true field element.  mont_mul takes a first operand up to 2^256 when the second is below r.
+// true field element.
 ZKB_DEV Fr wide_fix(const Wide9& w) {
     Fr lo, hi = fr_zero();
 #pragma unroll
     for (int i = 0; i < 8; ++i) lo.v[i] = w.l[i];
+    fe_final_sub(lo);   // 2^256 < 3r: two conditional subtractions make lo canonical
+    fe_final_sub(lo);
     hi.v[0] = w.l[8];
     const Fr r2 = fe_r2<FrP>();
     // lo R + hi 2^256 R = lo R + hi R^2
@@ -790,6 +792,7 @@ extern "C" {
 
 int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
              const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (k == 0) { *h_final = *h_claim; return ZKB_OK; }
     if (n == 0) return fail(ZKB_ERR_DIM, "zkip: empty input");
@@ -827,6 +830,7 @@ int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y
                    size_t B, size_t I, size_t O,
                    const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
                    zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (!B || !I || !O) return fail(ZKB_ERR_DIM, "zkFC::prove: empty dimension");
     const unsigned kB = clog2(B), kI = clog2(I), kO = clog2(O);
@@ -893,6 +897,7 @@ int zkb_zkfc_prove(const zkb_fr_t* d_X, const zkb_fr_t* d_W, const zkb_fr_t* d_Y
 }
 
 int zkb_tlookup_prep(const uint32_t* d_indices, size_t D, size_t N, zkb_fr_t* d_m, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (!N) return ZKB_OK;
     Scratch scratch(s);
@@ -1049,6 +1054,7 @@ int zkb_tlookup_prove_indexed(const zkb_fr_t* d_S, const uint32_t* d_indices, co
                               size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                               const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                               zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (!D || !N || (D & (D - 1)) || (N & (N - 1)) || D % N)
         return fail(ZKB_ERR_DIM, "D or N is not power of 2, or D is not divisible by N");
@@ -1070,6 +1076,7 @@ int zkb_tlookup_prove_indexed(const zkb_fr_t* d_S, const uint32_t* d_indices, co
 int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,
                        const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                        zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     if (K < 1 || K > (unsigned)kMaxHadamard) return fail(ZKB_ERR_LIMIT, "multi_hadamard: between 1 and 6 tensors");
     if (N == 1) { *h_final = *h_claim; return ZKB_OK; }
@@ -1163,6 +1170,7 @@ int zkb_zkfc_prove_sharded(const zkb_fr_t* d_X_local, const zkb_fr_t* d_W_local,
                            size_t B, size_t I_local, size_t O,
                            const zkb_fr_t* h_u_batch, const zkb_fr_t* h_u_input, const zkb_fr_t* h_u_output,
                            zkb_fr_t* h_polys, zkb_fr_t* h_claims, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     const int world = comm_world();
     if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
@@ -1226,6 +1234,7 @@ int zkb_tlookup_prove_sharded(const zkb_fr_t* d_S_local, const zkb_fr_t* d_table
                               size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                               const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                               zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
     cudaStream_t s = as_stream(stream);
     const int world = comm_world();
     if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");

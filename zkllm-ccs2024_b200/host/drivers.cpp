@@ -36,6 +36,7 @@
 #include "rescaling.cuh"
 #include "zkfc.cuh"
 #include "zksoftmax.cuh"
+#include "zkllm_ext.hpp"
 
 namespace {
 
@@ -249,6 +250,11 @@ int run_batch(const Args& a) {
     const char* prof_env = std::getenv("ZKLLM_PROFILE");
     const bool profile = prof_env && prof_env[0] == '1';
     if (profile) zkb_profile_enable(1);
+    // generators, weights, commitments and the activations handed from stage to stage stay on the device
+    // (every file is still written); ZKLLM_RESIDENT=0 reads every file from disk again, as separate processes do
+    const char* res_env = std::getenv("ZKLLM_RESIDENT");
+    zkllm::set_resident_files(!(res_env && res_env[0] == '0'));
+    zkllm::ResidentStats before = zkllm::resident_stats();
     std::string line;
     while (std::getline(in, line)) {
         std::istringstream words(line);
@@ -263,6 +269,12 @@ int run_batch(const Args& a) {
         const auto t0 = std::chrono::steady_clock::now();
         const int rc = stage_table().at(stage).first(cmd);
         const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        const zkllm::ResidentStats now = zkllm::resident_stats();
+        cerr << "[files] " << stage << " loads from disk " << now.loads_from_disk - before.loads_from_disk << " ("
+             << (now.bytes_from_disk - before.bytes_from_disk) / 1048576 << " MiB), from the device "
+             << now.loads_from_device - before.loads_from_device << " (" << (now.bytes_from_device - before.bytes_from_device) / 1048576
+             << " MiB)" << endl;
+        before = now;
         cerr << "[batch] " << stage << (stage == "self-attn" || stage == "rmsnorm" ? " " + cmd[0] : "") << " " << secs << " s" << endl;
         if (profile) {
             std::vector<char> buf(1 << 16);

@@ -5,6 +5,7 @@
 #include <climits>
 #include <cstdlib>
 #include <cstring>
+#include <iostream>
 #include <mutex>
 #include <stdexcept>
 
@@ -21,6 +22,7 @@ void check(int rc) {
 namespace {
 std::mutex g_seed_mu;
 bool g_seeded = false;
+bool g_seeded_by_env = false;
 std::mt19937_64 g_seed_rng;
 bool g_env_checked = false;
 Transcript* g_sink = nullptr;
@@ -29,6 +31,7 @@ Transcript* g_sink = nullptr;
 void seed_challenges(uint64_t seed) {
     std::lock_guard<std::mutex> lk(g_seed_mu);
     g_seeded = true;
+    g_seeded_by_env = false;
     g_env_checked = true;
     g_seed_rng.seed(seed);
 }
@@ -40,17 +43,23 @@ void unseed_challenges() {
 void set_transcript_sink(Transcript* sink) { g_sink = sink; }
 Transcript* transcript_sink() { return g_sink; }
 
-// fills `out` with `words` 32-bit words from the seeded stream; false when unseeded
-static bool seeded_words(uint32_t* out, size_t words) {
+// fills `out` with `words` 32-bit words from the seeded stream; false when unseeded.
+// for_generators: the draw makes tensor values (FrTensor::random*, hence Commitment::random and
+// ppgen).  Those honour only a seed set by seed_challenges(): a seed left in the environment
+// must not make commitment generators with predictable discrete logarithms.
+static bool seeded_words(uint32_t* out, size_t words, bool for_generators = false) {
     std::lock_guard<std::mutex> lk(g_seed_mu);
     if (!g_env_checked) {
         g_env_checked = true;
         if (const char* e = std::getenv("ZKLLM_CHALLENGE_SEED")) {
             g_seeded = true;
+            g_seeded_by_env = true;
             g_seed_rng.seed(std::strtoull(e, nullptr, 0));
+            std::cerr << "zkllm: ZKLLM_CHALLENGE_SEED is set - verifier challenges are deterministic (testing only, not sound)"
+                      << std::endl;
         }
     }
-    if (!g_seeded) return false;
+    if (!g_seeded || (for_generators && g_seeded_by_env)) return false;
     for (size_t i = 0; i < words; ++i) out[i] = (uint32_t)g_seed_rng();
     return true;
 }
@@ -212,7 +221,7 @@ void FrTensor::save_long(const string& filename) const {
 // Host-side generators stand in for the reference's cuRAND kernels
 // (fr-tensor.cu:444-510); the streams were never reproducible there either.
 static void fill_random_words(vector<uint32_t>& words) {
-    if (zkllm::seeded_words(words.data(), words.size())) return;
+    if (zkllm::seeded_words(words.data(), words.size(), true)) return;
     std::random_device rd;
     std::mt19937_64 rng(rd());
     for (auto& w : words) w = (uint32_t)rng();

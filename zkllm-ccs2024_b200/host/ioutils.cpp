@@ -2,14 +2,98 @@
 // counts 32-bit as in the reference.  The reference stages the whole file in a
 // pageable buffer; here two page-locked 16 MiB buffers alternate, so reading (or
 // writing) a chunk overlaps the DMA of its neighbour.
+//
+// Resident files (no counterpart in the reference, off by default): a process that runs many
+// stages - `zkllm-driver batch` - can keep a device copy of every file it loads or saves
+// (zkllm::set_resident_files).  A later loadbin of the same file is then a device-to-device copy:
+// generators, weights and commitments are read from disk once per process, and an activation
+// saved by one stage is already on the device when the next stage loads it.  Every file is still
+// written and a cached copy is used only while the file's size, inode and modification time are
+// those seen when the copy was made, so files rewritten by another program are read again.
 #include "ioutils.cuh"
 
+#include <sys/stat.h>
+
 #include <cstdio>
+#include <cstdlib>
+#include <list>
+#include <map>
 #include <stdexcept>
 
 #include "zkllm_ext.hpp"
 
 namespace {
+
+struct FileId {
+    off_t size = 0;
+    ino_t ino = 0;
+    long long mtime_ns = 0;
+    bool operator==(const FileId& o) const { return size == o.size && ino == o.ino && mtime_ns == o.mtime_ns; }
+};
+bool file_id(const string& name, FileId* id) {
+    struct stat st;
+    if (stat(name.c_str(), &st) != 0) return false;
+    id->size = st.st_size;
+    id->ino = st.st_ino;
+    id->mtime_ns = (long long)st.st_mtim.tv_sec * 1000000000LL + st.st_mtim.tv_nsec;
+    return true;
+}
+
+struct Resident {
+    FileId id;
+    void* dev = nullptr;
+    size_t bytes = 0;
+    std::list<string>::iterator age;     // position in the least-recently-used list
+};
+struct ResidentFiles {
+    bool on = false;
+    size_t limit = (size_t)24 << 30, used = 0;
+    std::map<string, Resident> files;
+    std::list<string> lru;               // front = most recently used
+    zkllm::ResidentStats stats;
+
+    void drop(const string& name) {
+        auto it = files.find(name);
+        if (it == files.end()) return;
+        zkb_free(it->second.dev);
+        used -= it->second.bytes;
+        lru.erase(it->second.age);
+        files.erase(it);
+    }
+    // keeps a device copy of `bytes` bytes at d_src as the content of `name` (as it is on disk now)
+    void remember(const string& name, const void* d_src, size_t bytes) {
+        drop(name);
+        FileId id;
+        if (!file_id(name, &id) || (size_t)id.size != bytes || bytes > limit) return;
+        while (used + bytes > limit && !lru.empty()) drop(lru.back());
+        void* p = nullptr;
+        if (zkb_malloc(&p, bytes) != ZKB_OK) return;          // no room: simply not cached
+        if (zkb_memcpy_d2d(p, d_src, bytes, nullptr) != ZKB_OK || zkb_sync(nullptr) != ZKB_OK) { zkb_free(p); return; }
+        lru.push_front(name);
+        Resident r;
+        r.id = id; r.dev = p; r.bytes = bytes; r.age = lru.begin();
+        files[name] = r;
+        used += bytes;
+    }
+    // copies the cached content of `name` to d_dst when the file is unchanged since it was cached
+    bool recall(const string& name, void* d_dst, size_t bytes) {
+        auto it = files.find(name);
+        if (it == files.end()) return false;
+        FileId now;
+        if (!file_id(name, &now) || !(now == it->second.id) || it->second.bytes != bytes) {
+            drop(name);
+            return false;
+        }
+        zkllm::check(zkb_memcpy_d2d(d_dst, it->second.dev, bytes, nullptr));
+        zkllm::check(zkb_sync(nullptr));
+        lru.splice(lru.begin(), lru, it->second.age);
+        return true;
+    }
+};
+ResidentFiles& resident() {
+    static ResidentFiles r;
+    return r;
+}
 
 constexpr size_t kChunk = 16u << 20;
 
@@ -35,18 +119,36 @@ struct File {
 
 }  // namespace
 
+namespace zkllm {
+void set_resident_files(bool on, size_t limit_bytes) {
+    ResidentFiles& r = resident();
+    r.on = on;
+    if (limit_bytes) r.limit = limit_bytes;
+    if (!on)
+        while (!r.lru.empty()) r.drop(r.lru.back());
+}
+ResidentStats resident_stats() { return resident().stats; }
+}  // namespace zkllm
+
 void savebin(const string& filename, const void* gpudata, uint size) {
-    File file(filename, "wb", "savebin");
-    const char* src = static_cast<const char*>(gpudata);
-    // chunk i travels to buffer i & 1 while chunk i - 1 is written out
-    size_t prev = 0;
-    for (size_t off = 0, i = 0; off < size || prev; off += kChunk, ++i) {
-        const size_t len = off < size ? (size - off < kChunk ? size - off : kChunk) : 0;
-        if (len) zkllm::check(zkb_memcpy_d2h_async(staging(i & 1), src + off, len, nullptr));
-        if (prev && fwrite(staging((i + 1) & 1), 1, prev, file.f) != prev)
-            throw std::runtime_error("savebin: short write to " + filename);
-        if (len) zkllm::check(zkb_sync(nullptr));
-        prev = len;
+    {
+        File file(filename, "wb", "savebin");
+        const char* src = static_cast<const char*>(gpudata);
+        // chunk i travels to buffer i & 1 while chunk i - 1 is written out
+        size_t prev = 0;
+        for (size_t off = 0, i = 0; off < size || prev; off += kChunk, ++i) {
+            const size_t len = off < size ? (size - off < kChunk ? size - off : kChunk) : 0;
+            if (len) zkllm::check(zkb_memcpy_d2h_async(staging(i & 1), src + off, len, nullptr));
+            if (prev && fwrite(staging((i + 1) & 1), 1, prev, file.f) != prev)
+                throw std::runtime_error("savebin: short write to " + filename);
+            if (len) zkllm::check(zkb_sync(nullptr));
+            prev = len;
+        }
+    }   // closed: size and modification time are final
+    ResidentFiles& r = resident();
+    if (r.on) {
+        r.remember(filename, gpudata, size);
+        r.stats.saved_files += 1;
     }
 }
 
@@ -60,7 +162,18 @@ uint findsize(const string& filename) {
 }
 
 void loadbin(const string& filename, void* gpudata, uint size) {
-    File file(filename, "rb", "loadbin");
+    ResidentFiles& r = resident();
+    if (r.on && r.recall(filename, gpudata, size)) {
+        r.stats.loads_from_device += 1;
+        r.stats.bytes_from_device += size;
+        return;
+    }
+    if (r.on) {
+        r.stats.loads_from_disk += 1;
+        r.stats.bytes_from_disk += size;
+    }
+    {
+        File file(filename, "rb", "loadbin");
     char* dst = static_cast<char*>(gpudata);
     for (size_t off = 0, i = 0; off < size; off += kChunk, ++i) {
         const size_t len = size - off < kChunk ? size - off : kChunk;
@@ -70,4 +183,6 @@ void loadbin(const string& filename, void* gpudata, uint size) {
         zkllm::check(zkb_memcpy_h2d_async(dst + off, staging(i & 1), len, nullptr));
     }
     zkllm::check(zkb_sync(nullptr));
+    }
+    if (r.on) r.remember(filename, gpudata, size);
 }

@@ -29,6 +29,17 @@ struct Transcript {
 void set_transcript_sink(Transcript* sink);   // nullptr = off (default)
 Transcript* transcript_sink();
 
+// Resident files: with `on`, loadbin / savebin (ioutils) keep a device copy of every file they
+// touch, up to limit_bytes in total (0 = keep the current limit, 24 GiB at first; least recently
+// used files go first), and a later loadbin of an unchanged file copies from the device instead of
+// reading the disk.  Off by default, like the reference, which reads every file again; turning it
+// off releases the copies.  `zkllm-driver batch` turns it on.
+struct ResidentStats {
+    unsigned long long loads_from_disk = 0, loads_from_device = 0, bytes_from_disk = 0, bytes_from_device = 0, saved_files = 0;
+};
+void set_resident_files(bool on, size_t limit_bytes = 0);
+ResidentStats resident_stats();
+
 // Throws std::runtime_error(msg) when a C-ABI call failed; dimension and
 // verifier failures carry the reference's message text.
 void check(int rc);
