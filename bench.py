@@ -135,6 +135,54 @@ def tlookup_inputs():
     return S, random_fr(ch, 1), random_fr(ch, 1), random_fr(ch, 23), random_fr(ch, 23)
 
 
+def kernel_times(z, fn, reps: int = 3) -> dict:
+    """CUDA-event time per kernel name (microseconds per call of fn, launches per call) from the library's own profiler.
+    Kernels of the two streams of a call overlap, so the sum can exceed the call's wall time."""
+    z.call("zkb_profile_reset")
+    z.call("zkb_profile_enable", ctypes.c_int(1))
+    for _ in range(reps):
+        fn()
+    z.call("zkb_profile_enable", ctypes.c_int(0))
+    buf = ctypes.create_string_buffer(1 << 16)
+    z.call("zkb_profile_read", buf, z.sz(len(buf)))
+    z.call("zkb_profile_reset")
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.rsplit(",", 2)
+        if not name.startswith("host:"):
+            out[name] = {"launches": int(cnt) // reps, "us": round(float(ms) * 1e3 / reps, 1)}
+    return dict(sorted(out.items(), key=lambda kv: -kv[1]["us"]))
+
+
+def run_opening(args) -> dict:
+    """--workload opening: one Commitment::me_open (zkb_me_open) over 2^logn seeded generators and scalars - wall
+    milliseconds per opening and CUDA-event time per kernel."""
+    from __graft_entry__ import load_package
+    z = load_package()
+    n = 1 << args.logn
+    rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 80 + args.logn))
+    gens = z.DeviceBuffer(144 * n)
+    z.call("zkb_g1_mul", z._p(z.DeviceBuffer.from_host(g1_generator_limbs())), z.sz(1), z._p(z.DeviceBuffer.from_host(random_fr(rng, n))),
+           z.sz(n), z._p(gens), z._p(0))
+    t = z.DeviceBuffer.from_host(random_fr(rng, n))
+    u = random_fr(rng, args.logn)
+    proof, out = np.zeros((3 * args.logn + 1, 36), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+
+    def run():
+        z.call("zkb_me_open", z._p(t), z._p(gens), z.sz(n), z._p(u), z.u32(args.logn), z._p(proof), z._p(out), z._p(0))
+
+    for _ in range(max(1, args.warmup)):
+        run()
+    times = []
+    for _ in range(max(1, args.steps)):
+        t0 = time.perf_counter()
+        run()
+        times.append((time.perf_counter() - t0) * 1e3)
+    return {"metric": "opening proof time (Commitment::me_open)", "unit": "ms", "value": sorted(times)[len(times) // 2],
+            "higher_is_better": False, "workload": f"me_open over 2^{args.logn} generators, {args.logn} rounds", "wall_ms": times,
+            "kernel_us": kernel_times(z, run, 1), "opening": bytes(out[0]).hex(), "data": "synthetic"}
+
+
 def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
     """zkFC::prove body (128x4096 . 4096x4096) and tLookupRange prep + prove (2^23 in 2^16):
     seconds per proof and algorithmic GB/s (bytes each live array is read/written once per round)"""
@@ -169,7 +217,7 @@ def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
     s = timed(zk)
     out["zkfc_prove"] = {"workload": "zkFC::prove body, X 128x4096, W 4096x4096", "seconds": s, "algorithmic_bytes": ZKFC_BYTES,
                          "gb_per_s": ZKFC_BYTES / s / 1e9, "frac_of_hbm_peak": ZKFC_BYTES / s / 1e9 / hbm_peak,
-                         "final_claim": bytes(claims[1]).hex()}
+                         "final_claim": bytes(claims[1]).hex(), "kernel_us": kernel_times(z, zk)}
     del dev
     S, alpha, beta, u, v = tlookup_inputs()
     d_S_int = torch.from_numpy(S).cuda()
@@ -190,7 +238,8 @@ def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
     s = timed(tl)
     out["tlookup_prove"] = {"workload": "tLookupRange(-32768, 65536) prep + prove, 2^23 values", "seconds": s,
                             "algorithmic_bytes": TL_BYTES, "gb_per_s": TL_BYTES / s / 1e9,
-                            "frac_of_hbm_peak": TL_BYTES / s / 1e9 / hbm_peak, "final_claim": bytes(tfinal[0]).hex()}
+                            "frac_of_hbm_peak": TL_BYTES / s / 1e9 / hbm_peak, "final_claim": bytes(tfinal[0]).hex(),
+                            "kernel_us": kernel_times(z, tl)}
     return out
 
 
@@ -325,9 +374,9 @@ def table_method_additions(sc: np.ndarray, m: int, n: int, windows: int) -> int:
 
 # DRAM bytes per launch of the dominant kernel come from one ncu capture each (profiles/), scaled by the work of this launch:
 # msm_accumulate_kernel (bucket method): 160.657 MB for 2048 x 11008 (row, generator) pairs;
-# msm_comb_kernel (combination tables): see NCU_COMB_DRAM_BYTES_PER_ADDITION (None until captured).
+# msm_comb_kernel (combination tables): 1951.5 MB for the 12,451,040 additions of a 1024 x 11008 launch.
 NCU_DRAM_BYTES_PER_POINT = 160.657e6 / (2048 * 11008)
-NCU_COMB_DRAM_BYTES_PER_ADDITION = None
+NCU_COMB_DRAM_BYTES_PER_ADDITION = 1951.476e6 / 12451040     # one 1024 x 11008 launch: 1929.7 MB read + 21.8 MB written, 12,451,040 additions
 CPU_BASELINE_SECONDS = 12.0
 LAYER_OUTPUTS = ["x1.bin", "temp_Q.bin", "temp_K.bin", "temp_V.bin", "temp_head_Y.bin", "temp_head_out.bin", "x2.bin", "x3.bin",
                  "x4.bin", "x5.bin"]
@@ -860,8 +909,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=11008)
-    ap.add_argument("--workload", default="commit", choices=["commit", "layer"],
-                    help="commit: the headline MSM benchmark; layer: one decoder layer through the stage drivers")
+    ap.add_argument("--workload", default="commit", choices=["commit", "layer", "opening"],
+                    help="commit: the headline MSM benchmark; layer: one decoder layer through the stage drivers; "
+                         "opening: one Commitment::me_open over 2^logn generators with per-kernel times")
+    ap.add_argument("--logn", type=int, default=17, help="opening workload: log2 of the number of generators")
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--embed", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=11008)
@@ -880,6 +931,9 @@ def main():
         args.warmup = 3
     if args.workload == "layer":
         print(json.dumps(run_layer(args)))
+        return
+    if args.workload == "opening":
+        print(json.dumps(run_opening(args)))
         return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:

@@ -174,6 +174,13 @@ int zkb_fr_add_bias(zkb_fr_t* d_z, const zkb_fr_t* d_bias, size_t rows, size_t c
  * The inputs are not modified. */
 int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n,
              const zkb_fr_t* h_u, unsigned k, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* zkip_stacked (zkfc.cu:153-228): A and B are [num, D] tensors (one vector pair per layer or head).  kN =
+ * ceilLog2(num) rounds over the stack - each weighted by eq over the remaining lower half of the stack, paired with
+ * h_uN[kN - 1 - r] and folded with h_vN[kN - 1 - r] - then zkip over D with h_uD.  h_polys receives 3 coefficients
+ * per round (kN + kD rounds); ZKB_ERR_VERIFY with "claim != q(0) + q(1)" (a stack round) or "claim != p(0) + p(1)". */
+int zkb_zkip_stacked(const zkb_fr_t* h_claim, const zkb_fr_t* d_A, const zkb_fr_t* d_B, size_t num, size_t D,
+                     const zkb_fr_t* h_uN, const zkb_fr_t* h_vN, unsigned kN, const zkb_fr_t* h_uD, unsigned kD,
+                     zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
 /* The first `rounds` rounds of zkip (zkfc.cu:94-151) without the verifier replay: no counterpart
  * in the reference; the building block of the multi-GPU split, where a rank's sums
  * are only part of each round polynomial.  Round r uses h_u[k - 1 - r].

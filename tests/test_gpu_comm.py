@@ -26,6 +26,8 @@ ROOT = Path(__file__).resolve().parent.parent
 
 @pytest.fixture(scope="module")
 def dev(zkb):
+    # PyTorch brings its own NCCL; a process that uses both loads PyTorch's first, and the library then shares that copy
+    import torch  # noqa: F401
     d = Dev(zkb)
     rank, world = ctypes.c_int(-1), ctypes.c_int(-1)
     zkb.call("zkb_comm_info", ctypes.byref(rank), ctypes.byref(world))

@@ -16,6 +16,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -38,7 +39,14 @@ std::mutex g_mu;
 
 int load_api() {
     if (g_api.handle) return ZKB_OK;
-    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);      // a copy the process already has
+    // A copy the process already has comes first: two NCCL builds under the same library name cannot
+    // live in one process, so a host that will load its own NCCL later (PyTorch, say) must do so before
+    // this call, or name that copy in ZKLLM_NCCL_LIB.
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!h) {
+        const char* named = std::getenv("ZKLLM_NCCL_LIB");
+        if (named && named[0]) h = dlopen(named, RTLD_NOW | RTLD_GLOBAL);
+    }
     if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
     if (!h) return fail(ZKB_ERR_ARG, std::string("comm: cannot load NCCL: ") + dlerror());

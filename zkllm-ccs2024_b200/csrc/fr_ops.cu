@@ -162,11 +162,18 @@ __global__ void __launch_bounds__(kThreads) fr_rowdot_kernel(const Fr* __restric
         if (threadIdx.x == 0) fr_store(out + o, acc);
     }
 }
-// The same with one warp per (row, part of the j range): no block barrier, four
+// The same with one warp per (row, part of the j range): no block barrier, ZKB_ROWDOT_UNROLL
 // loads in flight per lane.  out[p * rows + o] = partial sum of part p (parts > 1:
 // the caller adds the slices).
-__global__ void __launch_bounds__(kThreads) fr_rowdot_warp_kernel(const Fr* __restrict__ a, const Fr* __restrict__ E,
+#ifndef ZKB_ROWDOT_UNROLL
+#define ZKB_ROWDOT_UNROLL 4
+#endif
+#ifndef ZKB_ROWDOT_MINBLOCKS
+#define ZKB_ROWDOT_MINBLOCKS 1
+#endif
+__global__ void __launch_bounds__(kThreads, ZKB_ROWDOT_MINBLOCKS) fr_rowdot_warp_kernel(const Fr* __restrict__ a, const Fr* __restrict__ E,
                                                                    size_t rows, size_t J, unsigned parts, Fr* __restrict__ out) {
+    constexpr int U = ZKB_ROWDOT_UNROLL;
     const unsigned lane = threadIdx.x & 31u;
     const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
     const size_t jper = (J + parts - 1) / parts;
@@ -177,12 +184,12 @@ __global__ void __launch_bounds__(kThreads) fr_rowdot_warp_kernel(const Fr* __re
         LazyDot dot;
         dot.init();
         size_t j = j0 + lane;
-        for (; j + 96 < j1; j += 128) {
-            const Fr x0 = fr_load(row + j), x1 = fr_load(row + j + 32), x2 = fr_load(row + j + 64), x3 = fr_load(row + j + 96);
-            dot.add(x0, fr_load(E + j));
-            dot.add(x1, fr_load(E + j + 32));
-            dot.add(x2, fr_load(E + j + 64));
-            dot.add(x3, fr_load(E + j + 96));
+        for (; j + 32 * (U - 1) < j1; j += 32 * U) {
+            Fr x[U];
+#pragma unroll
+            for (int t = 0; t < U; ++t) x[t] = fr_load(row + j + 32 * t);
+#pragma unroll
+            for (int t = 0; t < U; ++t) dot.add(x[t], fr_load(E + j + 32 * t));
         }
         for (; j < j1; j += 32) dot.add(fr_load(row + j), fr_load(E + j));
         const Fr acc = warp_sum(dot.finish());

@@ -151,6 +151,38 @@ __global__ void __launch_bounds__(kThreads) zkip_round_kernel(const Fr* __restri
     grid_sum_finish<3>(acc, partial, ticket, out, 0x7u, red);
 }
 
+// One round of zkip_stacked (zkfc.cu:153-228): A and B are [num, D]; the round pairs head h with head
+// h + half_heads (zero past the last head), weights the three coefficient sums by eq(u_; h) over the lower
+// heads and folds the head axis with v.  One pass over A and B instead of the reference's two kernels,
+// three D-long fold passes and three sums.  `eq` covers the half_heads lower heads (lo/hi split as elsewhere).
+__global__ void __launch_bounds__(kThreads) zkip_stacked_round_kernel(const Fr* __restrict__ a, const Fr* __restrict__ b, size_t n_in,
+                                                                       size_t half, size_t D, Fr v_mont, EqTab eq,
+                                                                       Fr* __restrict__ na, Fr* __restrict__ nb,
+                                                                       Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
+    __shared__ Fr red[32];
+    Fr acc[3];
+    acc[0] = acc[1] = acc[2] = fr_zero();
+    const size_t lmask = ((size_t)1 << eq.kl) - 1;
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < half; g += (size_t)gridDim.x * blockDim.x) {
+        const size_t head = g / D;
+        Fr e = fr_load(eq.lo + (head & lmask));
+        if (eq.hi) e = fr_mmul(e, fr_load(eq.hi + (head >> eq.kl)));      // (lo R)(hi R)/R = e R
+        const Fr a0 = fr_load(a + g), b0 = fr_load(b + g);
+        const Fr a1 = g + half < n_in ? fr_load(a + g + half) : fr_zero();
+        const Fr b1 = g + half < n_in ? fr_load(b + g + half) : fr_zero();
+        const Fr da = fr_sub(a1, a0), db = fr_sub(b1, b0);
+        const Fr e0 = fr_mmul(a0, e), e1 = fr_mmul(da, e);
+        const Fr t0 = fr_mmul(e0, b0), t2 = fr_mmul(e1, db);
+        const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e0, e1), fr_add(b0, db)), t0), t2);
+        acc[0] = fr_add(acc[0], t0);
+        acc[1] = fr_add(acc[1], t1);
+        acc[2] = fr_add(acc[2], t2);
+        fr_store(na + g, fr_add(a0, fr_mmul(v_mont, da)));
+        fr_store(nb + g, fr_add(b0, fr_mmul(v_mont, db)));
+    }
+    grid_sum_finish<3>(acc, partial, ticket, out, 0x7u, red);
+}
+
 // The last rounds of zkip in ONE launch of one CTA: from kZkipTailHalf pairs down (above that one SM is too slow),
 // a round is a few microseconds of work and a separate launch each would cost
 // more than the arithmetic.  `vs` holds the challenges of these rounds in round
@@ -330,7 +362,11 @@ static int zkip_verify(const zkb_fr_t* h_claim, const zkb_fr_t* h_u, unsigned k,
 // Phase-1 round on (A, S) of size 2*half (tlookup.cu:74-109, 184-200).
 // sums: [0..2] eq-weighted coefficients of (A0 + A1 t)(S0 + beta + S1 t) (without
 // the alpha factor, applied on the host), [3] sum A0, [4] sum A1.
-__global__ void __launch_bounds__(kThreads) tl_phase1_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S, size_t half,
+// Resident CTAs per SM asked of the compiler for the two phase-1 kernels (register cap 65536 / (256 * this)).
+#ifndef ZKB_TL_MINBLOCKS
+#define ZKB_TL_MINBLOCKS 1
+#endif
+__global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S, size_t half,
                                                               Fr beta, Fr v_mont, EqTab eq, unsigned R,
                                                               Fr* __restrict__ nA, Fr* __restrict__ nS,
                                                               Fr* __restrict__ partial, unsigned* ticket, Fr* __restrict__ out) {
@@ -390,7 +426,7 @@ ZKB_DEV Fr tl_inverse_at(const Fr& s, uint32_t k, const Fr* __restrict__ T, cons
 //     t0 = e,    t2 = e (A1 - A0)(S1 - S0),    t1 = -t2,
 // one field product and one product by the difference S1 - S0 - a small integer for fixed-point
 // data, accumulated unreduced (LazyDot).  A pair with a zero inverse takes the general formulas.
-__global__ void __launch_bounds__(kThreads) tl_phase1_first_kernel(const Fr* __restrict__ S, const uint32_t* __restrict__ idx,
+__global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_first_kernel(const Fr* __restrict__ S, const uint32_t* __restrict__ idx,
                                                                     const Fr* __restrict__ T, const Fr* __restrict__ Bv, size_t N,
                                                                     size_t half, Fr beta, Fr v_mont, EqTab eq, unsigned R,
                                                                     Fr* __restrict__ nA, Fr* __restrict__ nS,
@@ -803,6 +839,67 @@ int zkb_zkip(const zkb_fr_t* h_claim, const zkb_fr_t* d_a, const zkb_fr_t* d_b, 
     ZKB_CUDA(cudaMemcpyAsync(h_polys, d_polys, 96 * (size_t)k, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return zkip_verify(h_claim, h_u, k, h_polys, h_final);
+}
+
+int zkb_zkip_stacked(const zkb_fr_t* h_claim, const zkb_fr_t* d_A, const zkb_fr_t* d_B, size_t num, size_t D,
+                     const zkb_fr_t* h_uN, const zkb_fr_t* h_vN, unsigned kN, const zkb_fr_t* h_uD, unsigned kD,
+                     zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
+    cudaStream_t s = as_stream(stream);
+    if (num == 0 || D == 0) return fail(ZKB_ERR_DIM, "a.size != N * D");
+    if (kN > 31) return fail(ZKB_ERR_LIMIT, "zkip_stacked: more than 31 variables over the stack");
+    if (kN != clog2(num)) return fail(ZKB_ERR_DIM, "zkip_stacked: uN.size() != ceilLog2(N)");
+    if (kN + kD == 0) { *h_final = *h_claim; return ZKB_OK; }
+    Scratch scratch(s);
+    Fr* d_polys = scratch.get_n<Fr>(3 * ((size_t)kN + kD) + 1);
+    if (!d_polys) return ZKB_ERR_CUDA;
+    const Fr* ca = CFR(d_A);
+    const Fr* cb = CFR(d_B);
+    size_t heads = num;
+    if (kN) {
+        const size_t half0 = (((size_t)1 << kN) >> 1) * D;
+        Fr* buf[2][2];
+        for (int i = 0; i < 2; ++i)
+            for (int j = 0; j < 2; ++j) {
+                buf[i][j] = scratch.get_n<Fr>(half0 >> i ? half0 >> i : 1);
+                if (!buf[i][j]) return ZKB_ERR_CUDA;
+            }
+        const unsigned max_grid = grid_for(half0, kThreads, 4);
+        Fr* partial = scratch.get_n<Fr>((size_t)max_grid * 3);
+        unsigned* ticket = scratch.get_n<unsigned>(4);
+        if (!partial || !ticket) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+        // round r weights by eq over uN[0 .. kN - 1 - r), pairs with uN[kN - 1 - r], folds with vN[kN - 1 - r]
+        EqTab tabs[33];
+        ZKB_TRY(make_eq_series(h_uN, kN - 1, kN, 0, tabs, scratch, s));
+        for (unsigned r = 0; r < kN; ++r) {
+            const size_t half_heads = ((size_t)1 << (kN - r)) >> 1;
+            const size_t half = half_heads * D;
+            const Fr v = dev_fr_mont(h_vN[kN - 1 - r]);
+            ZKB_LAUNCH(zkip_stacked_round_kernel, grid_for(half, kThreads, 4), kThreads, 0, s, ca, cb, heads * D, half, D, v, tabs[r],
+                       buf[r & 1][0], buf[r & 1][1], partial, ticket, d_polys + 3 * r);
+            ca = buf[r & 1][0];
+            cb = buf[r & 1][1];
+            heads = half_heads;
+        }
+    }
+    // what is left is one head: the plain inner-product sumcheck over D
+    if (kD) ZKB_TRY(zkip_device(ca, cb, D, h_uD, kD, kD, d_polys + 3 * kN, scratch, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_polys, d_polys, 96 * ((size_t)kN + kD), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    // the reference's checks (zkfc.cu:213-219): q = eq(u) * p, claim == q(0) + q(1)
+    hfr::H claim = hfr::load(*h_claim);
+    for (unsigned r = 0; r < kN; ++r) {
+        const hfr::H c[3] = {hfr::load(h_polys[3 * r]), hfr::load(h_polys[3 * r + 1]), hfr::load(h_polys[3 * r + 2])};
+        const hfr::H u = hfr::load(h_uN[kN - 1 - r]);
+        const hfr::H p1 = hfr::add(hfr::add(c[0], c[1]), c[2]);
+        const hfr::H lhs = hfr::add(hfr::mul(hfr::sub(hfr::from_u64(1), u), c[0]), hfr::mul(u, p1));
+        if (!hfr::eq(claim, lhs)) return fail(ZKB_ERR_VERIFY, "claim != q(0) + q(1)");
+        claim = hfr::poly_eval(c, 3, hfr::load(h_vN[kN - 1 - r]));
+    }
+    const zkb_fr_t mid = hfr::store(claim);
+    if (kD == 0) { *h_final = mid; return ZKB_OK; }
+    return zkip_verify(&mid, h_uD, kD, h_polys + 3 * kN, h_final);
 }
 
 int zkb_zkip_partial(const zkb_fr_t* d_a, const zkb_fr_t* d_b, size_t n, const zkb_fr_t* h_u, unsigned k, unsigned rounds,

@@ -93,42 +93,28 @@ Fr_t zkip(const Fr_t& claim, const FrTensor& a, const FrTensor& b, const vector<
 }
 
 // ---- stacked variants (reference: zkfc.cu:153-307) -----------------------------------------
-// One round over the leading `num` axis: the three coefficient tensors are folded
-// over their N_out axis with eq(uN minus last) and summed.
+// All rounds over the leading `num` axis and the inner-product rounds over D in one call: each stack
+// round is one fused kernel (coefficient sums weighted by eq over the lower half of the stack, and the fold).
 Fr_t zkip_stacked(const Fr_t& claim, const FrTensor& A, const FrTensor& B, const vector<Fr_t>& uN, const vector<Fr_t>& uD,
                   const vector<Fr_t> vN, uint N, uint D, vector<Polynomial>& proof) {
     if (uN.empty()) return zkip(claim, A, B, uD, proof);
     if (A.size != N * D) throw std::runtime_error("a.size != N * D");
     if (B.size != N * D) throw std::runtime_error("b.size != N * D");
-    const uint N_out = (1u << ceilLog2(N)) >> 1;
-    const uint size_out = N_out * D;
-    // halves of A and B along the num axis (the upper half is zero past N)
-    auto upper = [&](const FrTensor& T) {
-        FrTensor up(size_out);
-        check(zkb_memset0(up.gpu_data, sizeof(Fr_t) * (size_t)size_out, nullptr));
-        const uint have = (N > N_out ? N - N_out : 0) * D;
-        if (have) check(zkb_memcpy_d2d(up.gpu_data, T.gpu_data + size_out, sizeof(Fr_t) * (size_t)have, nullptr));
-        check(zkb_sync(nullptr));
-        return up;
-    };
-    FrTensor a0 = A.trunc(0, size_out), b0 = B.trunc(0, size_out);
-    FrTensor a1 = upper(A) - a0, b1 = upper(B) - b0;
-    FrTensor out0 = a0 * b0, out1 = a0 * b1 + a1 * b0, out2 = a1 * b1;
-    vector<Fr_t> u_(uN.begin(), uN.end() - 1);
-    vector<Fr_t> c(3);
-    if (!u_.empty()) {
-        c[0] = out0.partial_me(u_, N_out, D).sum();
-        c[1] = out1.partial_me(u_, N_out, D).sum();
-        c[2] = out2.partial_me(u_, N_out, D).sum();
-    } else {
-        c[0] = out0.sum(); c[1] = out1.sum(); c[2] = out2.sum();
-    }
-    Polynomial p(c);
-    proof.push_back(p);
-    auto q = Polynomial::eq(uN.back()) * p;
-    if (claim != q(kZero) + q(kOne)) throw std::runtime_error("claim != q(0) + q(1)");
-    FrTensor new_A = a0 + a1 * vN.back(), new_B = b0 + b1 * vN.back();
-    return zkip_stacked(p(vN.back()), new_A, new_B, {uN.begin(), uN.end() - 1}, uD, {vN.begin(), vN.end() - 1}, N_out, D, proof);
+    if (vN.size() < uN.size()) throw std::runtime_error("zkip_stacked: fewer fold challenges than stack variables");
+    const size_t rounds = uN.size() + uD.size();
+    vector<Fr_t> polys(3 * rounds + 1);
+    Fr_t final_claim;
+    // the reference pairs uN[i] with vN[i] from the back of both vectors
+    const vector<Fr_t> v_used(vN.end() - uN.size(), vN.end());
+    const int rc = zkb_zkip_stacked(&claim, A.gpu_data, B.gpu_data, N, D, uN.data(), v_used.data(), (unsigned)uN.size(),
+                                    ptr_or_dummy(uD), (unsigned)uD.size(), polys.data(), &final_claim, nullptr);
+    if (rc == ZKB_OK || rc == ZKB_ERR_VERIFY)
+        for (size_t r = 0; r < rounds; ++r) proof.push_back(Polynomial(vector<Fr_t>(polys.begin() + 3 * r, polys.begin() + 3 * r + 3)));
+    check(rc);
+    polys.resize(3 * rounds);
+    polys.push_back(final_claim);
+    record("zkip_stacked", polys);
+    return final_claim;
 }
 
 static FrTensor cat_weights(const vector<zkFC>& layers) {
