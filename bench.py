@@ -444,8 +444,11 @@ def run_ours(args) -> dict:
     d_out = d_all[rank * m * 36:(rank + 1) * m * 36]
     torch.cuda.synchronize()
 
+    method = {"auto": 0, "buckets": 1, "tables": 2}[args.method]
+
     def step():
-        z.call("zkb_commit_i32", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_sc.data_ptr()), z.sz(m * n), z._p(d_out.data_ptr()), sp)
+        z.call("zkb_commit_i32_method", z._p(d_gens.data_ptr()), z.sz(n), z._p(d_sc.data_ptr()), z.sz(m * n), z._p(d_out.data_ptr()),
+               ctypes.c_int(method), sp)
         if world > 1:
             # the exchange step of a row-sharded commitment, in place in the preallocated result
             z.call("zkb_comm_allgather", z._p(d_out.data_ptr()), z._p(d_all.data_ptr()), z.sz(m * 144), sp)
@@ -568,6 +571,33 @@ def run_ours(args) -> dict:
     if world > 1 and not args.no_sumcheck and world & (world - 1) == 0:
         sharded = sumcheck_sharded(z, torch, dist, world, rank, max(2, min(args.steps, 5)))
 
+    # ---- layers on several GPUs: replicas (the stage drivers are single-GPU; the proofs of different layers are independent) --
+    layer_replicas = None
+    if world > 1 and not args.no_layer:
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        dev_id = visible.split(",")[local] if visible else str(local)
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        try:
+            blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=dev_id)
+            mine = blk["one resident driver process"]
+            ok = mine["outputs_sha256"] == golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else True
+            secs = mine["seconds"]
+        except Exception as ex:
+            ok, secs = False, float("nan")
+            print(f"rank {rank}: layer replica failed: {str(ex)[-300:]}", file=sys.stderr)
+        wall = time.perf_counter() - t0
+        t = torch.tensor([secs, wall, 1.0 if ok else 0.0], device="cuda", dtype=torch.float64)
+        allt = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        per = [x.cpu().tolist() for x in allt]
+        worst = max(x[0] for x in per)
+        layer_replicas = {"workload": f"{world} Llama-2-7B-shape layers, one resident driver process per GPU, at the same time "
+                                      "(replicas: the stage drivers are single-GPU)",
+                          "layer_seconds_per_gpu": [x[0] for x in per], "layers_per_s": world / worst if worst == worst and worst > 0 else None,
+                          "wall_s_with_setup": max(x[1] for x in per), "all_outputs_equal_the_reference_sha": all(x[2] == 1.0 for x in per)}
+
     result = None
     if rank == 0:
         # ---- correctness on a sample of rows (checker: CPU restatement) -------------------
@@ -667,7 +697,7 @@ def run_ours(args) -> dict:
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "commit_sha256": commit_sha,
             "commit_sha256_equals_reference": sha_parity,
-            "sumcheck": sumcheck, "sumcheck_sharded": sharded, "strong": strong,
+            "sumcheck": sumcheck, "sumcheck_sharded": sharded, "strong": strong, "layer_replicas": layer_replicas,
         }
         if not (parity and e2e_ok) or sha_parity is False:
             result["error"] = "commitments differ from the oracle / the reference's recorded SHA"
@@ -748,7 +778,7 @@ def run_reference(args) -> dict:
             "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
-def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=None, log=None) -> dict:
+def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=None, log=None, device=None) -> dict:
     """One Llama-2-7B-shape decoder layer (seq 2048, hidden 4096, FFN 11008, random-init fixed-point weights) through the
     stage drivers with the reference's command lines and files: parameter commitment once, then for every (mode, passes) of
     `modes` the stages rmsnorm, self-attn (linear + attn), skip-connection, rmsnorm, ffn, skip-connection.  mode "process" =
@@ -763,6 +793,8 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
         out["unavailable"] = f"{bindir.relative_to(ROOT)} has no driver executables"
         return out
     env = dict(os.environ, ZKLLM_CHALLENGE_SEED="2024")
+    if device is not None:                       # the driver processes of this call see only this GPU
+        env["CUDA_VISIBLE_DEVICES"] = str(device)
     stages = {}
     server = {"proc": None, "log": []}
     state = {"batch": False}
@@ -924,6 +956,8 @@ def main():
     ap.add_argument("--layer-mode", default="batch", choices=["batch", "process"],
                     help="layer workload, our arm: all stages in one resident driver process, or one process per stage as the "
                          "reference's Python glue does (the reference arm always runs one process per stage)")
+    ap.add_argument("--method", default="auto", choices=["auto", "buckets", "tables"],
+                    help="commit workload: the library's choice of algorithm (what zkb_commit_i32 does), or one by name")
     ap.add_argument("--no-sumcheck", action="store_true", help="skip the zkFC / tLookup proof timings reported under 'sumcheck'")
     ap.add_argument("--no-layer", action="store_true", help="skip the decoder-layer workload reported under 'layer' (N = 1 only)")
     args = ap.parse_args()

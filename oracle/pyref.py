@@ -243,6 +243,42 @@ def eq_eval(u: int, v: int) -> int:
     return (2 * u * v - u - v + 1) % R_MOD
 
 
+def zkip_stacked(claim: int, A: list, B: list, uN: list, uD: list, vN: list, N: int, D: int, proof: list) -> int:
+    """zkip_stacked, zkfc.cu:187-228: A and B are [N, D]; one round per variable of the stack (paired with uN[-1], folded
+    with vN[-1], coefficient tensors folded over the lower half of the stack with eq(uN[:-1]) and summed), then zkip over D."""
+    A, B, uN, vN = list(A), list(B), list(uN), list(vN)
+    while uN:
+        if len(A) != N * D:
+            raise RuntimeError("a.size != N * D")
+        if len(B) != N * D:
+            raise RuntimeError("b.size != N * D")
+        n_out = (1 << ceil_log2(N)) >> 1
+        size_out = n_out * D
+        out = [[], [], []]
+        nA, nB = [], []
+        v = vN[-1]
+        for g in range(size_out):
+            a0, b0 = A[g], B[g]
+            a1 = ((A[g + size_out] if g + size_out < N * D else 0) - a0) % R_MOD
+            b1 = ((B[g + size_out] if g + size_out < N * D else 0) - b0) % R_MOD
+            out[0].append(a0 * b0 % R_MOD)
+            out[1].append((a0 * b1 + a1 * b0) % R_MOD)
+            out[2].append(a1 * b1 % R_MOD)
+            nA.append((a0 + v * a1) % R_MOD)
+            nB.append((b0 + v * b1) % R_MOD)
+        u_ = uN[:-1]
+        p = [sum(partial_me(o, u_, n_out, D)) % R_MOD if u_ else sum(o) % R_MOD for o in out]
+        proof.append(p)
+        u = uN[-1]
+        q0 = (1 - u) * poly_eval(p, 0) % R_MOD          # q = eq(u) * p
+        q1 = u * poly_eval(p, 1) % R_MOD
+        if claim != (q0 + q1) % R_MOD:
+            raise RuntimeError("claim != q(0) + q(1)")
+        claim = poly_eval(p, v)
+        A, B, uN, vN, N = nA, nB, uN[:-1], vN[:-1], n_out
+    return zkip(claim, A, B, uD, proof)
+
+
 # --- zkip / zkFC::prove (zkfc.cu:61-151) ----------------------------------------------
 def zkip(claim: int, a: list, b: list, u: list, proof: list) -> int:
     """Inner-product sumcheck, MSB first, challenges consumed from the back.

@@ -90,6 +90,35 @@ def test_zkfc_prove_rejects_wrong_output(dev):
     assert e.value.code == z.ERR_VERIFY
 
 
+@pytest.mark.parametrize("N,D", [(4, 8), (3, 5), (8, 1), (1, 16), (32, 128), (5, 64), (2, 1000)])
+def test_zkip_stacked(dev, N, D):
+    """the fused stack rounds + zkip over D against the restatement of zkfc.cu:187-228"""
+    z = dev.z
+    rng = random.Random(N * 1000 + D)
+    A, B = rand_fr(rng, N * D), rand_fr(rng, N * D)
+    kN, kD = R.ceil_log2(N), R.ceil_log2(D)
+    uN, vN, uD = rand_fr(rng, kN), rand_fr(rng, kN), rand_fr(rng, kD)
+    # the claim the stacked prover starts from: sum_n eq(uN; n) <A_n, B_n>
+    weights = [1] * N
+    for n in range(N):
+        for j, x in enumerate(uN):
+            weights[n] = weights[n] * (x if (n >> j) & 1 else (1 - x)) % R.R_MOD
+    claim = sum(weights[n] * sum(A[n * D + d] * B[n * D + d] for d in range(D)) for n in range(N)) % R.R_MOD
+    proof = []
+    exp_final = R.zkip_stacked(claim, A, B, uN, uD, vN, N, D, proof)
+    polys, final = np.zeros((max(3 * (kN + kD), 1), 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    dev.call("zkb_zkip_stacked", z._p(dev.hfr([claim])), z._p(dev.fr(A)), z._p(dev.fr(B)), z.sz(N), z.sz(D), z._p(dev.hfr(uN)),
+             z._p(dev.hfr(vN)), z.u32(kN), z._p(dev.hfr(uD)), z.u32(kD), z._p(polys), z._p(final), z._p(0))
+    got = R.fr_unpack(polys)[:3 * (kN + kD)]
+    assert [got[3 * i:3 * i + 3] for i in range(kN + kD)] == proof
+    assert R.fr_unpack(final)[0] == exp_final
+    if kN:
+        with pytest.raises(z.ZkbError) as e:
+            dev.call("zkb_zkip_stacked", z._p(dev.hfr([(claim + 1) % R.R_MOD])), z._p(dev.fr(A)), z._p(dev.fr(B)), z.sz(N), z.sz(D),
+                     z._p(dev.hfr(uN)), z._p(dev.hfr(vN)), z.u32(kN), z._p(dev.hfr(uD)), z.u32(kD), z._p(polys), z._p(final), z._p(0))
+        assert e.value.code == z.ERR_VERIFY and "claim != q(0) + q(1)" in e.value.msg
+
+
 def _tlookup(dev, S, table, m, alpha, beta, u, v, indices=None):
     """indices: None = zkb_tlookup_prove; a list = zkb_tlookup_prove_indexed with those claimed table positions"""
     z = dev.z

@@ -363,8 +363,10 @@ static int zkip_verify(const zkb_fr_t* h_claim, const zkb_fr_t* h_u, unsigned k,
 // sums: [0..2] eq-weighted coefficients of (A0 + A1 t)(S0 + beta + S1 t) (without
 // the alpha factor, applied on the host), [3] sum A0, [4] sum A1.
 // Resident CTAs per SM asked of the compiler for the two phase-1 kernels (register cap 65536 / (256 * this)).
+// Measured on the 2^23-value proof: 2 (128 registers, a few hundred bytes of spills) 405 + 856 us for the first and the
+// six later rounds against 544 + 904 us with 1 (218 / 174 registers, 8 warps per SM).
 #ifndef ZKB_TL_MINBLOCKS
-#define ZKB_TL_MINBLOCKS 1
+#define ZKB_TL_MINBLOCKS 2
 #endif
 __global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_kernel(const Fr* __restrict__ A, const Fr* __restrict__ S, size_t half,
                                                               Fr beta, Fr v_mont, EqTab eq, unsigned R,
@@ -442,7 +444,6 @@ __global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_first_ke
     const size_t npieces = (half + piece - 1) / piece;
     for (size_t c = blockIdx.x; c < npieces; c += gridDim.x) {
         Fr esum = fr_zero();                               // sum of the weights e R of the regular pairs
-        Fr g0 = fr_zero(), g1 = fr_zero(), g2 = fr_zero(); // general-formula pairs (each term carries 1/R)
         LazyDot lazy;                                      // sum of (S1 - S0) * e (A1 - A0), carries 1/R after finish()
         lazy.init();
         const size_t base = c * piece;
@@ -459,11 +460,17 @@ __global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_first_ke
                 esum = fr_add(esum, e);
                 lazy.add(c11, e01);
             } else {
+                // rare (S + beta = 0 somewhere in the pair): the general formulas, weighted in full at once so that
+                // the common path carries no accumulators for them
                 const Fr c10 = fr_add(s0, beta);
                 const Fr e00 = fr_mmul(a0, e);
-                const Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
-                const Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
-                g0 = fr_add(g0, t0); g1 = fr_add(g1, t1); g2 = fr_add(g2, t2);
+                Fr t0 = fr_mmul(e00, c10), t2 = fr_mmul(e01, c11);
+                Fr t1 = fr_sub(fr_sub(fr_mmul(fr_add(e00, e01), fr_add(c10, c11)), t0), t2);
+                if (eq.hi) {
+                    const Fr eh = fr_load(eq.hi + (base >> eq.kl));
+                    t0 = fr_mmul(t0, eh); t1 = fr_mmul(t1, eh); t2 = fr_mmul(t2, eh);
+                }
+                acc[0] = fr_add(acc[0], t0); acc[1] = fr_add(acc[1], t1); acc[2] = fr_add(acc[2], t2);
             }
             acc[3] = fr_add(acc[3], a0);
             acc[4] = fr_add(acc[4], c01);
@@ -471,14 +478,13 @@ __global__ void __launch_bounds__(kThreads, ZKB_TL_MINBLOCKS) tl_phase1_first_ke
             fr_store(nS + i, fr_add(s0, fr_mmul(v_mont, c11)));
         }
         // e R -> e / R, the scale of the other weighted terms (fixed by R^2 after the grid sum)
-        Fr q0 = fr_add(fr_mmul(fr_mmul(esum, one), one), g0);
-        const Fr lz = lazy.finish();
-        Fr q1 = fr_sub(g1, lz), q2 = fr_add(g2, lz);
+        Fr q0 = fr_mmul(fr_mmul(esum, one), one);
+        Fr q2 = lazy.finish();
         if (eq.hi) {
             const Fr eh = fr_load(eq.hi + (base >> eq.kl));
-            q0 = fr_mmul(q0, eh); q1 = fr_mmul(q1, eh); q2 = fr_mmul(q2, eh);
+            q0 = fr_mmul(q0, eh); q2 = fr_mmul(q2, eh);
         }
-        acc[0] = fr_add(acc[0], q0); acc[1] = fr_add(acc[1], q1); acc[2] = fr_add(acc[2], q2);
+        acc[0] = fr_add(acc[0], q0); acc[1] = fr_sub(acc[1], q2); acc[2] = fr_add(acc[2], q2);
     }
     grid_sum_finish<5>(acc, partial, ticket, out, 0x7u, red);
 }
