@@ -222,6 +222,45 @@ def test_commit_method_rejects_unknown(dev, gens):
     assert e.value.code == z.ERR_ARG
 
 
+def curve_points_outside_the_subgroup(count: int, seed: int) -> list:
+    """points of E(Fq): y^2 = x^3 + 4 that are not in the order-r subgroup (the cofactor is large, so a random
+    curve point almost never is); Jacobian triples with Z = 1"""
+    rng = random.Random(seed)
+    out = []
+    while len(out) < count:
+        x = rng.randrange(R.Q_MOD)
+        rhs = (x * x * x + 4) % R.Q_MOD
+        y = pow(rhs, (R.Q_MOD + 1) // 4, R.Q_MOD)          # q = 3 mod 4
+        if y * y % R.Q_MOD != rhs:
+            continue
+        P = (x, y, 1)
+        if R.g1_affine(R.g1_mul(P, R.R_MOD)) is not None:
+            out.append(P)
+    return out
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (2, 1), (4, 2), (5, 3), (8, 3), (6, 2)])
+def test_me_open_with_generators_outside_the_subgroup(dev, gens, n, k):
+    """a generator file need not hold points of order r: the opening then follows the reference's own arithmetic
+    (me_open_step, commitment.cu:79-109: scalars and challenges as 256 raw bits) and returns its group elements"""
+    z = dev.z
+    rng = random.Random(n * 11 + k)
+    wild = curve_points_outside_the_subgroup(n, 100 + n)
+    # a mixed set as well: one stray point among proper generators is enough to leave the fast path
+    for g in (wild, [wild[0]] + list(gens[:n - 1])):
+        t, u = rand_fr(rng, n), rand_fr(rng, k)
+        proof = []
+        exp = R.me_open(t, g, u, proof)
+        hp = np.zeros((3 * k + 1, 36), dtype=np.uint32)
+        ho = np.zeros((1, 8), dtype=np.uint32)
+        dev.call("zkb_me_open", z._p(dev.fr(t)), z._p(dev.g1(g)), z.sz(n), z._p(dev.hfr(u)), z.u32(k), z._p(hp), z._p(ho), z._p(0))
+        assert R.fr_unpack(ho)[0] == exp
+        got = R.g1_unpack(hp)
+        assert len(got) == len(proof)
+        for a, b in zip(got, proof):
+            assert affine_eq(a, b)
+
+
 @pytest.mark.parametrize("m,n", [(1, 3), (2, 8)])
 def test_commit_full_width(dev, gens, m, n):
     z = dev.z

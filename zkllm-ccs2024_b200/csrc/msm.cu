@@ -24,6 +24,8 @@
 #include "g1.cuh"
 #include "hostfr.hpp"
 
+#include <map>
+#include <mutex>
 #include <vector>
 
 namespace zkb {
@@ -686,6 +688,102 @@ static FoldDigits fold_digits(const zkb_fr_t& u) {
     return out;
 }
 
+// ---- generators outside the order-r subgroup ---------------------------------------
+// The shortcuts of the opening (endomorphism fold, T rows derived from earlier proof points, the tail as one
+// MSM) multiply scalars modulo r, which is the same group element only for points of order r - what
+// Commitment::random makes (commitment.cu:3-8), but not what an arbitrary generator file has to hold.  Every
+// generator set is therefore checked once, [r] P = O for all P, with r in 65 signed 4-bit digits shared by all
+// threads; the verdict is kept under a fingerprint of the set.  A set that fails takes the reference's own
+// arithmetic (me_open_step, commitment.cu:79-109): three MSM rows in every round, the fold as a plain
+// double-and-add by the challenge's 256 raw bits, every round folded.
+struct OrderDigits { signed char d[65]; };
+static OrderDigits order_digits() {
+    const uint64_t rmod[4] = {0xffffffff00000001ull, 0x53bda402fffe5bfeull, 0x3339d80809a1d805ull, 0x73eda753299d7d48ull};
+    OrderDigits out;
+    int carry = 0;
+    for (int w = 0; w < 65; ++w) {
+        int x = carry;
+        if (w < 64) x += (int)((rmod[w >> 4] >> (4 * (w & 15))) & 15u);
+        carry = 0;
+        if (x >= 8) { x -= 16; carry = 1; }
+        out.d[w] = (signed char)x;
+    }
+    return out;
+}
+
+__global__ void __launch_bounds__(128) g1_order_check_kernel(const G1Jac* __restrict__ gens, size_t n, OrderDigits dg,
+                                                              unsigned* __restrict__ bad) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const G1Jac p = g1_load(gens + i);
+        if (g1_is_identity(p)) continue;
+        G1Jac tab[8];
+        tab[0] = p;
+#pragma unroll 1
+        for (int t = 1; t < 8; ++t) tab[t] = (t & 1) ? g1_double_call(tab[t >> 1]) : g1_add_call(tab[t - 1], p);
+        G1Jac acc = g1_identity();
+#pragma unroll 1
+        for (int w = 64; w >= 0; --w) {
+            if (w != 64) {
+#pragma unroll 1
+                for (int d = 0; d < 4; ++d) acc = g1_double_call(acc);
+            }
+            const int a = dg.d[w];
+            if (a) {
+                G1Jac t = tab[(a < 0 ? -a : a) - 1];
+                if (a < 0) t = g1_neg(t);
+                acc = g1_add_call(acc, t);
+            }
+        }
+        if (!g1_is_identity(acc)) atomicOr(bad, 1u);
+    }
+}
+
+// *ok = every generator has order dividing r.  One small device-to-host copy per call for the fingerprint;
+// the check itself runs once per distinct set.
+static int generators_have_order_r(const G1Jac* d_gens, size_t n, bool* ok, Scratch& scratch, cudaStream_t s) {
+    static std::mutex mu;
+    static std::map<unsigned long long, bool> verdicts;
+    const size_t head = n < 4 ? n : 4, tail = n < 8 ? n - head : 4;
+    unsigned char sample[8 * sizeof(G1Jac)];
+    ZKB_CUDA(cudaMemcpyAsync(sample, d_gens, head * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+    if (tail) ZKB_CUDA(cudaMemcpyAsync(sample + head * sizeof(G1Jac), d_gens + (n - tail), tail * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    unsigned long long key = 0xcbf29ce484222325ull ^ (unsigned long long)n;
+    for (size_t i = 0; i < (head + tail) * sizeof(G1Jac); ++i) key = (key ^ sample[i]) * 0x100000001b3ull;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = verdicts.find(key);
+        if (it != verdicts.end()) { *ok = it->second; return ZKB_OK; }
+    }
+    unsigned* d_bad = scratch.get_n<unsigned>(4);
+    if (!d_bad) return ZKB_ERR_CUDA;
+    ZKB_CUDA(cudaMemsetAsync(d_bad, 0, 16, s));
+    ZKB_LAUNCH(g1_order_check_kernel, grid_for(n, 128), 128, 0, s, d_gens, n, order_digits(), d_bad);
+    unsigned h_bad = 0;
+    ZKB_CUDA(cudaMemcpyAsync(&h_bad, d_bad, 4, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    *ok = h_bad == 0;
+    std::lock_guard<std::mutex> lk(mu);
+    if (verdicts.size() > 4096) verdicts.clear();
+    verdicts[key] = *ok;
+    return ZKB_OK;
+}
+
+// The fold of me_open_step for any curve points: g' = g_odd + [u] (g_even - g_odd), u read as 256 raw bits.
+__global__ void __launch_bounds__(128) me_open_fold_generic_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size,
+                                                                    Fr u_raw, G1Jac* __restrict__ ngen) {
+    for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
+        const G1Aff a0 = g1_aff_load(bases + 2 * g);
+        if (2 * g + 1 >= old_size) {
+            g1_store(ngen + g, g1_mul_bits(g1_from_aff(a0), u_raw));
+            continue;
+        }
+        const G1Aff a1 = g1_aff_load(bases + 2 * g + 1);
+        const G1Jac diff = g1_add_mixed(g1_from_aff(a0), g1_aff_neg(a1));
+        g1_store(ngen + g, g1_add_mixed(g1_mul_bits(diff, u_raw), a1));
+    }
+}
+
 // ---- the last rounds of an opening, all at once --------------------------------
 // Once a round has at most kTailLen generators g (affine, in the order-r group),
 // every later generator is a known combination of them: with
@@ -931,8 +1029,10 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // sums on the side stream; all share one segment count, so a single reduction
     // after the last of them turns the buckets of every round into proof points
     // (the Horner chain over 37 windows is latency-bound: once, not once per round).
+    bool order_r = true;
+    ZKB_TRY(generators_have_order_r(reinterpret_cast<const G1Jac*>(d_gens), n, &order_r, keep, s));
     unsigned n_big = 0;
-    for (size_t c = n; n_big < k && c > kTailLen; c = (c + 1) / 2) ++n_big;
+    for (size_t c = n; n_big < k && (c > kTailLen || !order_r); c = (c + 1) / 2) ++n_big;
     // Only the first big round forms T = sum s_i g_i by an MSM.  With a = u (1 - u), b = (1 - u)^2, c = u^2 of a
     // round, the next round's T is  a T + b T0 + c T1  (expand sum s'_j g'_j with the two folds above), so
     // every later T is a fixed combination of the first T and the T0, T1 of the rounds before it: rounds
@@ -942,7 +1042,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     G1Jac* big_buckets = nullptr;
     G1Jac* big_points = nullptr;                 // T, T0, T1 of round 0, then T0, T1 of every later big round
     size_t per_row = 0;
-    const size_t big_rows = n_big ? 3 + 2 * (size_t)(n_big - 1) : 0;
+    const size_t big_rows = !n_big ? 0 : (order_r ? 3 + 2 * (size_t)(n_big - 1) : 3 * (size_t)n_big);
     if (n_big) {
         ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
         per_row = msm_bucket_count(big0) / 3;
@@ -955,11 +1055,11 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     size_t rows_done = 0;
     for (; r < n_big && rc == ZKB_OK; ++r) {
         const size_t nn = (cur + 1) / 2;
-        const unsigned n_rows = r == 0 ? 3u : 2u;
+        const unsigned n_rows = (r == 0 || !order_r) ? 3u : 2u;
         const Fr u_mont = host_fr(hfr::store(hfr::to_mont(hfr::load(h_u[r]))));
         Fr* rows_r = rows + 3 * used;
         G1Aff* bases_r = bases + used;
-        ZKB_LAUNCH(me_open_rows_kernel, grid_for(nn, 128), 128, 0, s, cs, cur, nn, u_mont, r == 0 ? 1u : 0u, rows_r, sc[r & 1]);
+        ZKB_LAUNCH(me_open_rows_kernel, grid_for(nn, 128), 128, 0, s, cs, cur, nn, u_mont, n_rows == 3 ? 1u : 0u, rows_r, sc[r & 1]);
         ZKB_TRY(to_affine_device(cg, bases_r, cur, s));
         ZKB_CUDA(cudaEventRecord(side->fork, s));
         ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
@@ -969,7 +1069,11 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
             rc = msm_shape(cur, n_rows, kMaxWindows, true, big0.nseg, &sh);
             if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_row * rows_done, round, side->st);
         }
-        ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
+        if (order_r) {
+            ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
+        } else {
+            ZKB_LAUNCH(me_open_fold_generic_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, host_fr(h_u[r]), gn[r & 1]);
+        }
         cs = sc[r & 1];
         cg = gn[r & 1];
         used += cur;
@@ -981,11 +1085,13 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         all.m = big_rows;
         Scratch fin(side->st);
         rc = msm_reduce_phase(big_buckets, all, big_points, fin, side->st);
-        if (rc == ZKB_OK) ZKB_CUDA(cudaMemcpyAsync(d_proof, big_points, 3 * sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
-        for (unsigned t = 1; t < n_big && rc == ZKB_OK; ++t)
+        if (rc == ZKB_OK && !order_r)      // three rows per round, already in proof order
+            ZKB_CUDA(cudaMemcpyAsync(d_proof, big_points, big_rows * sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
+        if (rc == ZKB_OK && order_r) ZKB_CUDA(cudaMemcpyAsync(d_proof, big_points, 3 * sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
+        for (unsigned t = 1; t < n_big && rc == ZKB_OK && order_r; ++t)
             ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t + 1, big_points + 3 + 2 * (size_t)(t - 1), 2 * sizeof(G1Jac),
                                      cudaMemcpyDeviceToDevice, side->st));
-        if (rc == ZKB_OK && n_big > 1) {
+        if (rc == ZKB_OK && n_big > 1 && order_r) {
             // coefficient of every point of big_points[0 .. 2 n_big - 1) in T of round t = 1 .. n_big - 1
             const size_t n_pts = 2 * (size_t)n_big - 1, n_der = n_big - 1;
             std::vector<hfr::H> a(n_big), b(n_big), c(n_big);
