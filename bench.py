@@ -594,9 +594,46 @@ def run_ours(args) -> dict:
         per = [x.cpu().tolist() for x in allt]
         worst = max(x[0] for x in per)
         layer_replicas = {"workload": f"{world} Llama-2-7B-shape layers, one resident driver process per GPU, at the same time "
-                                      "(replicas: the stage drivers are single-GPU)",
+                                      "(replicas: one whole layer per GPU)",
                           "layer_seconds_per_gpu": [x[0] for x in per], "layers_per_s": world / worst if worst == worst and worst > 0 else None,
                           "wall_s_with_setup": max(x[1] for x in per), "all_outputs_equal_the_reference_sha": all(x[2] == 1.0 for x in per)}
+
+    # ---- ONE layer on several GPUs: every GPU computes the outputs, each proof of the layer runs on one of them ----------
+    layer_split = None
+    if world > 1 and not args.no_layer:
+        import shutil
+        shared = [None]
+        if rank == 0:
+            shared[0] = tempfile.mkdtemp(dir=args.tmpdir, prefix="zkllm-layer-")
+            try:                                  # the parameters, once, where every rank's driver can read them
+                layer_workload("ours", [], args.seq, args.embed, args.hidden, device=dev_id, workdir=shared[0])
+            except Exception as ex:
+                print(f"layer split: parameter setup failed: {str(ex)[-300:]}", file=sys.stderr)
+                shutil.rmtree(shared[0], ignore_errors=True)
+                shared[0] = None
+        dist.broadcast_object_list(shared, src=0)
+        if shared[0] is not None:
+            try:
+                blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=dev_id,
+                                     params_dir=shared[0], share=(rank, world))
+                mine = blk["one resident driver process"]
+                ok = mine["outputs_sha256"] == golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else True
+                secs, stages_mine = mine["seconds"], mine["stages_s"]
+            except Exception as ex:
+                ok, secs, stages_mine = False, float("nan"), {}
+                print(f"rank {rank}: layer share failed: {str(ex)[-300:]}", file=sys.stderr)
+            t = torch.tensor([secs, 1.0 if ok else 0.0], device="cuda", dtype=torch.float64)
+            allt = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(allt, t)
+            per = [x.cpu().tolist() for x in allt]
+            worst = max(x[0] for x in per)
+            if rank == 0:
+                shutil.rmtree(shared[0], ignore_errors=True)
+            layer_split = {"workload": f"one Llama-2-7B-shape layer over {world} GPUs: every GPU computes the layer's outputs, each "
+                                       "of its proofs (lookups, sumchecks, weight openings) is run by one GPU; no exchange",
+                           "seconds": worst if worst == worst else None, "seconds_per_gpu": [x[0] for x in per],
+                           "stages_s_rank0": stages_mine,
+                           "every_gpu_wrote_the_reference_outputs": all(x[1] == 1.0 for x in per)}
 
     result = None
     if rank == 0:
@@ -698,6 +735,7 @@ def run_ours(args) -> dict:
             "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "commit_sha256": commit_sha,
             "commit_sha256_equals_reference": sha_parity,
             "sumcheck": sumcheck, "sumcheck_sharded": sharded, "strong": strong, "layer_replicas": layer_replicas,
+            "layer_split": layer_split,
         }
         if not (parity and e2e_ok) or sha_parity is False:
             result["error"] = "commitments differ from the oracle / the reference's recorded SHA"
@@ -778,14 +816,21 @@ def run_reference(args) -> dict:
             "e2e": {"value": v, "unit": "Mpts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
-def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=None, log=None, device=None) -> dict:
+def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=None, log=None, device=None,
+                   workdir=None, params_dir=None, share=None) -> dict:
     """One Llama-2-7B-shape decoder layer (seq 2048, hidden 4096, FFN 11008, random-init fixed-point weights) through the
     stage drivers with the reference's command lines and files: parameter commitment once, then for every (mode, passes) of
     `modes` the stages rmsnorm, self-attn (linear + attn), skip-connection, rmsnorm, ffn, skip-connection.  mode "process" =
     one process per stage, as the reference's Python glue runs them; "batch" = all stages in one resident driver process
     (this build only).  impl "reference" runs the reference's own driver executables (oracle/_ref/drivers, device-LTO build).
-    Wall seconds per stage (each includes file I/O, and start-up in process mode) and the SHA-256 of every integer output."""
+    Wall seconds per stage (each includes file I/O, and start-up in process mode) and the SHA-256 of every integer output.
+    workdir: use this directory and keep it (default: a temporary one); params_dir: a directory an earlier call (with
+    `workdir`, and possibly no modes) left the parameters and the layer's input in, so this call generates none;
+    share = (r, P): this call's driver proves only its share of the layer's proofs, as process r of P (all P compute every
+    output; see the head of host/drivers.cpp)."""
+    import contextlib
     import hashlib
+    import shutil
     bindir = (ROOT / "oracle" / "_ref" / "drivers") if impl == "reference" else (ROOT / "zkllm-ccs2024_b200" / "bin")
     shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((embed, hidden), "decoder")
     out = {"impl": impl, "workload": f"{shape} layer, seq {seq} hidden {embed} ffn {hidden}", "data": "synthetic"}
@@ -795,6 +840,8 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
     env = dict(os.environ, ZKLLM_CHALLENGE_SEED="2024")
     if device is not None:                       # the driver processes of this call see only this GPU
         env["CUDA_VISIBLE_DEVICES"] = str(device)
+    if share is not None:
+        env["ZKLLM_PROOF_RANK"], env["ZKLLM_PROOF_WORLD"] = str(share[0]), str(share[1])
     stages = {}
     server = {"proc": None, "log": []}
     state = {"batch": False}
@@ -836,15 +883,16 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
             if rc != 0:
                 raise RuntimeError("batch driver exited with an error")
 
-    with tempfile.TemporaryDirectory(dir=tmpdir) as tmp:
-        w = Path(tmp)
+    with (contextlib.nullcontext(workdir) if workdir else tempfile.TemporaryDirectory(dir=tmpdir)) as tmp:
+        w = Path(tmp)                                    # hand-off files of the stages (this call's own)
+        pdir = Path(params_dir) if params_dir else w     # generators, weights, commitments, the layer's input
         rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 64))
         params = [("input_layernorm.weight", 1, embed, embed), ("post_attention_layernorm.weight", 1, embed, embed),
                   ("self_attn.q_proj.weight", embed, embed, embed << 5), ("self_attn.k_proj.weight", embed, embed, embed << 5),
                   ("self_attn.v_proj.weight", embed, embed, embed << 5), ("mlp.up_proj.weight", embed, hidden, hidden << 5),
                   ("mlp.gate_proj.weight", embed, hidden, hidden << 5), ("mlp.down_proj.weight", hidden, embed, embed << 5)]
-        state["batch"] = modes[0][0] == "batch" and impl == "ours"
-        for name, in_dim, out_dim, pp_size in params:
+        state["batch"] = (not modes or modes[0][0] == "batch") and impl == "ours"
+        for name, in_dim, out_dim, pp_size in ([] if params_dir else params):
             if in_dim == 1:
                 wi = np.rint((1.0 + 0.1 * rng.standard_normal(out_dim)) * 65536).astype(np.int32)
             else:
@@ -853,10 +901,14 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
             run("ppgen", [pp_size, w / f"{name}-pp.bin"], w, "ppgen (8 generator sets)")
             run("commit-param", [w / f"{name}-pp.bin", w / f"layer-0-{name}-int.bin", w / f"layer-0-{name}-commitment.bin",
                                  in_dim, out_dim], w, "commit-param (8 parameters)")
-        x = np.rint(rng.standard_normal((seq, embed)) * 65536).astype(np.int32)
-        x.tofile(w / "x0.bin")
-        xs = np.arange(-(1 << 21), 1 << 21, dtype=np.float64) / 4096.0
-        np.rint(xs / (1.0 + np.exp(-xs)) * 16).astype(np.int32).tofile(w / "swiglu-table.bin")
+        if params_dir:
+            for nm in ("x0.bin", "swiglu-table.bin"):
+                shutil.copyfile(pdir / nm, w / nm)
+        else:
+            x = np.rint(rng.standard_normal((seq, embed)) * 65536).astype(np.int32)
+            x.tofile(w / "x0.bin")
+            xs = np.arange(-(1 << 21), 1 << 21, dtype=np.float64) / 4096.0
+            np.rint(xs / (1.0 + np.exp(-xs)) * 16).astype(np.int32).tofile(w / "swiglu-table.bin")
 
         def rms_inv(path):
             xf = np.fromfile(path, dtype=np.int32).reshape(seq, embed).astype(np.float64) / 65536.0
@@ -864,13 +916,13 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
 
         def prove_layer():
             rms_inv(w / "x0.bin")
-            run("rmsnorm", ["input", "x0.bin", seq, embed, w, "layer-0", "x1.bin"], w, "rmsnorm (input)")
-            run("self-attn", ["linear", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn linear")
-            run("self-attn", ["attn", "x1.bin", seq, embed, w, "layer-0", "unused.bin"], w, "self-attn attn")
+            run("rmsnorm", ["input", "x0.bin", seq, embed, pdir, "layer-0", "x1.bin"], w, "rmsnorm (input)")
+            run("self-attn", ["linear", "x1.bin", seq, embed, pdir, "layer-0", "unused.bin"], w, "self-attn linear")
+            run("self-attn", ["attn", "x1.bin", seq, embed, pdir, "layer-0", "unused.bin"], w, "self-attn attn")
             run("skip-connection", ["x0.bin", "temp_head_out.bin", "x2.bin"], w, "skip-connection (x2)")
             rms_inv(w / "x2.bin")
-            run("rmsnorm", ["post_attention", "x2.bin", seq, embed, w, "layer-0", "x3.bin"], w, "rmsnorm (post_attention)")
-            run("ffn", ["x3.bin", seq, embed, hidden, w, "layer-0", "x4.bin"], w, "ffn")
+            run("rmsnorm", ["post_attention", "x2.bin", seq, embed, pdir, "layer-0", "x3.bin"], w, "rmsnorm (post_attention)")
+            run("ffn", ["x3.bin", seq, embed, hidden, pdir, "layer-0", "x4.bin"], w, "ffn")
             run("skip-connection", ["x2.bin", "x4.bin", "x5.bin"], w, "skip-connection (x2)")
 
         def digest():

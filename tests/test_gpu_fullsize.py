@@ -102,3 +102,25 @@ def test_layer_7b_outputs_equal_the_reference_drivers(tmp_path):
     assert "unavailable" not in blk, blk
     got = blk["one resident driver process"]
     assert got["outputs_sha256"] == gold, got["output_files_sha256_16"]
+
+
+def test_layer_7b_proofs_shared_by_two_driver_processes(tmp_path):
+    """ZKLLM_PROOF_WORLD=2: both driver processes write the reference's outputs, every proof of the layer is run by
+    exactly one of them, and each process reports its share.  (Run one after the other here: they exchange nothing.)"""
+    import re
+    import bench
+    gold = GOLD.get("layer_7b_outputs_sha256")
+    params = tmp_path / "params"
+    params.mkdir()
+    bench.layer_workload("ours", [], 2048, 4096, 11008, workdir=str(params))
+    proofs, dealt = [], set()
+    for r in range(2):
+        log = tmp_path / f"driver{r}.log"
+        blk = bench.layer_workload("ours", [("batch", 1)], 2048, 4096, 11008, str(tmp_path), log=str(log), params_dir=str(params),
+                                   share=(r, 2))
+        assert blk["one resident driver process"]["outputs_sha256"] == gold
+        m = re.search(r"\[share\] process (\d) of 2: (\d+) of (\d+) proofs", log.read_text())
+        assert m and int(m.group(1)) == r, log.read_text()[-600:]
+        proofs.append(int(m.group(2)))
+        dealt.add(int(m.group(3)))
+    assert len(dealt) == 1 and sum(proofs) == dealt.pop() and min(proofs) > 0

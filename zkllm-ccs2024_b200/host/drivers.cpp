@@ -17,6 +17,17 @@
 // instead of one per stage.  After each line it prints "[batch] <stage> <s> s"
 // to stderr; with ZKLLM_PROFILE=1 it also prints the library's per-kernel times.
 // The first failing stage ends the batch with its exception.
+//
+// Several driver processes, one per GPU, can share the proofs of one layer: with
+// ZKLLM_PROOF_WORLD=P and ZKLLM_PROOF_RANK=r every process computes all the outputs
+// (they are cheap next to the proofs, and each process needs them as inputs of its
+// proofs), while every proof of the layer (a rescaling lookup, a zkFC sumcheck with
+// the opening of its weight, the softmax proof, ...) is run by exactly one process.
+// The proofs are independent of one another (each draws its own challenges), so
+// the processes exchange nothing; the layer is proven when all of them exit 0.
+// The deal is the same in every process: each proof goes to the process with the
+// least estimated work so far.  Give every process its own working directory for
+// the hand-off files and the same <workdir> for the parameters.
 // Each stage computes its fixed-point outputs in the field, proves them and
 // throws if a verifier equation fails, printing the reference's progress lines.
 #include <chrono>
@@ -53,6 +64,51 @@ struct StepClock {
         last = now;
     }
 };
+
+// Which of the P cooperating driver processes proves the next proof (see the head of this file).
+class ProofShare {
+public:
+    void configure(int rank, int world) {
+        if (world < 1 || rank < 0 || rank >= world) throw std::runtime_error("ZKLLM_PROOF_RANK / ZKLLM_PROOF_WORLD: bad values");
+        rank_ = rank;
+        load_.assign(world, 0.0);
+    }
+    // cost: estimated milliseconds of the proof; only the ratios matter
+    bool take(double cost) {
+        size_t to = 0;
+        for (size_t i = 1; i < load_.size(); ++i)
+            if (load_[i] < load_[to]) to = i;
+        load_[to] += cost;
+        ++dealt_;
+        if ((int)to != rank_) return false;
+        ++mine_;
+        return true;
+    }
+    void report() const {
+        if (load_.size() < 2) return;
+        double most = 0;
+        for (double l : load_) most = std::max(most, l);
+        cerr << "[share] process " << rank_ << " of " << load_.size() << ": " << mine_ << " of " << dealt_
+             << " proofs, estimated " << load_[rank_] << " ms here, " << most << " ms on the busiest" << endl;
+    }
+
+private:
+    int rank_ = 0;
+    std::vector<double> load_ = std::vector<double>(1, 0.0);
+    unsigned long dealt_ = 0, mine_ = 0;
+};
+
+ProofShare g_share;
+
+template <class Body>
+void proof(double cost, Body&& body) {
+    if (g_share.take(cost)) body();
+}
+
+// Estimates in milliseconds on one B200, from the stage clocks of the 7B-shape layer.
+double cost_lookup(size_t values) { return 1.0 + 1.0e-6 * values; }             // Rescaling::prove
+double cost_weight_claim(size_t weights) { return 4.0 + 2.0e-6 * weights; }     // zkFC::prove + the opening
+double cost_sumcheck(size_t values) { return 1.0 + 0.3e-6 * values; }
 
 // generator, int weights and commitment of one parameter of one layer
 Weight load_param(const std::string& workdir, const std::string& prefix, const std::string& name, uint in_dim, uint out_dim) {
@@ -100,11 +156,12 @@ int run_rmsnorm(const Args& a) {
     auto g_rms_ = rs_gain(g_rms);
     auto Y = g_rms_ * X;
     auto Y_ = rs_out(Y);
-    rs_out.prove(Y, Y_);
+    proof(cost_lookup(Y.size), [&] { rs_out.prove(Y, Y_); });
     Y_.save_int(a.at(6));
-    hadamard_product_sumcheck(g_rms_, X, random_vec(ceilLog2(Y.size)), random_vec(ceilLog2(Y.size)));
-    rs_gain.prove(g_rms, g_rms_);
-    verifyWeightClaim(weight, gain.prove(rms_inv, g_rms)[0]);
+    proof(cost_sumcheck(Y.size),
+          [&] { hadamard_product_sumcheck(g_rms_, X, random_vec(ceilLog2(Y.size)), random_vec(ceilLog2(Y.size))); });
+    proof(cost_lookup(g_rms.size), [&] { rs_gain.prove(g_rms, g_rms_); });
+    proof(cost_weight_claim(embed), [&] { verifyWeightClaim(weight, gain.prove(rms_inv, g_rms)[0]); });
     (void)seq;
     return 0;
 }
@@ -123,9 +180,11 @@ int run_self_attn(const Args& a) {
             raw.push_back(layers.back()->fc(input));
             scaled.push_back(layers.back()->rs(raw.back()));
         }
-        for (int i = 0; i < 3; ++i) layers[i]->rs.prove(raw[i], scaled[i]);
+        for (int i = 0; i < 3; ++i) proof(cost_lookup(raw[i].size), [&] { layers[i]->rs.prove(raw[i], scaled[i]); });
         // the reference opens k first, then q, then v
-        for (int i : {1, 0, 2}) verifyWeightClaim(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]);
+        for (int i : {1, 0, 2})
+            proof(cost_weight_claim((size_t)embed * embed),
+                  [&] { verifyWeightClaim(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]); });
         scaled[0].save_int("temp_Q.bin");
         scaled[1].save_int("temp_K.bin");
         scaled[2].save_int("temp_V.bin");
@@ -149,24 +208,30 @@ int run_self_attn(const Args& a) {
         auto out_ = rs2(out);
         auto out__ = rs1(out_);
         out__.save_int("temp_head_out.bin");
-        rs1.prove(out_, out__);
-        rs2.prove(out, out_);
+        proof(cost_lookup(out_.size), [&] { rs1.prove(out_, out__); });
+        proof(cost_lookup(out.size), [&] { rs2.prove(out, out_); });
         auto temp_rand = random_vec(3);
-        vector<Polynomial> proof;
-        auto u1 = random_vec(ceilLog2(seq));
-        auto u2 = random_vec(ceilLog2(d));
-        auto ud = random_vec(ceilLog2(seq));
-        auto claim = out.multi_dim_me({u1, u2}, {seq, d});
-        zkip(claim, Y.partial_me(u1, seq, seq), V.partial_me(u2, d, 1), ud, proof);
-        auto u_sm = random_vec(ceilLog2(Y.size));
-        auto v_sm = random_vec(ceilLog2(Y.size));
-        softmax.prove(Y, X, shift, X_shifted, X_segments, Y_segments, m_segments, u_sm, v_sm, temp_rand[0], temp_rand[1], temp_rand[2],
-                      proof);
-        auto u1_ = random_vec(ceilLog2(seq));
-        auto u2_ = random_vec(ceilLog2(seq));
-        auto ud_ = random_vec(ceilLog2(d));
-        auto claim_ = X.multi_dim_me({u1_, u2_}, {seq, seq});
-        zkip(claim_, Q.partial_me(u1_, seq, d), K.partial_me(u2_, seq, d), ud_, proof);
+        vector<Polynomial> polys;
+        proof(cost_sumcheck(Y.size + V.size), [&] {
+            auto u1 = random_vec(ceilLog2(seq));
+            auto u2 = random_vec(ceilLog2(d));
+            auto ud = random_vec(ceilLog2(seq));
+            auto claim = out.multi_dim_me({u1, u2}, {seq, d});
+            zkip(claim, Y.partial_me(u1, seq, seq), V.partial_me(u2, d, 1), ud, polys);
+        });
+        proof(8.0 * cost_lookup(Y.size), [&] {   // three segment lookups, the products between them and the row sums
+            auto u_sm = random_vec(ceilLog2(Y.size));
+            auto v_sm = random_vec(ceilLog2(Y.size));
+            softmax.prove(Y, X, shift, X_shifted, X_segments, Y_segments, m_segments, u_sm, v_sm, temp_rand[0], temp_rand[1],
+                          temp_rand[2], polys);
+        });
+        proof(cost_sumcheck(X.size + Q.size + K.size), [&] {
+            auto u1_ = random_vec(ceilLog2(seq));
+            auto u2_ = random_vec(ceilLog2(seq));
+            auto ud_ = random_vec(ceilLog2(d));
+            auto claim_ = X.multi_dim_me({u1_, u2_}, {seq, seq});
+            zkip(claim_, Q.partial_me(u1_, seq, d), K.partial_me(u2_, seq, d), ud_, polys);
+        });
         cout << "Self attention proof successfully verified!" << endl;
         return 0;
     }
@@ -203,23 +268,28 @@ int run_ffn(const Args& a) {
     down_out.save_int(a.at(6));   // the reference saves the value before the last rescaling
     clk.mark("save");
 
-    down.rs.prove(down_out, down_out_);
+    const size_t n_weights = (size_t)embed * hidden;
+    proof(cost_lookup(down_out.size), [&] { down.rs.prove(down_out, down_out_); });
     clk.mark("down rescale prove");
-    auto down_claim = down.fc.prove(down_in_, down_out)[0];
-    clk.mark("down fc prove");
-    verifyWeightClaim(down.w, down_claim);
+    proof(cost_weight_claim(n_weights), [&] {
+        auto down_claim = down.fc.prove(down_in_, down_out)[0];
+        clk.mark("down fc prove");
+        verifyWeightClaim(down.w, down_claim);
+    });
     clk.mark("down opening");
-    hidden_rescale.prove(down_in, down_in_);
+    proof(cost_lookup(down_in.size), [&] { hidden_rescale.prove(down_in, down_in_); });
     clk.mark("hidden rescale prove");
-    swiglu.prove(gate_out_, act.first, act.second, temp_rand[0], temp_rand[1], temp_rand[2], swiglu_u, swiglu_v, swiglu_proof);
+    proof(cost_lookup(gate_out_.size), [&] {
+        swiglu.prove(gate_out_, act.first, act.second, temp_rand[0], temp_rand[1], temp_rand[2], swiglu_u, swiglu_v, swiglu_proof);
+    });
     cout << "SwiGLU proof complete." << endl;
     clk.mark("swiglu prove");
-    gate.rs.prove(gate_out, gate_out_);
+    proof(cost_lookup(gate_out.size), [&] { gate.rs.prove(gate_out, gate_out_); });
     clk.mark("gate rescale prove");
-    verifyWeightClaim(gate.w, gate.fc.prove(input, gate_out)[0]);
+    proof(cost_weight_claim(n_weights), [&] { verifyWeightClaim(gate.w, gate.fc.prove(input, gate_out)[0]); });
     clk.mark("gate fc prove + opening");
-    up.rs.prove(up_out, up_out_);
-    verifyWeightClaim(up.w, up.fc.prove(input, up_out)[0]);
+    proof(cost_lookup(up_out.size), [&] { up.rs.prove(up_out, up_out_); });
+    proof(cost_weight_claim(n_weights), [&] { verifyWeightClaim(up.w, up.fc.prove(input, up_out)[0]); });
     clk.mark("up rescale + fc prove + opening");
     return 0;
 }
@@ -282,6 +352,7 @@ int run_batch(const Args& a) {
         }
         if (rc) return rc;
     }
+    g_share.report();
     return 0;
 }
 
@@ -304,6 +375,15 @@ int main(int argc, char* argv[]) {
         first = 2;
     }
     Args args(argv + first, argv + argc);
+    if (const char* world = std::getenv("ZKLLM_PROOF_WORLD")) {
+        const char* rank = std::getenv("ZKLLM_PROOF_RANK");
+        try {
+            g_share.configure(rank ? std::stoi(rank) : 0, std::stoi(world));
+        } catch (const std::exception& ex) {
+            cerr << "ZKLLM_PROOF_RANK / ZKLLM_PROOF_WORLD: " << ex.what() << endl;
+            return 2;
+        }
+    }
     if (args.size() < stages.at(stage).second) {
         cerr << stage << ": expected " << stages.at(stage).second << " arguments" << endl;
         return 2;
