@@ -601,39 +601,7 @@ def run_ours(args) -> dict:
     # ---- ONE layer on several GPUs: every GPU computes the outputs, each proof of the layer runs on one of them ----------
     layer_split = None
     if world > 1 and not args.no_layer:
-        import shutil
-        shared = [None]
-        if rank == 0:
-            shared[0] = tempfile.mkdtemp(dir=args.tmpdir, prefix="zkllm-layer-")
-            try:                                  # the parameters, once, where every rank's driver can read them
-                layer_workload("ours", [], args.seq, args.embed, args.hidden, device=dev_id, workdir=shared[0])
-            except Exception as ex:
-                print(f"layer split: parameter setup failed: {str(ex)[-300:]}", file=sys.stderr)
-                shutil.rmtree(shared[0], ignore_errors=True)
-                shared[0] = None
-        dist.broadcast_object_list(shared, src=0)
-        if shared[0] is not None:
-            try:
-                blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=dev_id,
-                                     params_dir=shared[0], share=(rank, world))
-                mine = blk["one resident driver process"]
-                ok = mine["outputs_sha256"] == golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else True
-                secs, stages_mine = mine["seconds"], mine["stages_s"]
-            except Exception as ex:
-                ok, secs, stages_mine = False, float("nan"), {}
-                print(f"rank {rank}: layer share failed: {str(ex)[-300:]}", file=sys.stderr)
-            t = torch.tensor([secs, 1.0 if ok else 0.0], device="cuda", dtype=torch.float64)
-            allt = [torch.empty_like(t) for _ in range(world)]
-            dist.all_gather(allt, t)
-            per = [x.cpu().tolist() for x in allt]
-            worst = max(x[0] for x in per)
-            if rank == 0:
-                shutil.rmtree(shared[0], ignore_errors=True)
-            layer_split = {"workload": f"one Llama-2-7B-shape layer over {world} GPUs: every GPU computes the layer's outputs, each "
-                                       "of its proofs (lookups, sumchecks, weight openings) is run by one GPU; no exchange",
-                           "seconds": worst if worst == worst else None, "seconds_per_gpu": [x[0] for x in per],
-                           "stages_s_rank0": stages_mine,
-                           "every_gpu_wrote_the_reference_outputs": all(x[1] == 1.0 for x in per)}
+        layer_split = layer_split_over_ranks(dist, rank, world, dev_id, args)
 
     result = None
     if rank == 0:
@@ -915,6 +883,8 @@ def layer_workload(impl: str, modes, seq: int, embed: int, hidden: int, tmpdir=N
             np.rint(65536.0 / np.sqrt((xf ** 2).mean(axis=1) + 1e-5)).astype(np.int32).tofile(w / "rms_inv_temp.bin")
 
         def prove_layer():
+            if share is not None and state["batch"]:
+                run("begin-layer", [], w, "begin-layer")       # every pass is dealt out the same way
             rms_inv(w / "x0.bin")
             run("rmsnorm", ["input", "x0.bin", seq, embed, pdir, "layer-0", "x1.bin"], w, "rmsnorm (input)")
             run("self-attn", ["linear", "x1.bin", seq, embed, pdir, "layer-0", "unused.bin"], w, "self-attn linear")
@@ -971,8 +941,67 @@ def layer_block(args) -> dict:
     return blk
 
 
+def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
+    """ONE decoder layer over the `world` processes of this job (one GPU each): rank 0 writes the parameters once where all
+    can read them, then every rank runs its own resident driver as process `rank` of `world` (ZKLLM_PROOF_RANK / _WORLD: all
+    compute the layer's outputs, each proof is run by one of them; host/drivers.cpp).  Seconds = the slowest rank's second
+    pass; every rank's output SHA is compared with the reference's (7B shape) and with rank 0's."""
+    import shutil
+    shared = [None]
+    if rank == 0:
+        shared[0] = tempfile.mkdtemp(dir=args.tmpdir, prefix="zkllm-layer-")
+        try:
+            layer_workload("ours", [], args.seq, args.embed, args.hidden, device=device, workdir=shared[0])
+        except Exception as ex:
+            print(f"layer split: parameter setup failed: {str(ex)[-300:]}", file=sys.stderr)
+            shutil.rmtree(shared[0], ignore_errors=True)
+            shared[0] = None
+    dist.broadcast_object_list(shared, src=0)
+    if shared[0] is None:
+        return {"error": "parameter setup failed on rank 0"}
+    mine = {"seconds": None, "sha": None, "stages_s": {}, "passes_s": []}
+    try:
+        blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=device,
+                             params_dir=shared[0], share=(rank, world),
+                             log=(f"{args.layer_log}.rank{rank}" if args.layer_log else None))
+        got = blk["one resident driver process"]
+        mine = {"seconds": got["seconds"], "sha": got["outputs_sha256"], "stages_s": got["stages_s"], "passes_s": got["passes_s"]}
+    except Exception as ex:
+        print(f"rank {rank}: layer share failed: {str(ex)[-300:]}", file=sys.stderr)
+    per = [None] * world
+    dist.all_gather_object(per, mine)
+    if rank == 0:
+        shutil.rmtree(shared[0], ignore_errors=True)
+    gold = golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else None
+    ok = all(q["seconds"] is not None for q in per)
+    shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((args.embed, args.hidden), "decoder")
+    return {"workload": f"one {shape} layer (seq {args.seq}) over {world} GPUs: every GPU computes the layer's outputs, each of its "
+                        "proofs (lookups, sumchecks, weight openings) is run by one GPU; no exchange between them",
+            "seconds": max(q["seconds"] for q in per) if ok else None,
+            "seconds_per_gpu": [q["seconds"] for q in per], "stages_s_rank0": per[0]["stages_s"],
+            "outputs_sha256": per[0]["sha"], "all_gpus_wrote_the_same_outputs": ok and len({q["sha"] for q in per}) == 1,
+            "reference_outputs_sha256": gold, "parity": (ok and all(q["sha"] == gold for q in per)) if gold else None}
+
+
 def run_layer(args) -> dict:
-    """--workload layer: the layer workload alone, one JSON line"""
+    """--workload layer: the layer workload alone, one JSON line.  Under a multi-process launch (WORLD_SIZE > 1, one
+    process per GPU) the ONE layer is shared by the ranks (layer_split_over_ranks); rank 0 prints."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+        rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+        dist.init_process_group("gloo")          # file names and timings only: the driver processes exchange nothing
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        blk = layer_split_over_ranks(dist, rank, world, visible.split(",")[local] if visible else str(local), args)
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return None
+        shape = blk.get("workload", "decoder layer").split(" layer")[0].replace("one ", "")
+        return {"metric": f"{shape} layer prove time", "unit": "s", "value": blk.get("seconds"), "higher_is_better": False,
+                "impl": "ours", "n_gpus": world, "mode": "one resident driver process per GPU, proofs shared", **blk}
+    if world > 1 and int(os.environ.get("RANK", "0")) != 0:
+        return None
     if args.impl == "reference":
         modes = [("process", max(1, args.layer_repeat))]
     else:
@@ -1016,7 +1045,9 @@ def main():
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.workload == "layer":
-        print(json.dumps(run_layer(args)))
+        out = run_layer(args)
+        if out is not None:
+            print(json.dumps(out))
         return
     if args.workload == "opening":
         print(json.dumps(run_opening(args)))

@@ -256,6 +256,19 @@ int zkb_tlookup_combine(const zkb_fr_t* h_parts, unsigned world, size_t D, size_
 int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N,
                        const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                        zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* All log2 N rounds of the same proof without the verifier replay (proof.cu:190-241; no counterpart in the
+ * reference: the building block of the multi-GPU split).  h_sums receives the (K+1) coefficient sums of every
+ * round, h_tails the K entries that are left (the inputs themselves when N is 1). */
+int zkb_multi_hadamard_partial(const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                               zkb_fr_t* h_sums, zkb_fr_t* h_tails, void* stream);
+/* The exchange step of the split multi_hadamard_sumchecks (no counterpart in the reference; proof.cu:190-241 are the
+ * checks replayed).  The K tensors of 2^kN entries are dealt out round-robin; rank p has run zkb_multi_hadamard_partial
+ * on its share with the challenges h_u + log2 world, h_v + log2 world.  h_parts holds the `world` blocks in rank
+ * order: (kN - log2 world) * (K+1) sums, then the rank's K surviving entries.  The sums are weighted by eq(u; p) over
+ * the rank's index bits and added, the last log2 world rounds run here on the surviving entries; h_polys receives
+ * (K+1) * kN coefficients.  Pure host arithmetic; ZKB_ERR_VERIFY with the reference's message when a round fails. */
+int zkb_multi_hadamard_combine(const zkb_fr_t* h_parts, unsigned world, unsigned K, unsigned kN, const zkb_fr_t* h_u,
+                               const zkb_fr_t* h_v, const zkb_fr_t* h_claim, zkb_fr_t* h_polys, zkb_fr_t* h_final);
 /* hadamard_product_sumcheck / inner_product_sumcheck / binary_sumcheck
  * (proof.cu:12-160), including the factor 2^-256 the reference leaves on the
  * product terms.  h_proof receives 3*k + 2 (3*k + 1 for binary) elements. */
@@ -381,6 +394,11 @@ int zkb_tlookup_prove_sharded(const zkb_fr_t* d_S_local, const zkb_fr_t* d_table
                               size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_beta,
                               const zkb_fr_t* h_u, const zkb_fr_t* h_v,
                               zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
+/* multi_hadamard_sumchecks (proof.cu:190-241) with the K tensors dealt out round-robin: rank p holds X_k[p::P]
+ * (N / P entries each); N, the claim and the challenges are those of the whole proof.  Outputs as
+ * zkb_multi_hadamard, on every rank. */
+int zkb_multi_hadamard_sharded(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs_local, unsigned K, size_t N,
+                               const zkb_fr_t* h_u, const zkb_fr_t* h_v, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream);
 
 #ifdef __cplusplus
 }

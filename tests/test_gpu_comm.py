@@ -131,6 +131,28 @@ def test_tlookup_sharded_single_rank(dev):
     assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
 
 
+def test_multi_hadamard_sharded_single_rank(dev):
+    import ctypes
+    z = dev.z
+    K, N = 3, 1 << 11
+    rng = np.random.Generator(np.random.PCG64(21))
+    Xs = [_rand_fr(rng, N) for _ in range(K)]
+    bufs = [z.fr_buffer(x) for x in Xs]
+    ptrs = (ctypes.c_void_p * K)(*[b.ptr for b in bufs])
+    u, v = _rand_fr(rng, 11), _rand_fr(rng, 11)
+    # the claim the proof needs: the product tensor evaluated at u
+    prod, claim = z.DeviceBuffer(32 * N), np.zeros((1, 8), dtype=np.uint32)
+    z.call("zkb_fr_mul", z._p(bufs[0]), z._p(bufs[1]), z._p(prod), z.sz(N), z._p(0))
+    z.call("zkb_fr_mul", z._p(prod), z._p(bufs[2]), z._p(prod), z.sz(N), z._p(0))
+    z.call("zkb_fr_mle_eval", z._p(prod), z.sz(N), z._p(u), z.u32(11), z._p(claim), z._p(0))
+    res = []
+    for name in ("zkb_multi_hadamard", "zkb_multi_hadamard_sharded"):
+        polys, fin = np.zeros((11 * (K + 1), 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        z.call(name, z._p(claim), ptrs, z.u32(K), z.sz(N), z._p(u), z._p(v), z._p(polys), z._p(fin), z._p(0))
+        res.append((polys, fin))
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
+
+
 RANK_SCRIPT = textwrap.dedent('''
     import ctypes, json, os, sys, time
     from pathlib import Path
@@ -211,6 +233,21 @@ RANK_SCRIPT = textwrap.dedent('''
            z._p(z.fr_buffer(limbs(counts[rank::world]))), z.sz(D), z.sz(N), z._p(alpha), z._p(beta), z._p(u), z._p(v), z._p(q1), z._p(f1),
            z._p(0))
     out["tlookup"] = bool(np.array_equal(q0, q1) and np.array_equal(f0, f1))
+    # multi-Hadamard sumcheck of three tensors
+    K, Nh = 3, 1 << 10
+    Xh = [rand_fr(rng, Nh) for _ in range(K)]
+    uh, vh, ch = rand_fr(rng, 10), rand_fr(rng, 10), rand_fr(rng, 1)   # an arbitrary claim: only round 0's check sees it
+    whole_b = [z.fr_buffer(x) for x in Xh]; share_b = [z.fr_buffer(np.ascontiguousarray(x[rank::world])) for x in Xh]
+    res = []
+    for name, bufs in (("zkb_multi_hadamard", whole_b), ("zkb_multi_hadamard_sharded", share_b)):
+        ptrs = (ctypes.c_void_p * K)(*[b.ptr for b in bufs])
+        hp, hf = np.zeros((10 * (K + 1), 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        try:
+            z.call(name, z._p(ch), ptrs, z.u32(K), z.sz(Nh), z._p(uh), z._p(vh), z._p(hp), z._p(hf), z._p(0))
+            res.append("no error")
+        except z.ZkbError as ex:
+            res.append((str(ex).split(":")[-1].strip(), hp.tobytes()))
+    out["hadamard"] = bool(res[0] == res[1] and res[0] != "no error")
     z.call("zkb_comm_destroy")
     print("RESULT " + json.dumps(out))
 ''')
@@ -230,4 +267,4 @@ def test_two_ranks_match_single_gpu(tmp_path):
         out, _ = pr.communicate(timeout=600)
         assert pr.returncode == 0, out[-2000:]
         line = [l for l in out.splitlines() if l.startswith("RESULT ")][-1]
-        assert json.loads(line[7:]) == {"commit": True, "commit_cols": True, "zkfc": True, "tlookup": True}, out[-2000:]
+        assert json.loads(line[7:]) == {"commit": True, "commit_cols": True, "zkfc": True, "tlookup": True, "hadamard": True}, out[-2000:]

@@ -464,6 +464,51 @@ def test_sharded_tlookup_equals_the_whole_proof(dev, world, logD, logN):
     assert np.array_equal(cpolys, polys) and np.array_equal(cfinal, final)
 
 
+@pytest.mark.parametrize("world,K,logN", [(2, 3, 12), (4, 2, 14), (8, 4, 10), (8, 2, 3)])
+def test_sharded_multi_hadamard_equals_the_whole_proof(dev, world, K, logN):
+    """The multi-GPU split of multi_hadamard_sumchecks with the ranks emulated in one process: every rank's rounds on the
+    device (zkb_multi_hadamard_partial on its round-robin share), then zkb_multi_hadamard_combine and its Python twin;
+    polynomials and final claim equal zkb_multi_hadamard's on the whole tensors."""
+    import ctypes
+    from zkllm_ccs2024_b200 import sharding as S
+    z = dev.z
+    N = 1 << logN
+    kP = world.bit_length() - 1
+    rng = np.random.Generator(np.random.PCG64(world * 100 + K * 10 + logN))
+    Xs = [_rand_fr(rng, N) for _ in range(K)]
+    u, v = _rand_fr(rng, logN), _rand_fr(rng, logN)
+    bufs = [z.fr_buffer(x) for x in Xs]
+    prod, claim = z.DeviceBuffer(32 * N), np.zeros((1, 8), dtype=np.uint32)
+    first = bufs[0]
+    for j in range(1, K):
+        dev.call("zkb_fr_mul", z._p(first), z._p(bufs[j]), z._p(prod), z.sz(N), z._p(0))
+        first = prod
+    dev.call("zkb_fr_mle_eval", z._p(first), z.sz(N), z._p(u), z.u32(logN), z._p(claim), z._p(0))
+    polys, final = np.zeros((logN * (K + 1), 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+    ptrs = (ctypes.c_void_p * K)(*[b.ptr for b in bufs])
+    dev.call("zkb_multi_hadamard", z._p(claim), ptrs, z.u32(K), z.sz(N), z._p(u), z._p(v), z._p(polys), z._p(final), z._p(0))
+    local = logN - kP
+    block = local * (K + 1) + K
+    parts = np.zeros((world, block, 8), dtype=np.uint32)
+    for rank in range(world):
+        shares = [z.fr_buffer(np.ascontiguousarray(x[rank::world])) for x in Xs]
+        sp = (ctypes.c_void_p * K)(*[b.ptr for b in shares])
+        dev.call("zkb_multi_hadamard_partial", sp, z.u32(K), z.sz(N // world), z._p(S.fr_host_or_dummy(u[kP:])),
+                 z._p(S.fr_host_or_dummy(v[kP:])), z._p(parts[rank]), z._p(parts[rank, local * (K + 1):]), z._p(0))
+    cpolys, cfinal = np.zeros_like(polys), np.zeros_like(final)
+    dev.call("zkb_multi_hadamard_combine", z._p(parts), z.u32(world), z.u32(K), z.u32(logN), z._p(u), z._p(v), z._p(claim), z._p(cpolys),
+             z._p(cfinal))
+    assert np.array_equal(cpolys, polys) and np.array_equal(cfinal, final)
+    per_rank = []
+    for rank in range(world):
+        vals = S.fr_limbs_to_ints(parts[rank])
+        per_rank.append(([vals[r * (K + 1):(r + 1) * (K + 1)] for r in range(local)], vals[local * (K + 1):]))
+    got_polys, got_final = S.multi_hadamard_combine(per_rank, S.fr_limbs_to_ints(u), S.fr_limbs_to_ints(v), S.fr_limbs_to_ints(claim)[0])
+    want = S.fr_limbs_to_ints(polys)
+    assert got_polys == [want[r * (K + 1):(r + 1) * (K + 1)] for r in range(logN)]
+    assert got_final == S.fr_limbs_to_ints(final)[0]
+
+
 def test_host_buffer_commitment_equals_the_device_path(dev):
     """zkb_commit_i32_host on a 1030 x 16384 matrix with 31-bit entries in some rows (five windows) against
     zkb_commit_i32 on device buffers, and three rows against the C++ oracle."""

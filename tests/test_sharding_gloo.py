@@ -59,7 +59,16 @@ def _worker(rank, world, port, m, q):
     polys, final = S.sharded_zkip(S.fr_ints_to_limbs(sums), S.fr_ints_to_limbs(la), S.fr_ints_to_limbs(lb), u, claim)
     proof = []
     ok_zkip = final == R.zkip(claim, a, b, u, proof) and polys == proof
-    q.put((rank, ok_rows and ok_mle and ok_zkip, parts, red))
+    # multi-Hadamard sumcheck of three 64-element tensors dealt out the same way
+    Xs = [[rs.randrange(R.R_MOD) for _ in range(64)] for _ in range(3)]
+    vh = [rs.randrange(R.R_MOD) for _ in range(6)]
+    eqw = [S.block_weight(u, i) for i in range(64)]
+    hclaim = sum(eqw[i] * Xs[0][i] * Xs[1][i] * Xs[2][i] for i in range(64)) % R.R_MOD
+    sums, tails = S.multi_hadamard_local_rounds([X[rank::world] for X in Xs], u[1:], vh[1:])
+    hpolys, hfinal = S.sharded_multi_hadamard(sums, tails, u, vh, hclaim)
+    hproof = []
+    ok_had = hfinal == R.multi_hadamard_sumchecks(hclaim, Xs, u, vh, hproof) and hpolys == hproof
+    q.put((rank, ok_rows and ok_mle and ok_zkip and ok_had, parts, red))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -137,3 +146,45 @@ def test_cpp_zkip_combine_matches_the_python_one():
             z.call("zkb_zkip_combine", z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.u32(k), z._p(S.fr_ints_to_limbs(u)),
                    z._p(S.fr_ints_to_limbs([claim + 1])), z._p(polys), z._p(final))
         assert "claim != p(0) + p(1)" in str(e.value)
+
+
+def test_cpp_multi_hadamard_combine_matches_the_reference_algorithm():
+    """zkb_multi_hadamard_combine is host arithmetic: per-rank blocks computed in Python go in, and the round polynomials of
+    multi_hadamard_sumchecks on the whole tensors (oracle) must come out, for 1, 2, 4 and 8 ranks."""
+    from tests.conftest import load_package
+    z = load_package()
+    from zkllm_ccs2024_b200 import sharding as S
+    from oracle import pyref as R
+    rng = random.Random(19)
+    for n, K, world in ((32, 3, 2), (32, 2, 4), (16, 4, 8), (16, 1, 1), (8, 6, 8)):
+        k = n.bit_length() - 1
+        kP = world.bit_length() - 1
+        Xs = [[rng.randrange(R.R_MOD) for _ in range(n)] for _ in range(K)]
+        u = [rng.randrange(R.R_MOD) for _ in range(k)]
+        v = [rng.randrange(R.R_MOD) for _ in range(k)]
+        eqw = [S.block_weight(u, i) for i in range(n)]
+        claim = 0
+        for i in range(n):
+            t = eqw[i]
+            for X in Xs:
+                t = t * X[i] % R.R_MOD
+            claim = (claim + t) % R.R_MOD
+        want = []
+        want_final = R.multi_hadamard_sumchecks(claim, Xs, u, v, want)
+        per_rank, flat = [], []
+        for p in range(world):
+            sums, tails = S.multi_hadamard_local_rounds([X[p::world] for X in Xs], u[kP:], v[kP:])
+            per_rank.append((sums, tails))
+            flat += [c for row in sums for c in row] + tails
+        py_polys, py_final = S.multi_hadamard_combine(per_rank, u, v, claim)
+        assert py_polys == want and py_final == want_final
+        polys, final = np.zeros(((K + 1) * k, 8), dtype=np.uint32), np.zeros((1, 8), dtype=np.uint32)
+        args = lambda c: (z._p(S.fr_ints_to_limbs(flat)), z.u32(world), z.u32(K), z.u32(k), z._p(S.fr_ints_to_limbs(u)),
+                          z._p(S.fr_ints_to_limbs(v)), z._p(S.fr_ints_to_limbs([c])), z._p(polys), z._p(final))
+        z.call("zkb_multi_hadamard_combine", *args(claim))
+        got = S.fr_limbs_to_ints(polys)
+        assert [got[(K + 1) * r:(K + 1) * (r + 1)] for r in range(k)] == want
+        assert S.fr_limbs_to_ints(final)[0] == want_final
+        with pytest.raises(z.ZkbError) as e:
+            z.call("zkb_multi_hadamard_combine", *args(claim + 1))
+        assert "multi_hadamard_sumchecks: claim != p(0) + p(1)" in str(e.value)

@@ -158,9 +158,74 @@ int zkb_tlookup_combine(const zkb_fr_t* h_parts, unsigned world, size_t D, size_
     return tlookup_assemble(flat.data(), D, N, h_alpha, h_u, h_v, h_polys, h_final);
 }
 
+// Per-rank block: (kN - log2 world) * (K + 1) coefficient sums of the rank's own rounds, then its K surviving entries.
+int zkb_multi_hadamard_combine(const zkb_fr_t* h_parts, unsigned world, unsigned K, unsigned kN, const zkb_fr_t* h_u,
+                               const zkb_fr_t* h_v, const zkb_fr_t* h_claim, zkb_fr_t* h_polys, zkb_fr_t* h_final) {
+    if (!world || (world & (world - 1))) return fail(ZKB_ERR_ARG, "multi_hadamard: the number of ranks must be a power of two");
+    if (K < 1 || K > 6) return fail(ZKB_ERR_LIMIT, "multi_hadamard: between 1 and 6 tensors");
+    const unsigned kP = log2u(world);
+    if (kN < kP) return fail(ZKB_ERR_DIM, "multi_hadamard: more ranks than entries");
+    const unsigned local = kN - kP, W = K + 1;
+    const size_t block = (size_t)local * W + K;
+    std::vector<H> polys((size_t)kN * W, hfr::zero());
+    // a rank's sums carry eq over the variables above its index bits; the factor of the index bits is its weight
+    for (unsigned p = 0; p < world; ++p) {
+        const H w = eq_weight(h_u, kP, p);
+        for (size_t i = 0; i < (size_t)local * W; ++i)
+            polys[i] = hfr::add(polys[i], hfr::mul(w, hfr::load(h_parts[p * block + i])));
+    }
+    // the last log2(world) rounds on the `world` surviving entries of every tensor (entry p = rank p)
+    std::vector<std::vector<H>> x(K, std::vector<H>(world));
+    for (unsigned p = 0; p < world; ++p)
+        for (unsigned j = 0; j < K; ++j) x[j][p] = hfr::load(h_parts[p * block + (size_t)local * W + j]);
+    size_t M = world;
+    for (unsigned r = local; r < kN; ++r) {
+        const size_t half = M / 2;
+        const unsigned below = kN - 1 - r;               // variables still unbound below this one
+        const H v = hfr::load(h_v[kN - 1 - r]);
+        std::vector<H> c(W, hfr::zero());
+        for (size_t g = 0; g < half; ++g) {
+            std::vector<H> prod(W, hfr::zero());         // prod_j (x_j[g] + t (x_j[g + half] - x_j[g]))
+            prod[0] = hfr::from_u64(1);
+            for (unsigned j = 0; j < K; ++j) {
+                const H a0 = x[j][g], d = hfr::sub(x[j][g + half], x[j][g]);
+                for (unsigned i = j + 1; i >= 1; --i) prod[i] = hfr::add(hfr::mul(prod[i], a0), hfr::mul(prod[i - 1], d));
+                prod[0] = hfr::mul(prod[0], a0);
+                x[j][g] = hfr::add(a0, hfr::mul(v, d));
+            }
+            const H e = eq_weight(h_u, below, g);
+            for (unsigned i = 0; i < W; ++i) c[i] = hfr::add(c[i], hfr::mul(e, prod[i]));
+        }
+        for (unsigned i = 0; i < W; ++i) polys[(size_t)r * W + i] = c[i];
+        M = half;
+    }
+    for (size_t i = 0; i < polys.size(); ++i) h_polys[i] = hfr::store(polys[i]);
+    return hadamard_replay(h_claim, h_polys, K, kN, h_u, h_v, h_final);
+}
+
 }  // extern "C"
 
 namespace zkb {
+
+int hadamard_replay(const zkb_fr_t* h_claim, const zkb_fr_t* h_polys, unsigned K, unsigned kN, const zkb_fr_t* h_u,
+                    const zkb_fr_t* h_v, zkb_fr_t* h_final) {
+    H claim = hfr::load(*h_claim);
+    std::vector<H> c(K + 1);
+    for (unsigned r = 0; r < kN; ++r) {
+        for (unsigned i = 0; i <= K; ++i) c[i] = hfr::load(h_polys[(size_t)r * (K + 1) + i]);
+        const H ub = hfr::load(h_u[kN - 1 - r]);
+        const H e0 = hfr::sub(hfr::from_u64(1), ub);
+        const H e1 = hfr::sub(hfr::add(ub, ub), hfr::from_u64(1));
+        // (c * eq)(0) + (c * eq)(1) = c(0) e0 + c(1) (e0 + e1)
+        H c_at1 = hfr::zero();
+        for (unsigned i = 0; i <= K; ++i) c_at1 = hfr::add(c_at1, c[i]);
+        const H lhs = hfr::add(hfr::mul(c[0], e0), hfr::mul(c_at1, hfr::add(e0, e1)));
+        if (!hfr::eq(claim, lhs)) return fail(ZKB_ERR_VERIFY, "multi_hadamard_sumchecks: claim != p(0) + p(1)");
+        claim = hfr::poly_eval(c.data(), (int)K + 1, hfr::load(h_v[kN - 1 - r]));
+    }
+    *h_final = hfr::store(claim);
+    return ZKB_OK;
+}
 
 // Round polynomials of the lookup sumcheck from the per-round sums, with the
 // reference's checks (tlookup.cu:281-322): sums[0] = sum B*m, then 11 values per round

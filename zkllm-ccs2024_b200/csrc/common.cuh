@@ -107,5 +107,9 @@ inline unsigned div_up(size_t a, size_t b) { return (unsigned)((a + b - 1) / b);
 // reference's checks (defined in combine.cu; used by the single- and the multi-GPU prover).
 int tlookup_assemble(const zkb_fr_t* sums, size_t D, size_t N, const zkb_fr_t* h_alpha, const zkb_fr_t* h_u,
                      const zkb_fr_t* h_v, zkb_fr_t* h_polys, zkb_fr_t* h_final);
+// The verifier equations of multi_hadamard_sumchecks (proof.cu:190-241) on the K + 1 coefficients of each of the kN
+// rounds: claim == (c * eq(u))(0) + (c * eq(u))(1), next claim = c(v).  Host arithmetic (combine.cu).
+int hadamard_replay(const zkb_fr_t* h_claim, const zkb_fr_t* h_polys, unsigned K, unsigned kN, const zkb_fr_t* h_u,
+                    const zkb_fr_t* h_v, zkb_fr_t* h_final);
 
 }  // namespace zkb

@@ -692,49 +692,34 @@ static FoldDigits fold_digits(const zkb_fr_t& u) {
 // The shortcuts of the opening (endomorphism fold, T rows derived from earlier proof points, the tail as one
 // MSM) multiply scalars modulo r, which is the same group element only for points of order r - what
 // Commitment::random makes (commitment.cu:3-8), but not what an arbitrary generator file has to hold.  Every
-// generator set is therefore checked once, [r] P = O for all P, with r in 65 signed 4-bit digits shared by all
-// threads; the verdict is kept under a fingerprint of the set.  A set that fails takes the reference's own
-// arithmetic (me_open_step, commitment.cu:79-109): three MSM rows in every round, the fold as a plain
-// double-and-add by the challenge's 256 raw bits, every round folded.
-struct OrderDigits { signed char d[65]; };
-static OrderDigits order_digits() {
-    const uint64_t rmod[4] = {0xffffffff00000001ull, 0x53bda402fffe5bfeull, 0x3339d80809a1d805ull, 0x73eda753299d7d48ull};
-    OrderDigits out;
-    int carry = 0;
-    for (int w = 0; w < 65; ++w) {
-        int x = carry;
-        if (w < 64) x += (int)((rmod[w >> 4] >> (4 * (w & 15))) & 15u);
-        carry = 0;
-        if (x >= 8) { x -= 16; carry = 1; }
-        out.d[w] = (signed char)x;
+// generator set is therefore checked once; the verdict is kept under a fingerprint of the set.  A set that fails
+// takes the reference's own arithmetic (me_open_step, commitment.cu:79-109): three MSM rows in every round, the
+// fold as a plain double-and-add by the challenge's 256 raw bits, every round folded.
+//
+// The check is the endomorphism test of BLS12 curves (M. Scott, "A note on group membership tests for G1, G2 and
+// GT on BLS pairing-friendly curves", 2021): with the curve parameter z (r = z^4 - z^2 + 1) a curve point P has
+// order r exactly when phi(P) = [z^2 - 1] P, written here as phi(P) + P = [|z|] [|z|] P.  |z| = 0xd201000000010000
+// has six bits set, so a point costs 126 doublings and 12 additions instead of the 255 and ~70 of [r] P = O.
+__device__ static G1Jac g1_mul_abs_z(const G1Jac& p) {
+    constexpr unsigned long long kAbsZ = 0xd201000000010000ull;
+    G1Jac acc = p;
+#pragma unroll 1
+    for (int b = 62; b >= 0; --b) {
+        acc = g1_double_call(acc);
+        if ((kAbsZ >> b) & 1ull) acc = g1_add_call(acc, p);
     }
-    return out;
+    return acc;
 }
 
-__global__ void __launch_bounds__(128) g1_order_check_kernel(const G1Jac* __restrict__ gens, size_t n, OrderDigits dg,
-                                                              unsigned* __restrict__ bad) {
+__global__ void __launch_bounds__(128) g1_order_check_kernel(const G1Jac* __restrict__ gens, size_t n, unsigned* __restrict__ bad) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const G1Jac p = g1_load(gens + i);
         if (g1_is_identity(p)) continue;
-        G1Jac tab[8];
-        tab[0] = p;
-#pragma unroll 1
-        for (int t = 1; t < 8; ++t) tab[t] = (t & 1) ? g1_double_call(tab[t >> 1]) : g1_add_call(tab[t - 1], p);
-        G1Jac acc = g1_identity();
-#pragma unroll 1
-        for (int w = 64; w >= 0; --w) {
-            if (w != 64) {
-#pragma unroll 1
-                for (int d = 0; d < 4; ++d) acc = g1_double_call(acc);
-            }
-            const int a = dg.d[w];
-            if (a) {
-                G1Jac t = tab[(a < 0 ? -a : a) - 1];
-                if (a < 0) t = g1_neg(t);
-                acc = g1_add_call(acc, t);
-            }
-        }
-        if (!g1_is_identity(acc)) atomicOr(bad, 1u);
+        const G1Jac zzp = g1_mul_abs_z(g1_mul_abs_z(p));
+        G1Jac e = p;
+        e.x = fq_mul(e.x, fq_beta_mont());
+        const G1Jac lhs = g1_add_call(e, p);
+        if (!g1_is_identity(g1_add_call(zzp, g1_neg(lhs)))) atomicOr(bad, 1u);
     }
 }
 
@@ -758,7 +743,7 @@ static int generators_have_order_r(const G1Jac* d_gens, size_t n, bool* ok, Scra
     unsigned* d_bad = scratch.get_n<unsigned>(4);
     if (!d_bad) return ZKB_ERR_CUDA;
     ZKB_CUDA(cudaMemsetAsync(d_bad, 0, 16, s));
-    ZKB_LAUNCH(g1_order_check_kernel, grid_for(n, 128), 128, 0, s, d_gens, n, order_digits(), d_bad);
+    ZKB_LAUNCH(g1_order_check_kernel, grid_for(n, 128), 128, 0, s, d_gens, n, d_bad);
     unsigned h_bad = 0;
     ZKB_CUDA(cudaMemcpyAsync(&h_bad, d_bad, 4, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));

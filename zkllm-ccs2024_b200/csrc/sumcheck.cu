@@ -1118,6 +1118,54 @@ static int tlookup_rounds_device(const Fr* d_S, const Fr* d_table, const Fr* d_m
     return ZKB_OK;
 }
 
+// All log2(N) rounds of multi_hadamard_sumchecks (proof.cu:190-241) on the device: round r pairs entry g with g + M/2,
+// weights the K + 1 coefficients of prod_k (X_k[g] + t (X_k[g + M/2] - X_k[g])) by eq over the variables below the
+// current one (u[0 .. kN-1-r)) and folds with v[kN-1-r].  d_sums receives K + 1 sums per round; fin[j] points at the one
+// entry of tensor j that is left (the input itself when N is 1).
+static int hadamard_rounds_device(const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                                  Fr* d_sums, const Fr** fin, Scratch& scratch, cudaStream_t s) {
+    const unsigned kN = clog2(N);
+    HadamardPtrs ptrs;
+    for (unsigned j = 0; j < K; ++j) ptrs.in[j] = CFR(h_d_Xs[j]);
+    if (kN) {
+        Fr* bufs[2][kMaxHadamard];
+        for (int i = 0; i < 2; ++i)
+            for (unsigned j = 0; j < K; ++j) {
+                bufs[i][j] = scratch.get_n<Fr>((N / 2) >> i ? (N / 2) >> i : 1);
+                if (!bufs[i][j]) return ZKB_ERR_CUDA;
+            }
+        const unsigned max_grid = (unsigned)sm_count() * 4;
+        Fr* partial = scratch.get_n<Fr>((size_t)max_grid * (K + 1));
+        unsigned* ticket = scratch.get_n<unsigned>(4);
+        if (!partial || !ticket) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
+        size_t M = N;
+        EqTab tabs[33];
+        ZKB_TRY(make_eq_series(h_u, kN - 1, kN, 0, tabs, scratch, s));
+        for (unsigned r = 0; r < kN; ++r) {
+            const size_t half = M / 2;
+            const EqTab eq = tabs[r];
+            for (unsigned j = 0; j < K; ++j) ptrs.out[j] = bufs[r & 1][j];
+            const Fr v = dev_fr_mont(h_v[kN - 1 - r]);
+            unsigned R, grid;
+            pieces_for(half, &R, &grid);
+            Fr* out = d_sums + (size_t)r * (K + 1);
+            switch (K) {
+                case 1: ZKB_LAUNCH(hadamard_round_kernel<1>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+                case 2: ZKB_LAUNCH(hadamard_round_kernel<2>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+                case 3: ZKB_LAUNCH(hadamard_round_kernel<3>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+                case 4: ZKB_LAUNCH(hadamard_round_kernel<4>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+                case 5: ZKB_LAUNCH(hadamard_round_kernel<5>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+                default: ZKB_LAUNCH(hadamard_round_kernel<6>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
+            }
+            for (unsigned j = 0; j < K; ++j) ptrs.in[j] = bufs[r & 1][j];
+            M = half;
+        }
+    }
+    for (unsigned j = 0; j < K; ++j) fin[j] = ptrs.in[j];
+    return ZKB_OK;
+}
+
 extern "C" {
 
 int zkb_tlookup_partial(const zkb_fr_t* d_S, const zkb_fr_t* d_table, const zkb_fr_t* d_m, size_t D, size_t N,
@@ -1186,60 +1234,29 @@ int zkb_multi_hadamard(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs, u
     if (N == 0 || (N & (N - 1))) return fail(ZKB_ERR_DIM, "N is not a power of 2");
     const unsigned kN = clog2(N);
     Scratch scratch(s);
-    Fr* bufs[2][kMaxHadamard];
-    for (int i = 0; i < 2; ++i)
-        for (unsigned j = 0; j < K; ++j) {
-            bufs[i][j] = scratch.get_n<Fr>((N / 2) >> i ? (N / 2) >> i : 1);
-            if (!bufs[i][j]) return ZKB_ERR_CUDA;
-        }
-    const unsigned max_grid = (unsigned)sm_count() * 4;
-    Fr* partial = scratch.get_n<Fr>((size_t)max_grid * (K + 1));
-    unsigned* ticket = scratch.get_n<unsigned>(4);
     Fr* d_sums = scratch.get_n<Fr>((size_t)kN * (K + 1));
-    if (!partial || !ticket || !d_sums) return ZKB_ERR_CUDA;
-    ZKB_CUDA(cudaMemsetAsync(ticket, 0, 16, s));
-    HadamardPtrs ptrs;
-    for (unsigned j = 0; j < K; ++j) ptrs.in[j] = CFR(h_d_Xs[j]);
-    size_t M = N;
-    EqTab tabs[33];
-    if (kN) ZKB_TRY(make_eq_series(h_u, kN - 1, kN, 0, tabs, scratch, s));
-    for (unsigned r = 0; r < kN; ++r) {
-        const size_t half = M / 2;
-        const EqTab eq = tabs[r];
-        for (unsigned j = 0; j < K; ++j) ptrs.out[j] = bufs[r & 1][j];
-        const Fr v = dev_fr_mont(h_v[kN - 1 - r]);
-        unsigned R, grid;
-        pieces_for(half, &R, &grid);
-        Fr* out = d_sums + (size_t)r * (K + 1);
-        switch (K) {
-            case 1: ZKB_LAUNCH(hadamard_round_kernel<1>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-            case 2: ZKB_LAUNCH(hadamard_round_kernel<2>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-            case 3: ZKB_LAUNCH(hadamard_round_kernel<3>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-            case 4: ZKB_LAUNCH(hadamard_round_kernel<4>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-            case 5: ZKB_LAUNCH(hadamard_round_kernel<5>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-            default: ZKB_LAUNCH(hadamard_round_kernel<6>, grid, kThreads, 0, s, ptrs, half, v, eq, R, partial, ticket, out); break;
-        }
-        for (unsigned j = 0; j < K; ++j) ptrs.in[j] = bufs[r & 1][j];
-        M = half;
-    }
+    if (!d_sums) return ZKB_ERR_CUDA;
+    const Fr* fin[kMaxHadamard];
+    ZKB_TRY(hadamard_rounds_device(h_d_Xs, K, N, h_u, h_v, d_sums, fin, scratch, s));
     ZKB_CUDA(cudaMemcpyAsync(h_polys, d_sums, (size_t)kN * (K + 1) * 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
-    using hfr::H;
-    H claim = hfr::load(*h_claim);
-    std::vector<H> c(K + 1);
-    for (unsigned r = 0; r < kN; ++r) {
-        for (unsigned i = 0; i <= K; ++i) c[i] = hfr::load(h_polys[(size_t)r * (K + 1) + i]);
-        const H ub = hfr::load(h_u[kN - 1 - r]);
-        const H e0 = hfr::sub(hfr::from_u64(1), ub);
-        const H e1 = hfr::sub(hfr::add(ub, ub), hfr::from_u64(1));
-        // (c * eq)(0) + (c * eq)(1) = c(0) e0 + c(1) (e0 + e1)
-        H c_at1 = hfr::zero();
-        for (unsigned i = 0; i <= K; ++i) c_at1 = hfr::add(c_at1, c[i]);
-        const H lhs = hfr::add(hfr::mul(c[0], e0), hfr::mul(c_at1, hfr::add(e0, e1)));
-        if (!hfr::eq(claim, lhs)) return fail(ZKB_ERR_VERIFY, "multi_hadamard_sumchecks: claim != p(0) + p(1)");
-        claim = hfr::poly_eval(c.data(), (int)K + 1, hfr::load(h_v[kN - 1 - r]));
-    }
-    *h_final = hfr::store(claim);
+    return hadamard_replay(h_claim, h_polys, K, kN, h_u, h_v, h_final);
+}
+
+int zkb_multi_hadamard_partial(const zkb_fr_t* const* h_d_Xs, unsigned K, size_t N, const zkb_fr_t* h_u, const zkb_fr_t* h_v,
+                               zkb_fr_t* h_sums, zkb_fr_t* h_tails, void* stream) {
+    cudaStream_t s = as_stream(stream);
+    if (K < 1 || K > (unsigned)kMaxHadamard) return fail(ZKB_ERR_LIMIT, "multi_hadamard: between 1 and 6 tensors");
+    if (N == 0 || (N & (N - 1))) return fail(ZKB_ERR_DIM, "N is not a power of 2");
+    const unsigned kN = clog2(N);
+    Scratch scratch(s);
+    Fr* d_sums = scratch.get_n<Fr>((size_t)kN * (K + 1) + 1);
+    if (!d_sums) return ZKB_ERR_CUDA;
+    const Fr* fin[kMaxHadamard];
+    ZKB_TRY(hadamard_rounds_device(h_d_Xs, K, N, h_u, h_v, d_sums, fin, scratch, s));
+    if (kN) ZKB_CUDA(cudaMemcpyAsync(h_sums, d_sums, (size_t)kN * (K + 1) * 32, cudaMemcpyDeviceToHost, s));
+    for (unsigned j = 0; j < K; ++j) ZKB_CUDA(cudaMemcpyAsync(h_tails + j, fin[j], 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
     return ZKB_OK;
 }
 
@@ -1368,6 +1385,34 @@ int zkb_tlookup_prove_sharded(const zkb_fr_t* d_S_local, const zkb_fr_t* d_table
     ZKB_CUDA(cudaMemcpyAsync(all.data(), d_all, all.size() * 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return zkb_tlookup_combine(all.data(), (unsigned)world, D, N, h_alpha, h_beta, h_u, h_v, h_polys, h_final);
+}
+
+int zkb_multi_hadamard_sharded(const zkb_fr_t* h_claim, const zkb_fr_t* const* h_d_Xs_local, unsigned K, size_t N,
+                               const zkb_fr_t* h_u, const zkb_fr_t* h_v, zkb_fr_t* h_polys, zkb_fr_t* h_final, void* stream) {
+    ZKB_API_RANGE();
+    cudaStream_t s = as_stream(stream);
+    const int world = comm_world();
+    if (world < 1) return fail(ZKB_ERR_ARG, "comm: not initialised (zkb_comm_init)");
+    if (world & (world - 1)) return fail(ZKB_ERR_ARG, "multi_hadamard: the number of ranks must be a power of two");
+    if (K < 1 || K > (unsigned)kMaxHadamard) return fail(ZKB_ERR_LIMIT, "multi_hadamard: between 1 and 6 tensors");
+    if (N == 0 || (N & (N - 1))) return fail(ZKB_ERR_DIM, "N is not a power of 2");
+    if (N < (size_t)world) return fail(ZKB_ERR_DIM, "multi_hadamard: more ranks than entries");
+    const unsigned kN = clog2(N), kP = clog2((size_t)world), local = kN - kP;
+    const size_t block = (size_t)local * (K + 1) + K;     // this rank's sums, then its K surviving entries
+    Scratch scratch(s);
+    Fr* d_part = scratch.get_n<Fr>(block);
+    Fr* d_all = scratch.get_n<Fr>(block * world);
+    if (!d_part || !d_all) return ZKB_ERR_CUDA;
+    const Fr* fin[kMaxHadamard];
+    // a rank's own rounds bind the variables above its index bits
+    ZKB_TRY(hadamard_rounds_device(h_d_Xs_local, K, N / world, h_u + kP, h_v + kP, d_part, fin, scratch, s));
+    for (unsigned j = 0; j < K; ++j)
+        ZKB_CUDA(cudaMemcpyAsync(d_part + (size_t)local * (K + 1) + j, fin[j], 32, cudaMemcpyDeviceToDevice, s));
+    ZKB_TRY(comm_allgather(d_part, d_all, block * 32, s));
+    std::vector<zkb_fr_t> all(block * world);
+    ZKB_CUDA(cudaMemcpyAsync(all.data(), d_all, all.size() * 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaStreamSynchronize(s));
+    return zkb_multi_hadamard_combine(all.data(), (unsigned)world, K, kN, h_u, h_v, h_claim, h_polys, h_final);
 }
 
 }  // extern "C"

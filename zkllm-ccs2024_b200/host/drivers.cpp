@@ -26,8 +26,9 @@
 // The proofs are independent of one another (each draws its own challenges), so
 // the processes exchange nothing; the layer is proven when all of them exit 0.
 // The deal is the same in every process: each proof goes to the process with the
-// least estimated work so far.  Give every process its own working directory for
-// the hand-off files and the same <workdir> for the parameters.
+// least estimated work so far; a batch line "begin-layer" starts the deal afresh, so
+// that every layer of a batch is dealt out the same way.  Give every process its own
+// working directory for the hand-off files and the same <workdir> for the parameters.
 // Each stage computes its fixed-point outputs in the field, proves them and
 // throws if a verifier equation fails, printing the reference's progress lines.
 #include <chrono>
@@ -73,6 +74,7 @@ public:
         rank_ = rank;
         load_.assign(world, 0.0);
     }
+    void begin_layer() { load_.assign(load_.size(), 0.0); }
     // cost: estimated milliseconds of the proof; only the ratios matter
     bool take(double cost) {
         size_t to = 0;
@@ -89,7 +91,7 @@ public:
         double most = 0;
         for (double l : load_) most = std::max(most, l);
         cerr << "[share] process " << rank_ << " of " << load_.size() << ": " << mine_ << " of " << dealt_
-             << " proofs, estimated " << load_[rank_] << " ms here, " << most << " ms on the busiest" << endl;
+             << " proofs; last layer: estimated " << load_[rank_] << " ms here, " << most << " ms on the busiest" << endl;
     }
 
 private:
@@ -332,6 +334,11 @@ int run_batch(const Args& a) {
         for (std::string w; words >> w;) cmd.push_back(w);
         if (cmd.empty() || cmd[0][0] == '#') continue;
         const std::string stage = cmd[0];
+        if (stage == "begin-layer") {
+            g_share.begin_layer();
+            cerr << "[batch] begin-layer 0 s" << endl;
+            continue;
+        }
         if (!stage_table().count(stage)) throw std::runtime_error("batch: unknown stage " + stage);
         cmd.erase(cmd.begin());
         if (cmd.size() < stage_table().at(stage).second) throw std::runtime_error("batch: too few arguments for " + stage);

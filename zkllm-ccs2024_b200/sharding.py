@@ -411,3 +411,72 @@ def sharded_tlookup_prove(z, d_S_local, d_T_local, d_m_local, D: int, N: int, al
            z._p(np.ascontiguousarray(beta, dtype=np.uint32)), z._p(fr_host_or_dummy(u)), z._p(fr_host_or_dummy(v)), z._p(polys),
            z._p(final))
     return polys, final
+
+
+# ---- multi_hadamard_sumchecks (proof.cu:190-241) split the same way ------------------------
+# The K tensors are dealt out round-robin.  Round r weights the K + 1 coefficients of
+# prod_k (X_k[g] + t (X_k[g + M/2] - X_k[g])) by eq over the variables below the current one; that
+# weight factors into eq over the rank's index bits (one constant per rank) and eq over the rest, so
+# a rank runs its log2(N/P) rounds alone with u[log2 P:], v[log2 P:] (zkb_multi_hadamard_partial) and
+# the exchange carries its sums and its K surviving entries.
+
+def multi_hadamard_local_rounds(Xs_local, u_local, v_local):
+    """A rank's own rounds in integers (what zkb_multi_hadamard_partial computes on the device): returns
+    (sums, tails) - the K + 1 coefficient sums of every round and the K surviving entries."""
+    Xs = [[int(x) % R_MOD for x in X] for X in Xs_local]
+    u, v = list(u_local), list(v_local)
+    K, sums = len(Xs), []
+    while len(Xs[0]) > 1:
+        half = len(Xs[0]) // 2
+        below = len(u) - 1
+        c = [0] * (K + 1)
+        for g in range(half):
+            prod = [1] + [0] * K
+            for j, X in enumerate(Xs):
+                a0, d = X[g], (X[g + half] - X[g]) % R_MOD
+                for i in range(j + 1, 0, -1):
+                    prod[i] = (prod[i] * a0 + prod[i - 1] * d) % R_MOD
+                prod[0] = prod[0] * a0 % R_MOD
+            e = block_weight(u[:below], g)
+            c = [(ci + e * pi) % R_MOD for ci, pi in zip(c, prod)]
+        sums.append(c)
+        Xs = [[(X[g] + v[-1] * (X[g + half] - X[g])) % R_MOD for g in range(half)] for X in Xs]
+        u, v = u[:-1], v[:-1]
+    return sums, [X[0] for X in Xs]
+
+
+def multi_hadamard_combine(per_rank, u, v, claim: int):
+    """per_rank[p] = (sums, tails) of rank p as multi_hadamard_local_rounds returns them for its share X_k[p::P] with
+    the challenges u[log2 P:], v[log2 P:].  u, v: the global challenges.  Returns (polys, final_claim) - what
+    multi_hadamard_sumchecks on the whole tensors pushes and returns; raises RuntimeError with the reference's message."""
+    world = len(per_rank)
+    if world < 1 or world & (world - 1):
+        raise ValueError("the number of ranks must be a power of two")
+    kP = world.bit_length() - 1
+    K = len(per_rank[0][1])
+    n_local = len(per_rank[0][0])
+    w = [block_weight(u[:kP], p) for p in range(world)]
+    polys = [[sum(w[p] * per_rank[p][0][r][i] for p in range(world)) % R_MOD for i in range(K + 1)] for r in range(n_local)]
+    more, _ = multi_hadamard_local_rounds([[per_rank[p][1][j] for p in range(world)] for j in range(K)], u[:kP], v[:kP])
+    polys += more
+    kN = n_local + kP
+    for r, c in enumerate(polys):
+        ub, vb = u[kN - 1 - r], v[kN - 1 - r]
+        e0, e1 = (1 - ub) % R_MOD, (2 * ub - 1) % R_MOD
+        if claim != (c[0] * e0 + sum(c) * (e0 + e1)) % R_MOD:
+            raise RuntimeError("multi_hadamard_sumchecks: claim != p(0) + p(1)")
+        acc = 0
+        for coef in reversed(c):
+            acc = (acc * vb + coef) % R_MOD
+        claim = acc
+    return polys, claim
+
+
+def sharded_multi_hadamard(sums, tails, u, v, claim: int, group=None):
+    """The exchange step: every rank passes its (sums, tails) in integers and receives (polys, final_claim)."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    per_rank = [None] * world
+    dist.all_gather_object(per_rank, (sums, tails), group=group)
+    return multi_hadamard_combine(per_rank, u, v, claim)
