@@ -75,6 +75,14 @@ int zkb_free(void* d_ptr);                     /* waits for the device first, li
  * which calls cudaMalloc / cudaFree per tensor, fr-tensor.cu:158-179).  zkb_pool_trim waits for the device and
  * returns cached memory to the driver down to keep_bytes. */
 int zkb_pool_trim(size_t keep_bytes);
+/* Guard bands around every block the library hands out (debug aid, no counterpart in the reference; also switched on
+ * by ZKLLM_GUARD=1 in the environment): 256 bytes of a fixed pattern before and after each scratch block and each
+ * zkb_malloc buffer allocated while it is on, compared with the pattern when the block is released.
+ * zkb_guard_report waits for the device and returns how many blocks were checked, how many had a band written, the
+ * size in bytes of the first such block and its side (0 = before, 1 = after, -1 = none); reset != 0 clears the counts. */
+int zkb_guard_enable(int on);
+int zkb_guard_report(unsigned long long* blocks_checked, unsigned long long* blocks_damaged,
+                     unsigned long long* first_damaged_bytes, int* first_damaged_side, int reset);
 /* Page-locked host memory and copies that do not wait (no counterpart in the
  * reference, whose ioutils.cu:3-45 stages files through pageable memory): the host
  * buffer must stay untouched until zkb_sync on the same stream. */

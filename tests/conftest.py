@@ -35,3 +35,23 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def zkb():
     return load_package()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With ZKLLM_GUARD=1 the library puts guard bands around every block it hands out (tests/test_gpu_guard.py); a
+    session run that way fails if any band was written."""
+    import ctypes
+    import os
+    z = sys.modules.get("zkllm_ccs2024_b200")
+    if os.environ.get("ZKLLM_GUARD") != "1" or z is None:
+        return
+    blocks, damaged, first = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    side = ctypes.c_int()
+    try:
+        z.call("zkb_guard_report", ctypes.byref(blocks), ctypes.byref(damaged), ctypes.byref(first), ctypes.byref(side), ctypes.c_int(0))
+    except Exception:          # no device in this session
+        return
+    print(f"\n[guard] {blocks.value} blocks checked, {damaged.value} with a written guard band")
+    if damaged.value:
+        print(f"[guard] first: a block of {first.value} bytes, written {'before' if side.value == 0 else 'after'} it")
+        session.exitstatus = 1

@@ -154,8 +154,68 @@ struct AllocClock {
     }
 };
 
+// ---- guard bands (debug aid; stands in for a memory checker) ---------------------------
+// With ZKLLM_GUARD=1 in the environment, or after zkb_guard_enable(1), every block the library hands out - the
+// scratch blocks of all entry points and the buffers of zkb_malloc - is allocated with 256 bytes before and after it
+// that hold a fixed pattern.  When the block is released a small kernel compares the bands with the pattern, in the
+// stream's order, and counts a block whose band was written: a kernel that stores outside its buffer by up to 64
+// words is caught wherever the buffer came from the library.  zkb_guard_report returns the counts.  Reads outside
+// a buffer are not seen (the bands are valid memory); wrong results from them are what the parity tests catch.
+constexpr size_t kGuardBytes = 256;
+constexpr uint32_t kGuardWord = 0xA5C3F00Du;
+struct GuardStats { unsigned long long blocks, damaged, first_bytes; unsigned first_side, pad; };
+__device__ GuardStats g_guard_stats;
+static std::atomic<int> g_guard_on{-1};          // -1: not decided yet (environment), 0 / 1
+
+static bool guard_on() {
+    int v = g_guard_on.load();
+    if (v < 0) {
+        const char* e = std::getenv("ZKLLM_GUARD");
+        v = (e && e[0] == '1') ? 1 : 0;
+        g_guard_on.store(v);
+    }
+    return v == 1;
+}
+static size_t guard_round(size_t bytes) { return (bytes + 3) & ~(size_t)3; }
+
+__global__ void guard_fill_kernel(uint32_t* lo, uint32_t* hi) {
+    lo[threadIdx.x] = kGuardWord;
+    hi[threadIdx.x] = kGuardWord;
+}
+__global__ void guard_check_kernel(const uint32_t* lo, const uint32_t* hi, unsigned long long bytes) {
+    const bool bad_lo = lo[threadIdx.x] != kGuardWord, bad_hi = hi[threadIdx.x] != kGuardWord;
+    const int any = __syncthreads_or(bad_lo || bad_hi);
+    const int any_lo = __syncthreads_or(bad_lo);
+    if (threadIdx.x == 0) {
+        atomicAdd(&g_guard_stats.blocks, 1ull);
+        if (any && atomicAdd(&g_guard_stats.damaged, 1ull) == 0) {
+            g_guard_stats.first_bytes = bytes;
+            g_guard_stats.first_side = any_lo ? 0u : 1u;
+        }
+    }
+}
+// base: what the pool returned for bytes + 2 bands; returns the user pointer
+static void* guard_arm(void* base, size_t bytes, cudaStream_t s) {
+    char* b = static_cast<char*>(base);
+    guard_fill_kernel<<<1, kGuardBytes / 4, 0, s>>>(reinterpret_cast<uint32_t*>(b),
+                                                    reinterpret_cast<uint32_t*>(b + kGuardBytes + guard_round(bytes)));
+    return b + kGuardBytes;
+}
+static void guard_verify(void* base, size_t bytes, cudaStream_t s) {
+    char* b = static_cast<char*>(base);
+    guard_check_kernel<<<1, kGuardBytes / 4, 0, s>>>(reinterpret_cast<const uint32_t*>(b),
+                                                     reinterpret_cast<const uint32_t*>(b + kGuardBytes + guard_round(bytes)),
+                                                     (unsigned long long)bytes);
+}
+// buffers of zkb_malloc that carry bands: user pointer -> user bytes
+static std::mutex g_guard_mu;
+static std::map<void*, size_t> g_guarded;
+
 Scratch::~Scratch() {
-    for (int i = 0; i < n_; ++i) cudaFreeAsync(blocks_[i], stream_);
+    for (int i = 0; i < n_; ++i) {
+        if (guarded_[i]) guard_verify(blocks_[i], guarded_[i], stream_);
+        cudaFreeAsync(blocks_[i], stream_);
+    }
 }
 
 void* Scratch::get(size_t bytes) {
@@ -165,14 +225,17 @@ void* Scratch::get(size_t bytes) {
     }
     if (bytes == 0) bytes = 16;
     AllocClock clock(0);
+    const bool guard = guard_on();
     void* p = nullptr;
-    cudaError_t e = pool_alloc(&p, bytes, stream_);
+    cudaError_t e = pool_alloc(&p, guard ? guard_round(bytes) + 2 * kGuardBytes : bytes, stream_);
     if (e != cudaSuccess) {
         cuda_fail(e, "cudaMallocAsync(scratch)");
         return nullptr;
     }
-    blocks_[n_++] = p;
-    return p;
+    blocks_[n_] = p;
+    guarded_[n_] = guard ? bytes : 0;
+    ++n_;
+    return guard ? guard_arm(p, bytes, stream_) : p;
 }
 
 }  // namespace zkb
@@ -233,7 +296,16 @@ int zkb_profile_read(char* buf, size_t cap) {
 int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!d_ptr) return fail(ZKB_ERR_ARG, "zkb_malloc: null out pointer");
     AllocClock clock(1);
-    ZKB_CUDA(pool_alloc(d_ptr, bytes ? bytes : 16, (cudaStream_t)0));
+    if (!bytes) bytes = 16;
+    if (guard_on()) {
+        void* base = nullptr;
+        ZKB_CUDA(pool_alloc(&base, guard_round(bytes) + 2 * kGuardBytes, (cudaStream_t)0));
+        *d_ptr = guard_arm(base, bytes, (cudaStream_t)0);
+        std::lock_guard<std::mutex> lk(g_guard_mu);
+        g_guarded[*d_ptr] = bytes;
+    } else {
+        ZKB_CUDA(pool_alloc(d_ptr, bytes, (cudaStream_t)0));
+    }
     ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     return ZKB_OK;
 }
@@ -241,7 +313,38 @@ int zkb_free(void* d_ptr) {
     if (!d_ptr) return ZKB_OK;
     AllocClock clock(2);
     ZKB_CUDA(cudaDeviceSynchronize());
+    size_t guarded = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_guard_mu);
+        auto it = g_guarded.find(d_ptr);
+        if (it != g_guarded.end()) { guarded = it->second; g_guarded.erase(it); }
+    }
+    if (guarded) {
+        void* base = static_cast<char*>(d_ptr) - kGuardBytes;
+        guard_verify(base, guarded, (cudaStream_t)0);
+        ZKB_CUDA(cudaFreeAsync(base, (cudaStream_t)0));
+        return ZKB_OK;
+    }
     ZKB_CUDA(cudaFreeAsync(d_ptr, (cudaStream_t)0));
+    return ZKB_OK;
+}
+int zkb_guard_enable(int on) {
+    g_guard_on.store(on ? 1 : 0);
+    return ZKB_OK;
+}
+int zkb_guard_report(unsigned long long* blocks_checked, unsigned long long* blocks_damaged,
+                     unsigned long long* first_damaged_bytes, int* first_damaged_side, int reset) {
+    ZKB_CUDA(cudaDeviceSynchronize());
+    GuardStats st;
+    ZKB_CUDA(cudaMemcpyFromSymbol(&st, g_guard_stats, sizeof(st)));
+    if (blocks_checked) *blocks_checked = st.blocks;
+    if (blocks_damaged) *blocks_damaged = st.damaged;
+    if (first_damaged_bytes) *first_damaged_bytes = st.first_bytes;
+    if (first_damaged_side) *first_damaged_side = st.damaged ? (int)st.first_side : -1;
+    if (reset) {
+        memset(&st, 0, sizeof(st));
+        ZKB_CUDA(cudaMemcpyToSymbol(g_guard_stats, &st, sizeof(st)));
+    }
     return ZKB_OK;
 }
 int zkb_pool_trim(size_t keep_bytes) {

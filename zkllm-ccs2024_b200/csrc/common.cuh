@@ -84,7 +84,8 @@ public:
 private:
     static constexpr int kMax = 256;
     cudaStream_t stream_;
-    void* blocks_[kMax];
+    void* blocks_[kMax];        // what the pool returned
+    size_t guarded_[kMax];      // user bytes of a block with guard bands, 0 for a plain block
     int n_ = 0;
 };
 
