@@ -515,8 +515,11 @@ static double bucket_cost(size_t m, size_t n, int W) {
 // combination tables of msm_comb.cuh with 3-bit windows - whichever needs fewer field
 // products.  method: ZKB_MSM_AUTO, or one of the two by name.
 static constexpr size_t kCombTableLimit = (size_t)12 << 30;
+// early_table: tables of this generator set that the caller built while the scalars were still being copied
+// (zkb_commit_i32_host), or nullptr.
 static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d_scalars, size_t n_scalars,
-                             G1Jac* d_out, Scratch& scratch, cudaStream_t s, int method = ZKB_MSM_AUTO) {
+                             G1Jac* d_out, Scratch& scratch, cudaStream_t s, int method = ZKB_MSM_AUTO,
+                             const G1Aff* early_table = nullptr) {
     if (n_gen == 0 || n_scalars % n_gen) return fail(ZKB_ERR_DIM, "Commitment::commit_int - Incompatible dimensions");
     if (method != ZKB_MSM_AUTO && method != ZKB_MSM_BUCKETS && method != ZKB_MSM_TABLES)
         return fail(ZKB_ERR_ARG, "commit: unknown method");
@@ -534,6 +537,7 @@ static int commit_i32_device(const G1Jac* d_gens, size_t n_gen, const int32_t* d
     if (method == ZKB_MSM_AUTO)
         tables = comb_table_bytes(n_gen) <= kCombTableLimit && comb_cost(m, n_gen, W3) < bucket_cost(m, n_gen, W7);
     if (!tables) return msm_rows<false>(d_gens, n_gen, d_scalars, m, W7, d_out, scratch, s);
+    if (early_table) return msm_comb_run(early_table, n_gen, d_scalars, m, W3, d_out, scratch, s);
     G1Aff* bases = scratch.get_n<G1Aff>(n_gen);
     if (!bases) return ZKB_ERR_CUDA;
     ZKB_TRY(to_affine_device(d_gens, bases, n_gen, s));
@@ -964,6 +968,31 @@ int zkb_commit_i32_host(const zkb_g1_t* h_gens, size_t n_gen, const int32_t* h_s
     G1Jac* d_out = scratch.get_n<G1Jac>(m);
     if (!d_gens || !d_sc || !d_out) return ZKB_ERR_CUDA;
     ZKB_CUDA(cudaMemcpyAsync(d_gens, h_gens, n_gen * sizeof(G1Jac), cudaMemcpyHostToDevice, s));
+    // The combination tables depend on the generators only.  When the shape makes them the likely choice (decided
+    // for 16-bit scalars; the real choice follows once the scalars are here and their range is known), they are
+    // built on the caller's stream while the scalars cross the bus on the second stream.
+    const G1Aff* early_table = nullptr;
+    SideStream* side = nullptr;
+    const int w3_guess = comb_windows_for_max(1u << 15), w7_guess = windows_for_max(1u << 15);
+    if (m >= 64 && comb_table_bytes(n_gen) <= kCombTableLimit && comb_cost(m, n_gen, w3_guess) < bucket_cost(m, n_gen, w7_guess))
+        side = side_stream();
+    if (side) {
+        std::lock_guard<std::mutex> turn(side->busy);
+        Drain drain{side->st};
+        ZKB_CUDA(cudaEventRecord(side->fork, s));                 // d_sc exists from here on in s's order
+        ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
+        ZKB_CUDA(cudaMemcpyAsync(d_sc, h_scalars, n_scalars * sizeof(int32_t), cudaMemcpyHostToDevice, side->st));
+        ZKB_CUDA(cudaEventRecord(side->join, side->st));
+        G1Aff* bases = scratch.get_n<G1Aff>(n_gen);
+        if (!bases) return ZKB_ERR_CUDA;
+        ZKB_TRY(to_affine_device(d_gens, bases, n_gen, s));
+        ZKB_TRY(comb_tables_build(bases, n_gen, &early_table, scratch, s));
+        ZKB_CUDA(cudaStreamWaitEvent(s, side->join, 0));
+        ZKB_TRY(commit_i32_device(d_gens, n_gen, d_sc, n_scalars, d_out, scratch, s, ZKB_MSM_AUTO, early_table));
+        ZKB_CUDA(cudaMemcpyAsync(h_out, d_out, m * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+        ZKB_CUDA(cudaStreamSynchronize(s));
+        return ZKB_OK;
+    }
     ZKB_CUDA(cudaMemcpyAsync(d_sc, h_scalars, n_scalars * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     ZKB_TRY(commit_i32_device(d_gens, n_gen, d_sc, n_scalars, d_out, scratch, s));
     ZKB_CUDA(cudaMemcpyAsync(h_out, d_out, m * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));

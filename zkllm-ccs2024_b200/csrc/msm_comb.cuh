@@ -301,10 +301,25 @@ static unsigned comb_segments(size_t m, size_t n_quads, int W) {
     return best;
 }
 
-// All rows through combination tables.  bases: n affine generators; scalars: int32 [m][n] with
-// |s| within the range of W windows (comb_windows_for_max).
-static int msm_comb_rows(const G1Aff* bases, size_t n, const int32_t* d_scalars, size_t m, int W,
-                         G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+// The tables of one generator set: entry (q, i) = the combination of generators 4q..4q+3 with the four digits of i.
+// They depend on the generators only, so a caller whose scalars are still on their way to the device can build them first.
+static int comb_tables_build(const G1Aff* bases, size_t n, const G1Aff** table_out, Scratch& scratch, cudaStream_t s) {
+    const size_t n_quads = (n + 3) / 4, n_pad = n_quads * 4, n_pairs = n_quads * 2;
+    G1Aff* singles = scratch.get_n<G1Aff>(n_pad * 8);
+    G1Aff* pairs = scratch.get_n<G1Aff>(n_pairs * 64);
+    G1Aff* table = scratch.get_n<G1Aff>(n_quads * (size_t)kCombEntries);
+    if (!singles || !pairs || !table) return ZKB_ERR_CUDA;
+    ZKB_LAUNCH(comb_singles_kernel, div_up(n_pad, 128), 128, 0, s, bases, n, n_pad, singles);
+    ZKB_LAUNCH(comb_pairs_kernel, div_up(n_pairs * 8, 128), 128, 0, s, singles, n_pairs, pairs);
+    ZKB_LAUNCH(comb_quads_kernel, div_up(n_quads * 64, 128), 128, 0, s, pairs, n_quads, table);
+    *table_out = table;
+    return ZKB_OK;
+}
+
+// All rows through the tables of comb_tables_build.  scalars: int32 [m][n] with |s| within the range of W windows
+// (comb_windows_for_max).
+static int msm_comb_run(const G1Aff* table, size_t n, const int32_t* d_scalars, size_t m, int W,
+                        G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
     if (m == 0) return ZKB_OK;
     CombShape sh;
     sh.m = m; sh.n = n; sh.W = W;
@@ -312,22 +327,23 @@ static int msm_comb_rows(const G1Aff* bases, size_t n, const int32_t* d_scalars,
     sh.nseg = comb_segments(m, sh.n_quads, W);
     sh.qps = (unsigned)((sh.n_quads + sh.nseg - 1) / sh.nseg);
     sh.nseg = (unsigned)((sh.n_quads + sh.qps - 1) / sh.qps);
-    const size_t n_pad = sh.n_quads * 4, n_pairs = sh.n_quads * 2;
-    G1Aff* singles = scratch.get_n<G1Aff>(n_pad * 8);
-    G1Aff* pairs = scratch.get_n<G1Aff>(n_pairs * 64);
-    G1Aff* table = scratch.get_n<G1Aff>(sh.n_quads * (size_t)kCombEntries);
     const size_t n_chains = (size_t)W * sh.nseg * m;
     G1Jac* part = scratch.get_n<G1Jac>(n_chains);
     G1Jac* win = scratch.get_n<G1Jac>((size_t)W * m);
-    if (!singles || !pairs || !table || !part || !win) return ZKB_ERR_CUDA;
+    if (!part || !win) return ZKB_ERR_CUDA;
     if ((n_chains + 127) / 128 > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: problem too large for one launch");
-    ZKB_LAUNCH(comb_singles_kernel, div_up(n_pad, 128), 128, 0, s, bases, n, n_pad, singles);
-    ZKB_LAUNCH(comb_pairs_kernel, div_up(n_pairs * 8, 128), 128, 0, s, singles, n_pairs, pairs);
-    ZKB_LAUNCH(comb_quads_kernel, div_up(sh.n_quads * 64, 128), 128, 0, s, pairs, sh.n_quads, table);
     ZKB_LAUNCH(msm_comb_kernel, div_up(n_chains, 128), 128, 0, s, table, d_scalars, sh, part);
     ZKB_LAUNCH(msm_comb_window_kernel, div_up(m * (size_t)W, 128), 128, 0, s, part, sh, win);
     ZKB_LAUNCH(msm_comb_sum_kernel, div_up(m, 128), 128, 0, s, win, sh, d_out);
     return ZKB_OK;
+}
+
+static int msm_comb_rows(const G1Aff* bases, size_t n, const int32_t* d_scalars, size_t m, int W,
+                         G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+    if (m == 0) return ZKB_OK;
+    const G1Aff* table = nullptr;
+    ZKB_TRY(comb_tables_build(bases, n, &table, scratch, s));
+    return msm_comb_run(table, n, d_scalars, m, W, d_out, scratch, s);
 }
 
 }  // namespace zkb
