@@ -34,6 +34,7 @@ static constexpr int kWinBits = 7;
 static constexpr int kBuckets = 64;           // |digit| in 1..64
 static constexpr unsigned kMaxSeg = 16384;    // columns per sorted list (u16 entries: col << 1 | neg)
 static constexpr int kMaxWindows = 37;        // ceil(259 / 7) for full-width scalars
+static constexpr int kGlvWindows = 19;        // ceil(133 / 7): the 128-bit halves of a scalar split by the endomorphism
 
 // ---- digits ------------------------------------------------------------------
 // int32 scalar: magnitude + sign; digit w of (|s| + K), K = 0x40 in every field.
@@ -95,7 +96,20 @@ struct MsmShape {
     size_t m, n;          // rows, generators
     unsigned nseg, seg;   // column segments per row and their length
     int W;                // windows
+    // Full-width scalars fill only a few buckets of the top window (a 256-bit value has 4 bits there, a 128-bit
+    // half 2), so those few lists would be many times longer than all others and one warp would walk them long
+    // after the rest of the grid has finished.  The top window therefore spreads every digit over `top_spread`
+    // buckets by the low bits of the column: bucket (|d| - 1) * top_spread + (column mod top_spread); a small
+    // kernel adds them back into bucket |d| - 1 before the reduction (msm_top_collapse_kernel).  1 = off.
+    unsigned top_spread;
 };
+
+// bucket 1..64 of a non-zero digit d in window w for column c
+ZKB_DEV unsigned bucket_of(const MsmShape& sh, int w, int d, size_t c) {
+    const unsigned a = (unsigned)(d < 0 ? -d : d);
+    if (sh.top_spread > 1 && w == sh.W - 1) return (a - 1) * sh.top_spread + (unsigned)(c & (sh.top_spread - 1)) + 1;
+    return a;
+}
 
 // One CTA per (segment, row, window class z): for each of its windows (z, z + gridDim.z, ...),
 // counting-sort the non-zero digits of the segment by bucket.  ent: u16 lists, offs: 65 offsets per list.
@@ -123,7 +137,7 @@ __global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ 
                 d = digit_of_u64((unsigned long long)a + bias_u64(), w);
                 if (v < 0) d = -d;
             }
-            if (d) atomicAdd(&hist[d < 0 ? -d : d], 1u);
+            if (d) atomicAdd(&hist[bucket_of(sh, w, d, c)], 1u);
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -148,7 +162,7 @@ __global__ void __launch_bounds__(256) msm_sort_kernel(const void* __restrict__ 
                 if (v < 0) d = -d;
             }
             if (d) {
-                const unsigned pos = atomicAdd(&cursor[d < 0 ? -d : d], 1u);
+                const unsigned pos = atomicAdd(&cursor[bucket_of(sh, w, d, c)], 1u);
                 list[pos] = (uint16_t)((c << 1) | (d < 0 ? 1u : 0u));
             }
         }
@@ -225,6 +239,19 @@ __global__ void __launch_bounds__(kAccWarps * 32, ZKB_ACC_MINBLOCKS) msm_accumul
         acc = g1_add_mixed(acc, p);
     }
     g1_store(buckets + list_id * kBuckets + b, acc);
+}
+
+// One CTA of 64 threads per (row, segment) list: the spread buckets of the top window (MsmShape::top_spread)
+// added back into bucket |d| - 1, the others cleared.
+__global__ void __launch_bounds__(64) msm_top_collapse_kernel(G1Jac* __restrict__ buckets, MsmShape sh) {
+    const size_t list_id = (size_t)blockIdx.x * sh.W + (sh.W - 1);
+    G1Jac* b = buckets + list_id * kBuckets;
+    const unsigned F = sh.top_spread, j = threadIdx.x;
+    G1Jac sum = g1_identity();
+    if (j < kBuckets / F)
+        for (unsigned t = 0; t < F; ++t) sum = g1_add(sum, g1_load(b + j * F + t));
+    __syncthreads();
+    g1_store(b + j, sum);
 }
 
 // Thread per (row, window, group of 8 buckets): sums the segment partials of its
@@ -383,7 +410,8 @@ __global__ void __launch_bounds__(32) msm_horner_kernel(const G1Jac* __restrict_
 static int msm_shape(size_t n, size_t m, int W, bool full, size_t nseg_fixed, MsmShape* out) {
     MsmShape sh;
     sh.m = m; sh.n = n; sh.W = W;
-    const size_t want_lists = full ? 96 : 4096;
+    static const size_t exp_lists = [] { const char* e = std::getenv("ZKB_EXP_LISTS"); return e ? (size_t)atoi(e) : (size_t)0; }();
+    const size_t want_lists = full ? (W <= 19 ? (exp_lists ? exp_lists : 192) : 96) : 4096;
     size_t nseg = (want_lists + m - 1) / m;
     const size_t min_seg_len = full ? 64 : 256;
     if (nseg > (n + min_seg_len - 1) / min_seg_len) nseg = (n + min_seg_len - 1) / min_seg_len;
@@ -398,6 +426,8 @@ static int msm_shape(size_t n, size_t m, int W, bool full, size_t nseg_fixed, Ms
     if (m * nseg > 0xffffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
     sh.nseg = (unsigned)nseg;
     sh.seg = (unsigned)((n + nseg - 1) / nseg);
+    // the top digit of a 256-bit scalar in 37 windows is at most 16, of a 128-bit half in 19 windows at most 4
+    sh.top_spread = !full ? 1u : (W == kMaxWindows ? 4u : (W == kGlvWindows ? 16u : 1u));
     *out = sh;
     return ZKB_OK;
 }
@@ -440,9 +470,13 @@ static int msm_accumulate_phase(const G1Aff* bases, const void* d_scalars, const
 
 // Phase 2: bucket sums -> one point per row.  Only m, nseg and W of the shape are used,
 // so the buckets of several phase-1 calls with equal nseg and W reduce together.
-static int msm_reduce_phase(const G1Jac* buckets, const MsmShape& sh, G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
+static int msm_reduce_phase(G1Jac* buckets, const MsmShape& sh, G1Jac* d_out, Scratch& scratch, cudaStream_t s) {
     const size_t m = sh.m;
     const int W = sh.W;
+    if (sh.top_spread > 1) {
+        if (m * sh.nseg > 0x7fffffffull) return fail(ZKB_ERR_LIMIT, "commit: too many (row, segment) lists");
+        ZKB_LAUNCH(msm_top_collapse_kernel, (unsigned)(m * sh.nseg), 64, 0, s, buckets, sh);
+    }
     G1Jac* Lg = scratch.get_n<G1Jac>(m * W * 8);
     G1Jac* Gg = scratch.get_n<G1Jac>(m * W * 8);
     if (!Lg || !Gg) return ZKB_ERR_CUDA;
@@ -490,6 +524,99 @@ static int msm_rows(const G1Jac* d_gens, size_t n, const void* d_scalars, size_t
     if (!bases) return ZKB_ERR_CUDA;
     ZKB_TRY(to_affine_device(d_gens, bases, n, s));
     return msm_rows_affine<FULL>(bases, n, d_scalars, m, W, d_out, scratch, s);
+}
+
+// ---- full-width scalars over points of order r, through the endomorphism -------------------
+// phi(x, y) = (beta x, y) = [lambda] (x, y) on the order-r group, lambda = z^2 - 1 (128 bits).  A scalar k (raw
+// 256-bit limbs, any value) is reduced modulo r and written k = k1 + k2 lambda with k1 < lambda, k2 < 2^128, and
+// k P = k1 P + k2 phi(P): an MSM over n points with 255-bit scalars becomes one over 2n points with 128-bit
+// scalars.  The bucket additions stay the same (2 x 19 windows for 37), but the per-window sums, their
+// reduction and the doublings of the final Horner pass (the longest dependent chain of a small MSM) halve.
+// Only zkb_me_open's fast path uses it, after its generators passed the order check.
+
+ZKB_DEV void glv_split(const Fr& raw, Fr& k1, Fr& k2) {
+    typedef unsigned __int128 u128;
+    const u128 lambda = ((u128)0xac45a4010001a402ull << 64) | 0x00000000ffffffffull;
+    const uint64_t rmod[4] = {0xffffffff00000001ull, 0x53bda402fffe5bfeull, 0x3339d80809a1d805ull, 0x73eda753299d7d48ull};
+    uint64_t limb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) limb[i] = ((uint64_t)raw.v[2 * i + 1] << 32) | raw.v[2 * i];
+    k1 = fr_zero();
+    k2 = fr_zero();
+    if ((limb[0] | limb[1] | limb[2] | limb[3]) == 0) return;
+    for (int pass = 0; pass < 2; ++pass) {          // 2^256 < 3 r
+        bool ge = true;
+        for (int i = 3; i >= 0; --i)
+            if (limb[i] != rmod[i]) { ge = limb[i] > rmod[i]; break; }
+        if (!ge) break;
+        uint64_t borrow = 0;
+        for (int i = 0; i < 4; ++i) {
+            const u128 d = (u128)limb[i] - rmod[i] - borrow;
+            limb[i] = (uint64_t)d;
+            borrow = (uint64_t)(d >> 64) ? 1 : 0;
+        }
+    }
+    u128 rem = 0, quo = 0;                           // schoolbook division by lambda, one bit at a time
+#pragma unroll 1
+    for (int bit = 255; bit >= 0; --bit) {
+        const bool top = (bool)(rem >> 127);
+        rem = (rem << 1) | ((limb[bit >> 6] >> (bit & 63)) & 1u);
+        quo <<= 1;
+        if (top || rem >= lambda) { rem -= lambda; quo |= 1; }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        k1.v[i] = (uint32_t)(rem >> (32 * i));
+        k2.v[i] = (uint32_t)(quo >> (32 * i));
+    }
+}
+
+__global__ void __launch_bounds__(256) glv_rows_kernel(const Fr* __restrict__ rows, size_t total, Fr* __restrict__ out) {
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        Fr k1, k2;
+        glv_split(fr_load(rows + e), k1, k2);
+        fr_store(out + 2 * e, k1);
+        fr_store(out + 2 * e + 1, k2);
+    }
+}
+
+// beta: the cube root of unity in Fq that goes with lambda (Montgomery form)
+ZKB_DEV Fq fq_beta_mont() {
+    constexpr uint32_t t[12] = {0x8671f071u, 0xcd03c9e4u, 0x1fcda5d2u, 0x5dab2246u, 0xd3851b95u, 0x587042afu,
+                                0x01bacb9eu, 0x8eb60ebeu, 0x83d050d2u, 0x03f97d6eu, 0x54638741u, 0x18f02065u};
+    Fq r;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) r.v[i] = t[i];
+    return r;
+}
+__global__ void __launch_bounds__(256) glv_bases_kernel(const G1Aff* __restrict__ bases, size_t n, G1Aff* __restrict__ out) {
+    const Fq beta = fq_beta_mont();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        G1Aff p = g1_aff_load(bases + i);
+        g1_aff_store(out + 2 * i, p);
+        p.x = fq_mul(p.x, beta);                     // the affine identity (0, 0) stays what it is
+        g1_aff_store(out + 2 * i + 1, p);
+    }
+}
+
+// bases2: 2n points, rows2: m x 2n scalars for msm_*<true> with kGlvWindows windows
+static int glv_expand(const G1Aff* bases, size_t n, const Fr* d_rows, size_t m, G1Aff** bases2, Fr** rows2,
+                      Scratch& scratch, cudaStream_t s) {
+    *bases2 = scratch.get_n<G1Aff>(2 * n);
+    *rows2 = scratch.get_n<Fr>(2 * m * n);
+    if (!*bases2 || !*rows2) return ZKB_ERR_CUDA;
+    ZKB_LAUNCH(glv_bases_kernel, grid_for(n, 256), 256, 0, s, bases, n, *bases2);
+    ZKB_LAUNCH(glv_rows_kernel, grid_for(m * n, 256), 256, 0, s, d_rows, m * n, *rows2);
+    return ZKB_OK;
+}
+
+static int msm_rows_affine_glv(const G1Aff* bases, size_t n, const Fr* d_rows, size_t m, G1Jac* d_out, Scratch& scratch,
+                               cudaStream_t s) {
+    if (m == 0) return ZKB_OK;
+    G1Aff* b2 = nullptr;
+    Fr* r2 = nullptr;
+    ZKB_TRY(glv_expand(bases, n, d_rows, m, &b2, &r2, scratch, s));
+    return msm_rows_affine<true>(b2, 2 * n, r2, m, kGlvWindows, d_out, scratch, s);
 }
 
 // Smallest W such that |s| + K stays below 128^W for every |s| <= max_abs, where
@@ -587,44 +714,35 @@ ZKB_DEV G1Jac g1_from_aff(const G1Aff& a) {
 
 // u * P for the one scalar u all pairs of a round share, through the curve's
 // endomorphism phi(x, y) = (beta x, y) = lambda (x, y) on the order-r group:
-// u = k1 + k2 lambda with 128-bit halves (host: fold_digits), and
-// k1 P + k2 phi(P) by one pass of 33 signed 4-bit windows over both halves with
-// a table of 1P..8P.  128 doublings and 66 additions instead of 255 and ~128.
-struct FoldDigits { signed char d1[33], d2[33]; };
-
-ZKB_DEV Fq fq_beta_mont() {
-    constexpr uint32_t t[12] = {0x8671f071u, 0xcd03c9e4u, 0x1fcda5d2u, 0x5dab2246u, 0xd3851b95u, 0x587042afu,
-                                0x01bacb9eu, 0x8eb60ebeu, 0x83d050d2u, 0x03f97d6eu, 0x54638741u, 0x18f02065u};
-    Fq r;
-#pragma unroll
-    for (int i = 0; i < 12; ++i) r.v[i] = t[i];
-    return r;
-}
+// u = k1 + k2 lambda with 128-bit halves (host: fold_digits), both halves in width-5
+// non-adjacent form (odd digits -15..15, on average one non-zero digit in six), and
+// k1 P + k2 phi(P) by one pass over the bits of both halves with a table of P, 3P, .. 15P:
+// 130 doublings and about 43 additions instead of 255 and ~128.  The digits are the same
+// for every thread, so the pass does not diverge.
+struct FoldDigits { signed char d1[130], d2[130]; };
 
 __device__ __noinline__ static G1Jac g1_add_call(const G1Jac& p, const G1Jac& q) { return g1_add(p, q); }
 __device__ __noinline__ static G1Jac g1_double_call(const G1Jac& p) { return g1_double(p); }
 
 __device__ static G1Jac g1_mul_shared_scalar(const G1Jac& p, const FoldDigits& dg) {
-    G1Jac tab[8];
+    G1Jac tab[8];                                   // (2j + 1) P
     tab[0] = p;
+    const G1Jac p2 = g1_double_call(p);
 #pragma unroll 1
-    for (int i = 1; i < 8; ++i) tab[i] = (i & 1) ? g1_double_call(tab[i >> 1]) : g1_add_call(tab[i - 1], p);
+    for (int j = 1; j < 8; ++j) tab[j] = g1_add_call(tab[j - 1], p2);
     const Fq beta = fq_beta_mont();
     G1Jac acc = g1_identity();
 #pragma unroll 1
-    for (int w = 32; w >= 0; --w) {
-        if (w != 32) {
-#pragma unroll 1
-            for (int d = 0; d < 4; ++d) acc = g1_double_call(acc);
-        }
-        const int a = dg.d1[w], b = dg.d2[w];
+    for (int i = 129; i >= 0; --i) {
+        acc = g1_double_call(acc);
+        const int a = dg.d1[i], b = dg.d2[i];
         if (a) {
-            G1Jac t = tab[(a < 0 ? -a : a) - 1];
+            G1Jac t = tab[((a < 0 ? -a : a) - 1) >> 1];
             if (a < 0) t = g1_neg(t);
             acc = g1_add_call(acc, t);
         }
         if (b) {
-            G1Jac t = tab[(b < 0 ? -b : b) - 1];
+            G1Jac t = tab[((b < 0 ? -b : b) - 1) >> 1];
             t.x = fq_mul(t.x, beta);
             if (b < 0) t = g1_neg(t);
             acc = g1_add_call(acc, t);
@@ -647,7 +765,7 @@ __global__ void __launch_bounds__(128) me_open_fold_kernel(const G1Aff* __restri
     }
 }
 
-// Host: u (standard form, below r) = k1 + k2 * lambda, then signed 4-bit digits of both halves.
+// Host: u (standard form, below r) = k1 + k2 * lambda, then the width-5 non-adjacent form of both halves.
 static FoldDigits fold_digits(const zkb_fr_t& u) {
     typedef unsigned __int128 u128;
     const u128 lambda = ((u128)0xac45a4010001a402ull << 64) | 0x00000000ffffffffull;
@@ -680,13 +798,15 @@ static FoldDigits fold_digits(const zkb_fr_t& u) {
     for (int h = 0; h < 2; ++h) {
         signed char* d = h ? out.d2 : out.d1;
         u128 v = k[h];
-        int carry = 0;
-        for (int w = 0; w < 33; ++w) {
-            int x = (int)(v & 15u) + carry;
-            v >>= 4;
-            carry = 0;
-            if (x >= 8) { x -= 16; carry = 1; }
-            d[w] = (signed char)x;
+        for (int i = 0; i < 130; ++i) {              // width-5 non-adjacent form, least significant digit first
+            int x = 0;
+            if (v & 1u) {
+                x = (int)(v & 31u);
+                if (x >= 16) { x -= 32; v += (u128)(-x); }   // v < 2^128 - 31 here: lambda and the quotient are below 2^128 - 2^125
+                else v -= (u128)x;
+            }
+            d[i] = (signed char)x;
+            v >>= 1;
         }
     }
     return out;
@@ -1045,6 +1165,8 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // (the Horner chain over 37 windows is latency-bound: once, not once per round).
     bool order_r = true;
     ZKB_TRY(generators_have_order_r(reinterpret_cast<const G1Jac*>(d_gens), n, &order_r, keep, s));
+    static const bool exp_glv = [] { const char* e = std::getenv("ZKB_EXP_GLV"); return !(e && e[0] == '0'); }();
+    static const bool exp_serial = [] { const char* e = std::getenv("ZKB_EXP_SERIAL"); return e && e[0] == '1'; }();
     unsigned n_big = 0;
     for (size_t c = n; n_big < k && (c > kTailLen || !order_r); c = (c + 1) / 2) ++n_big;
     // Only the first big round forms T = sum s_i g_i by an MSM.  With a = u (1 - u), b = (1 - u)^2, c = u^2 of a
@@ -1058,7 +1180,8 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     size_t per_row = 0;
     const size_t big_rows = !n_big ? 0 : (order_r ? 3 + 2 * (size_t)(n_big - 1) : 3 * (size_t)n_big);
     if (n_big) {
-        ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
+        if (order_r && exp_glv) ZKB_TRY(msm_shape(2 * n, 3, kGlvWindows, true, 0, &big0));
+        else ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
         per_row = msm_bucket_count(big0) / 3;
         big_buckets = keep.get_n<G1Jac>(per_row * big_rows);
         big_points = keep.get_n<G1Jac>(big_rows);
@@ -1077,12 +1200,22 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         ZKB_TRY(to_affine_device(cg, bases_r, cur, s));
         ZKB_CUDA(cudaEventRecord(side->fork, s));
         ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
+        if (exp_serial) cudaStreamSynchronize(s);
         {
             Scratch round(side->st);   // sorted lists of this round, released in the side stream's order
             MsmShape sh;
-            rc = msm_shape(cur, n_rows, kMaxWindows, true, big0.nseg, &sh);
-            if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_row * rows_done, round, side->st);
+            if (order_r && exp_glv) {
+                G1Aff* b2 = nullptr;
+                Fr* r2 = nullptr;
+                rc = glv_expand(bases_r, cur, rows_r, n_rows, &b2, &r2, round, side->st);
+                if (rc == ZKB_OK) rc = msm_shape(2 * cur, n_rows, kGlvWindows, true, big0.nseg, &sh);
+                if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(b2, r2, sh, big_buckets + per_row * rows_done, round, side->st);
+            } else {
+                rc = msm_shape(cur, n_rows, kMaxWindows, true, big0.nseg, &sh);
+                if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_row * rows_done, round, side->st);
+            }
         }
+        if (exp_serial) cudaStreamSynchronize(side->st);
         if (order_r) {
             ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
         } else {
@@ -1134,7 +1267,11 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
             G1Jac* d_der = fin.get_n<G1Jac>(n_der);
             if (!d_coef || !d_der) return ZKB_ERR_CUDA;
             ZKB_CUDA(cudaMemcpyAsync(d_coef, coef.data(), coef.size() * sizeof(Fr), cudaMemcpyHostToDevice, side->st));
-            rc = msm_rows<true>(big_points, n_pts, d_coef, n_der, kMaxWindows, d_der, fin, side->st);
+            G1Aff* pts_aff = fin.get_n<G1Aff>(n_pts);
+            if (!pts_aff) return ZKB_ERR_CUDA;
+            rc = to_affine_device(big_points, pts_aff, n_pts, side->st);
+            if (rc == ZKB_OK && exp_glv) rc = msm_rows_affine_glv(pts_aff, n_pts, d_coef, n_der, d_der, fin, side->st);
+            else if (rc == ZKB_OK) rc = msm_rows_affine<true>(pts_aff, n_pts, d_coef, n_der, kMaxWindows, d_der, fin, side->st);
             for (unsigned t = 1; t < n_big && rc == ZKB_OK; ++t)
                 ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t, d_der + (t - 1), sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
         }
@@ -1154,7 +1291,8 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         ZKB_LAUNCH(me_open_tail_prep_kernel, 1, 1024, 0, s, cs, cur, d_um, K, S, Wt);
         ZKB_LAUNCH(me_open_tail_rows_kernel, grid_for((3 * (size_t)K + 1) * cur, 128), 128, 0, s, S, Wt, cur, K, tail_rows);
         ZKB_TRY(to_affine_device(cg, bases_t, cur, s));
-        rc = msm_rows_affine<true>(bases_t, cur, tail_rows, 3 * (size_t)K + 1, kMaxWindows, d_proof + 3 * r, keep, s);
+        if (exp_glv) rc = msm_rows_affine_glv(bases_t, cur, tail_rows, 3 * (size_t)K + 1, d_proof + 3 * r, keep, s);
+        else rc = msm_rows_affine<true>(bases_t, cur, tail_rows, 3 * (size_t)K + 1, kMaxWindows, d_proof + 3 * r, keep, s);
         cs = S + (size_t)K * cur;   // the fully folded scalar
     }
     // the caller's stream takes the side stream's work back before anything is read or released
