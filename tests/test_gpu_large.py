@@ -193,6 +193,27 @@ def test_matmul_integer_path_and_its_fallbacks(dev, M, N, P, amax, bmax):
     assert R.fr_unpack(dC.to_host(np.uint32, (M * P, 8))) == exp
 
 
+@pytest.mark.parametrize("M,N,P,amax,bmax", [(300, 1000, 500, (1 << 23) - 1, (1 << 15) - 1), (257, 4100, 131, (1 << 23) - 1, (1 << 15) - 1),
+                                             (129, 16384, 65, (1 << 23) - 1, (1 << 15) - 1), (512, 600, 512, 255, 255),
+                                             (300, 1000, 500, 1 << 23, (1 << 15) - 1)])
+def test_matmul_through_8_bit_limbs_on_the_tensor_cores(dev, M, N, P, amax, bmax):
+    """left operand below 2^23, right operand below 2^15, at least 2^27 products: three and two byte limbs, six 8-bit
+    tensor-core products with 32-bit accumulators, recombined exactly; extreme entries of both signs, ragged edges, the
+    longest inner dimension the accumulators allow; the last case is one past the limb range and takes the int64 kernel"""
+    z = dev.z
+    rng = np.random.Generator(np.random.PCG64(M + N + P))
+    A = rng.integers(-amax, amax + 1, size=(M, N), dtype=np.int64)
+    B = rng.integers(-bmax, bmax + 1, size=(N, P), dtype=np.int64)
+    A[0, :], B[:, 0] = amax, bmax                         # the largest sums of products, both signs
+    A[1, :], B[:, 1] = -amax, bmax
+    A[2, :], B[:, 2] = -amax, -bmax
+    exp = [int(v) % R.R_MOD for v in (A @ B).reshape(-1)]  # exact in int64: |sum| < 2^23 2^15 2^14
+    dC = z.DeviceBuffer(32 * M * P)
+    dev.call("zkb_fr_matmul", z._p(z.fr_buffer(_fr_of_ints(A))), z._p(z.fr_buffer(_fr_of_ints(B))), z._p(dC), z.sz(M), z.sz(N),
+             z.sz(P), z._p(0))
+    assert R.fr_unpack(dC.to_host(np.uint32, (M * P, 8))) == exp
+
+
 def test_matmul_with_general_field_elements_uses_the_field_kernel(dev):
     z = dev.z
     M, N, P = 96, 512, 96

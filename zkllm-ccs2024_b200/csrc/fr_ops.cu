@@ -622,6 +622,141 @@ ZKB_DEV Fr fr_from_split(long long acc_lo, long long acc_hi) {
     return fr_add(r, fr_from_i64(acc_lo));
 }
 
+// ---- exact integer matmul on the tensor cores, through 8-bit limbs -------------------------
+// For a left operand below 2^23 and a right operand below 2^15 in magnitude (activations times weights: the six
+// linear layers of a decoder layer), A = a2 2^16 + a1 2^8 + a0 and B = b1 2^8 + b0 with a0, a1, b0 in [0, 255] and
+// a2, b1 signed bytes, and A B = sum_{i,j} 2^(8(i+j)) a_i b_j: six 8-bit products with 32-bit accumulators
+// (mma.sync m16n8k32, the integer tensor-core instruction; |a_i b_j| <= 255^2 per term, so two products of one weight
+// 2^(8c) share an accumulator for up to 16384 terms).  Exact: the epilogue recombines the four accumulators in 64 bits.
+static constexpr int kI8TileM = 128, kI8TileP = 64, kI8TileK = 64, kI8Pitch = 80;   // pitch: 64 bytes + 16, conflict-free
+static constexpr size_t kI8MaxK = 16384;
+
+// A [M][K] int32 -> three byte planes [M][Kp], zero padded to Kp (a multiple of 64)
+__global__ void i8_split_rows_kernel(const int32_t* __restrict__ a, size_t M, size_t K, size_t Kp, uint8_t* __restrict__ p0,
+                                     uint8_t* __restrict__ p1, int8_t* __restrict__ p2) {
+    const size_t total = M * Kp;
+    for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = t / Kp, k = t % Kp;
+        const int v = k < K ? a[r * K + k] : 0;
+        p0[t] = (uint8_t)(v & 255);
+        p1[t] = (uint8_t)((v >> 8) & 255);
+        p2[t] = (int8_t)(v >> 16);             // arithmetic shift: the signed top limb
+    }
+}
+// B [K][P] int32 -> two byte planes of the transpose [P][Kp]
+__global__ void i8_split_cols_kernel(const int32_t* __restrict__ b, size_t K, size_t P, size_t Kp, uint8_t* __restrict__ p0,
+                                     int8_t* __restrict__ p1) {
+    __shared__ int32_t tile[32][33];
+    const size_t k0 = (size_t)blockIdx.y * 32, c0 = (size_t)blockIdx.x * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const size_t k = k0 + j, c = c0 + threadIdx.x;
+        tile[j][threadIdx.x] = (k < K && c < P) ? b[k * P + c] : 0;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const size_t c = c0 + j, k = k0 + threadIdx.x;
+        if (c < P && k < Kp) {
+            const int v = tile[threadIdx.x][j];
+            p0[c * Kp + k] = (uint8_t)(v & 255);
+            p1[c * Kp + k] = (int8_t)(v >> 8);
+        }
+    }
+}
+
+#define ZKB_IMMA(TA, TB, acc, a, b)                                                                              \
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32." TA "." TB ".s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, " \
+                 "{%0,%1,%2,%3};"                                                                                \
+                 : "+r"(acc[0]), "+r"(acc[1]), "+r"(acc[2]), "+r"(acc[3])                                        \
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]))
+
+// One CTA: a 128 x 64 tile of C; eight warps as 4 x 2, each 32 x 32 = 2 x 4 instruction tiles, four accumulator sets.
+__global__ void __launch_bounds__(256) i8_limb_matmul_kernel(const uint8_t* __restrict__ A0, const uint8_t* __restrict__ A1,
+                                                              const int8_t* __restrict__ A2, const uint8_t* __restrict__ B0,
+                                                              const int8_t* __restrict__ B1, Fr* __restrict__ C, size_t M,
+                                                              size_t Kp, size_t P) {
+    __shared__ __align__(16) uint8_t As[3][kI8TileM][kI8Pitch];
+    __shared__ __align__(16) uint8_t Bs[2][kI8TileP][kI8Pitch];
+    const size_t row0 = (size_t)blockIdx.y * kI8TileM, col0 = (size_t)blockIdx.x * kI8TileP;
+    const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, tig = lane & 3u;
+    const unsigned wm = (warp >> 1) * 32, wp = (warp & 1u) * 32;
+    int acc[4][2][4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[c][i][j][e] = 0;
+    const uint8_t* Ap[3] = {A0, A1, reinterpret_cast<const uint8_t*>(A2)};
+    const uint8_t* Bp[2] = {B0, reinterpret_cast<const uint8_t*>(B1)};
+    for (size_t k0 = 0; k0 < Kp; k0 += kI8TileK) {
+        // global -> shared, 16 bytes per access: 128 rows x 4 vectors per A plane, 64 x 4 per B plane
+        for (unsigned v = threadIdx.x; v < 3 * kI8TileM * 4; v += 256) {
+            const unsigned pl = v / (kI8TileM * 4), r = (v / 4) % kI8TileM, q = v & 3u;
+            uint4 x = make_uint4(0, 0, 0, 0);
+            if (row0 + r < M) x = *reinterpret_cast<const uint4*>(Ap[pl] + (row0 + r) * Kp + k0 + 16 * q);
+            *reinterpret_cast<uint4*>(&As[pl][r][16 * q]) = x;
+        }
+        for (unsigned v = threadIdx.x; v < 2 * kI8TileP * 4; v += 256) {
+            const unsigned pl = v / (kI8TileP * 4), r = (v / 4) % kI8TileP, q = v & 3u;
+            uint4 x = make_uint4(0, 0, 0, 0);
+            if (col0 + r < P) x = *reinterpret_cast<const uint4*>(Bp[pl] + (col0 + r) * Kp + k0 + 16 * q);
+            *reinterpret_cast<uint4*>(&Bs[pl][r][16 * q]) = x;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kI8TileK; kk += 32) {
+            unsigned a[3][2][4], b[2][4][2];
+#pragma unroll
+            for (int pl = 0; pl < 3; ++pl)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const unsigned r = wm + 16 * i + g;
+                    a[pl][i][0] = *reinterpret_cast<const unsigned*>(&As[pl][r][kk + 4 * tig]);
+                    a[pl][i][1] = *reinterpret_cast<const unsigned*>(&As[pl][r + 8][kk + 4 * tig]);
+                    a[pl][i][2] = *reinterpret_cast<const unsigned*>(&As[pl][r][kk + 16 + 4 * tig]);
+                    a[pl][i][3] = *reinterpret_cast<const unsigned*>(&As[pl][r + 8][kk + 16 + 4 * tig]);
+                }
+#pragma unroll
+            for (int pl = 0; pl < 2; ++pl)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned c = wp + 8 * j + g;
+                    b[pl][j][0] = *reinterpret_cast<const unsigned*>(&Bs[pl][c][kk + 4 * tig]);
+                    b[pl][j][1] = *reinterpret_cast<const unsigned*>(&Bs[pl][c][kk + 16 + 4 * tig]);
+                }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ZKB_IMMA("u8", "u8", acc[0][i][j], a[0][i], b[0][j]);   // a0 b0
+                    ZKB_IMMA("u8", "u8", acc[1][i][j], a[1][i], b[0][j]);   // a1 b0
+                    ZKB_IMMA("u8", "s8", acc[1][i][j], a[0][i], b[1][j]);   // a0 b1
+                    ZKB_IMMA("s8", "u8", acc[2][i][j], a[2][i], b[0][j]);   // a2 b0
+                    ZKB_IMMA("u8", "s8", acc[2][i][j], a[1][i], b[1][j]);   // a1 b1
+                    ZKB_IMMA("s8", "s8", acc[3][i][j], a[2][i], b[1][j]);   // a2 b1
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const size_t r = row0 + wm + 16 * i + g + ((e & 2) ? 8 : 0);
+                const size_t c = col0 + wp + 8 * j + 2 * tig + (e & 1);
+                if (r < M && c < P) {
+                    const long long v = (long long)acc[0][i][j][e] + ((long long)acc[1][i][j][e] << 8) +
+                                        ((long long)acc[2][i][j][e] << 16) + ((long long)acc[3][i][j][e] << 24);
+                    fr_store(C + r * P + c, fr_from_i64(v));
+                }
+            }
+}
+#undef ZKB_IMMA
+
 static constexpr int kImTile = 64, kImK = 16;
 template <bool WIDE>
 __global__ void __launch_bounds__(256) i32_matmul_kernel(const int32_t* __restrict__ A, const int32_t* __restrict__ Ahi,
@@ -917,6 +1052,21 @@ int zkb_fr_matmul(const zkb_fr_t* d_a, const zkb_fr_t* d_b, zkb_fr_t* d_c, size_
         const unsigned __int128 limit = (unsigned __int128)1 << 62;
         dim3 gi(div_up(P, kImTile), div_up(M, kImTile));
         if (gi.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^22 rows");
+        if (!h[0] && !h[2] && h[1] < (1u << 23) && h[3] < (1u << 15) && N <= kI8MaxK && M * N * P >= ((size_t)1 << 27)) {
+            // both operands short enough for 8-bit limbs: the tensor-core path
+            const size_t Kp = (N + kI8TileK - 1) / kI8TileK * kI8TileK;
+            uint8_t* pa = scratch.get_n<uint8_t>(3 * M * Kp);
+            uint8_t* pb = scratch.get_n<uint8_t>(2 * P * Kp);
+            if (!pa || !pb) return ZKB_ERR_CUDA;
+            dim3 gt(div_up(P, 32), div_up(Kp, 32)), g8(div_up(P, kI8TileP), div_up(M, kI8TileM));
+            if (gt.y > 65535 || g8.y > 65535) return fail(ZKB_ERR_LIMIT, "matmul: more than 2^22 rows");
+            ZKB_LAUNCH(i8_split_rows_kernel, grid_for(M * Kp, kThreads), kThreads, 0, s, ia, M, N, Kp, pa, pa + M * Kp,
+                       reinterpret_cast<int8_t*>(pa + 2 * M * Kp));
+            ZKB_LAUNCH(i8_split_cols_kernel, gt, dim3(32, 8), 0, s, ib, N, P, Kp, pb, reinterpret_cast<int8_t*>(pb + P * Kp));
+            ZKB_LAUNCH(i8_limb_matmul_kernel, g8, 256, 0, s, pa, pa + M * Kp, reinterpret_cast<const int8_t*>(pa + 2 * M * Kp), pb,
+                       reinterpret_cast<const int8_t*>(pb + P * Kp), FR(d_c), M, Kp, P);
+            return ZKB_OK;
+        }
         if (!h[0] && !h[2] && bound < limit) {
             ZKB_LAUNCH(i32_matmul_kernel<false>, gi, 256, 0, s, ia, nullptr, ib, FR(d_c), M, N, P);
             return ZKB_OK;

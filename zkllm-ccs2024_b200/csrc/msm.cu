@@ -410,8 +410,9 @@ __global__ void __launch_bounds__(32) msm_horner_kernel(const G1Jac* __restrict_
 static int msm_shape(size_t n, size_t m, int W, bool full, size_t nseg_fixed, MsmShape* out) {
     MsmShape sh;
     sh.m = m; sh.n = n; sh.W = W;
-    static const size_t exp_lists = [] { const char* e = std::getenv("ZKB_EXP_LISTS"); return e ? (size_t)atoi(e) : (size_t)0; }();
-    const size_t want_lists = full ? (W <= 19 ? (exp_lists ? exp_lists : 192) : 96) : 4096;
+    // full-width scalars come with few rows: enough (row, segment) lists for about 7000 warps of 32 lists per
+    // (window, bucket) - twice as many segments for the 19 windows of the endomorphism split as for 37
+    const size_t want_lists = full ? (W <= kGlvWindows ? 192 : 96) : 4096;
     size_t nseg = (want_lists + m - 1) / m;
     const size_t min_seg_len = full ? 64 : 256;
     if (nseg > (n + min_seg_len - 1) / min_seg_len) nseg = (n + min_seg_len - 1) / min_seg_len;
@@ -725,6 +726,7 @@ __device__ __noinline__ static G1Jac g1_add_call(const G1Jac& p, const G1Jac& q)
 __device__ __noinline__ static G1Jac g1_double_call(const G1Jac& p) { return g1_double(p); }
 
 __device__ static G1Jac g1_mul_shared_scalar(const G1Jac& p, const FoldDigits& dg) {
+    if (g1_is_identity(p)) return p;
     G1Jac tab[8];                                   // (2j + 1) P
     tab[0] = p;
     const G1Jac p2 = g1_double_call(p);
@@ -751,7 +753,12 @@ __device__ static G1Jac g1_mul_shared_scalar(const G1Jac& p, const FoldDigits& d
     return acc;
 }
 
-__global__ void __launch_bounds__(128) me_open_fold_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size,
+// Measured on 2^19 generators, the fold alone: 2 CTAs per SM (214 registers) 51 ms, 3 CTAs (168) 59 ms, 4 CTAs 64 ms; an
+// affine table with mixed additions and a non-inlined field product changed nothing.
+#ifndef ZKB_FOLD_MINBLOCKS
+#define ZKB_FOLD_MINBLOCKS 2
+#endif
+__global__ void __launch_bounds__(128, ZKB_FOLD_MINBLOCKS) me_open_fold_kernel(const G1Aff* __restrict__ bases, size_t old_size, size_t new_size,
                                                             FoldDigits dg, G1Jac* __restrict__ ngen) {
     for (size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x; g < new_size; g += (size_t)gridDim.x * blockDim.x) {
         const G1Aff a0 = g1_aff_load(bases + 2 * g);
@@ -1165,8 +1172,6 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // (the Horner chain over 37 windows is latency-bound: once, not once per round).
     bool order_r = true;
     ZKB_TRY(generators_have_order_r(reinterpret_cast<const G1Jac*>(d_gens), n, &order_r, keep, s));
-    static const bool exp_glv = [] { const char* e = std::getenv("ZKB_EXP_GLV"); return !(e && e[0] == '0'); }();
-    static const bool exp_serial = [] { const char* e = std::getenv("ZKB_EXP_SERIAL"); return e && e[0] == '1'; }();
     unsigned n_big = 0;
     for (size_t c = n; n_big < k && (c > kTailLen || !order_r); c = (c + 1) / 2) ++n_big;
     // Only the first big round forms T = sum s_i g_i by an MSM.  With a = u (1 - u), b = (1 - u)^2, c = u^2 of a
@@ -1180,7 +1185,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     size_t per_row = 0;
     const size_t big_rows = !n_big ? 0 : (order_r ? 3 + 2 * (size_t)(n_big - 1) : 3 * (size_t)n_big);
     if (n_big) {
-        if (order_r && exp_glv) ZKB_TRY(msm_shape(2 * n, 3, kGlvWindows, true, 0, &big0));
+        if (order_r) ZKB_TRY(msm_shape(2 * n, 3, kGlvWindows, true, 0, &big0));
         else ZKB_TRY(msm_shape(n, 3, kMaxWindows, true, 0, &big0));
         per_row = msm_bucket_count(big0) / 3;
         big_buckets = keep.get_n<G1Jac>(per_row * big_rows);
@@ -1200,11 +1205,10 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         ZKB_TRY(to_affine_device(cg, bases_r, cur, s));
         ZKB_CUDA(cudaEventRecord(side->fork, s));
         ZKB_CUDA(cudaStreamWaitEvent(side->st, side->fork, 0));
-        if (exp_serial) cudaStreamSynchronize(s);
         {
             Scratch round(side->st);   // sorted lists of this round, released in the side stream's order
             MsmShape sh;
-            if (order_r && exp_glv) {
+            if (order_r) {
                 G1Aff* b2 = nullptr;
                 Fr* r2 = nullptr;
                 rc = glv_expand(bases_r, cur, rows_r, n_rows, &b2, &r2, round, side->st);
@@ -1215,7 +1219,6 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
                 if (rc == ZKB_OK) rc = msm_accumulate_phase<true>(bases_r, rows_r, sh, big_buckets + per_row * rows_done, round, side->st);
             }
         }
-        if (exp_serial) cudaStreamSynchronize(side->st);
         if (order_r) {
             ZKB_LAUNCH(me_open_fold_kernel, grid_for(nn, 128), 128, 0, s, bases_r, cur, nn, fold_digits(h_u[r]), gn[r & 1]);
         } else {
@@ -1270,8 +1273,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
             G1Aff* pts_aff = fin.get_n<G1Aff>(n_pts);
             if (!pts_aff) return ZKB_ERR_CUDA;
             rc = to_affine_device(big_points, pts_aff, n_pts, side->st);
-            if (rc == ZKB_OK && exp_glv) rc = msm_rows_affine_glv(pts_aff, n_pts, d_coef, n_der, d_der, fin, side->st);
-            else if (rc == ZKB_OK) rc = msm_rows_affine<true>(pts_aff, n_pts, d_coef, n_der, kMaxWindows, d_der, fin, side->st);
+            if (rc == ZKB_OK) rc = msm_rows_affine_glv(pts_aff, n_pts, d_coef, n_der, d_der, fin, side->st);
             for (unsigned t = 1; t < n_big && rc == ZKB_OK; ++t)
                 ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t, d_der + (t - 1), sizeof(G1Jac), cudaMemcpyDeviceToDevice, side->st));
         }
@@ -1291,8 +1293,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         ZKB_LAUNCH(me_open_tail_prep_kernel, 1, 1024, 0, s, cs, cur, d_um, K, S, Wt);
         ZKB_LAUNCH(me_open_tail_rows_kernel, grid_for((3 * (size_t)K + 1) * cur, 128), 128, 0, s, S, Wt, cur, K, tail_rows);
         ZKB_TRY(to_affine_device(cg, bases_t, cur, s));
-        if (exp_glv) rc = msm_rows_affine_glv(bases_t, cur, tail_rows, 3 * (size_t)K + 1, d_proof + 3 * r, keep, s);
-        else rc = msm_rows_affine<true>(bases_t, cur, tail_rows, 3 * (size_t)K + 1, kMaxWindows, d_proof + 3 * r, keep, s);
+        rc = msm_rows_affine_glv(bases_t, cur, tail_rows, 3 * (size_t)K + 1, d_proof + 3 * r, keep, s);
         cs = S + (size_t)K * cur;   // the fully folded scalar
     }
     // the caller's stream takes the side stream's work back before anything is read or released

