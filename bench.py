@@ -183,6 +183,43 @@ def run_opening(args) -> dict:
             "kernel_us": kernel_times(z, run, 1), "opening": bytes(out[0]).hex(), "data": "synthetic"}
 
 
+def run_matmul(args) -> dict:
+    """--workload matmul: FrTensor::matmul (zkb_fr_matmul) of a seq x embed activation matrix (entries below 2^19) with an
+    embed x hidden weight matrix (round(N(0, 0.02) 2^16)) - the forward pass of a linear layer, exact integers; wall
+    milliseconds, CUDA-event time per kernel, tensor-core throughput of the 8-bit-limb kernel, four entries checked."""
+    from __graft_entry__ import load_package
+    z = load_package()
+    M, N, P = args.seq, args.embed, args.hidden
+    rng = np.random.Generator(np.random.PCG64(0x5EED0000 + 90))
+    A = rng.integers(-(1 << 19), 1 << 19, size=(M, N), dtype=np.int64)
+    B = np.rint(rng.standard_normal((N, P)) * 0.02 * 65536).astype(np.int64)
+    dA, dB = z.fr_buffer(ints_to_fr_limbs(A)), z.fr_buffer(ints_to_fr_limbs(B))
+    dC = z.DeviceBuffer(32 * M * P)
+
+    def run():
+        z.call("zkb_fr_matmul", z._p(dA), z._p(dB), z._p(dC), z.sz(M), z.sz(N), z.sz(P), z._p(0))
+        z.call("zkb_sync", z._p(0))
+
+    for _ in range(max(1, args.warmup)):
+        run()
+    times = []
+    for _ in range(max(1, args.steps)):
+        t0 = time.perf_counter()
+        run()
+        times.append((time.perf_counter() - t0) * 1e3)
+    kern = kernel_times(z, run, 1)
+    got = dC.to_host(np.uint32, (M * P, 8))[:4 * P:P + 1]
+    exp = ints_to_fr_limbs(np.array([A[i] @ B[:, i] for i in range(4)], dtype=np.int64))
+    out = {"metric": "FrTensor::matmul time", "unit": "ms", "value": sorted(times)[len(times) // 2], "higher_is_better": False,
+           "workload": f"{M} x {N} times {N} x {P}, exact integers", "wall_ms": times, "kernel_us": kern,
+           "sample_ok": bool(np.array_equal(got, exp)), "data": "synthetic"}
+    k8 = kern.get("i8_limb_matmul_kernel")
+    if k8:      # six 8-bit products per entry of the integer product
+        out["tensor_core"] = {"int8_tera_ops_per_s": 2 * 6 * M * N * P / (k8["us"] / k8["launches"] * 1e-6) / 1e12,
+                              "note": "six 8-bit limb products (mma.sync m16n8k32) per integer product, 32-bit accumulators"}
+    return out
+
+
 def sumcheck_ours(z, torch, steps: int, hbm_peak: float) -> dict:
     """zkFC::prove body (128x4096 . 4096x4096) and tLookupRange prep + prove (2^23 in 2^16):
     seconds per proof and algorithmic GB/s (bytes each live array is read/written once per round)"""
@@ -1027,9 +1064,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=11008)
-    ap.add_argument("--workload", default="commit", choices=["commit", "layer", "opening"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "layer", "opening", "matmul"],
                     help="commit: the headline MSM benchmark; layer: one decoder layer through the stage drivers; "
-                         "opening: one Commitment::me_open over 2^logn generators with per-kernel times")
+                         "opening: one Commitment::me_open over 2^logn generators with per-kernel times; "
+                         "matmul: the forward pass of a linear layer (seq x embed times embed x hidden)")
     ap.add_argument("--logn", type=int, default=17, help="opening workload: log2 of the number of generators")
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--embed", type=int, default=4096)
@@ -1056,6 +1094,9 @@ def main():
         return
     if args.workload == "opening":
         print(json.dumps(run_opening(args)))
+        return
+    if args.workload == "matmul":
+        print(json.dumps(run_matmul(args)))
         return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:
