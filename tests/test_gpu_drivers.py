@@ -141,6 +141,12 @@ def test_batch_mode_runs_stages_in_one_process(tmp_path):
     assert res.returncode == 0, res.stderr[-2000:]
     assert res.stderr.count("[batch] skip-connection") == 2
     assert np.array_equal(np.fromfile(tmp_path / "w.bin", dtype=np.int32).astype(np.int64), (x + 2 * y).reshape(-1))
+    # the output files come from a writer thread by default; written in place they are the same
+    first = (tmp_path / "z.bin").read_bytes(), (tmp_path / "w.bin").read_bytes()
+    res = subprocess.run([str(BIN / "zkllm-driver"), "batch", str(script)], cwd=tmp_path, env=dict(env, ZKLLM_DEFERRED_SAVES="0"),
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert ((tmp_path / "z.bin").read_bytes(), (tmp_path / "w.bin").read_bytes()) == first
     # from standard input, and an unknown stage fails loudly
     res = subprocess.run([str(BIN / "zkllm-driver"), "batch", "-"], cwd=tmp_path, env=env, capture_output=True, text=True,
                          input="skip-connection x.bin y.bin z2.bin\nno-such-stage a b\n", timeout=600)

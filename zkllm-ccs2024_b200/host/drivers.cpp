@@ -158,8 +158,8 @@ int run_rmsnorm(const Args& a) {
     auto g_rms_ = rs_gain(g_rms);
     auto Y = g_rms_ * X;
     auto Y_ = rs_out(Y);
-    proof(cost_lookup(Y.size), [&] { rs_out.prove(Y, Y_); });
     Y_.save_int(a.at(6));
+    proof(cost_lookup(Y.size), [&] { rs_out.prove(Y, Y_); });
     proof(cost_sumcheck(Y.size),
           [&] { hadamard_product_sumcheck(g_rms_, X, random_vec(ceilLog2(Y.size)), random_vec(ceilLog2(Y.size))); });
     proof(cost_lookup(g_rms.size), [&] { rs_gain.prove(g_rms, g_rms_); });
@@ -182,14 +182,14 @@ int run_self_attn(const Args& a) {
             raw.push_back(layers.back()->fc(input));
             scaled.push_back(layers.back()->rs(raw.back()));
         }
+        scaled[0].save_int("temp_Q.bin");
+        scaled[1].save_int("temp_K.bin");
+        scaled[2].save_int("temp_V.bin");
         for (int i = 0; i < 3; ++i) proof(cost_lookup(raw[i].size), [&] { layers[i]->rs.prove(raw[i], scaled[i]); });
         // the reference opens k first, then q, then v
         for (int i : {1, 0, 2})
             proof(cost_weight_claim((size_t)embed * embed),
                   [&] { verifyWeightClaim(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]); });
-        scaled[0].save_int("temp_Q.bin");
-        scaled[1].save_int("temp_K.bin");
-        scaled[2].save_int("temp_V.bin");
         for (auto* l : layers) delete l;
         cout << "QKV linear proof successfully verified!" << endl;
         return 0;
@@ -326,6 +326,9 @@ int run_batch(const Args& a) {
     // (every file is still written); ZKLLM_RESIDENT=0 reads every file from disk again, as separate processes do
     const char* res_env = std::getenv("ZKLLM_RESIDENT");
     zkllm::set_resident_files(!(res_env && res_env[0] == '0'));
+    // output files go to the disk from a writer thread while the stage proves; each is complete before its line is answered
+    const char* def_env = std::getenv("ZKLLM_DEFERRED_SAVES");
+    zkllm::set_deferred_saves(!(def_env && def_env[0] == '0'));
     zkllm::ResidentStats before = zkllm::resident_stats();
     std::string line;
     while (std::getline(in, line)) {
@@ -345,6 +348,7 @@ int run_batch(const Args& a) {
         if (profile) zkb_profile_reset();
         const auto t0 = std::chrono::steady_clock::now();
         const int rc = stage_table().at(stage).first(cmd);
+        zkllm::flush_saves();
         const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         const zkllm::ResidentStats now = zkllm::resident_stats();
         cerr << "[files] " << stage << " loads from disk " << now.loads_from_disk - before.loads_from_disk << " ("

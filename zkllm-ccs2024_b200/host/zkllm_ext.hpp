@@ -40,6 +40,14 @@ struct ResidentStats {
 void set_resident_files(bool on, size_t limit_bytes = 0);
 ResidentStats resident_stats();
 
+// Deferred writes: with `on`, savebin (and so every save / save_int / save_long) copies the tensor to a page-locked
+// host buffer and returns; a writer thread puts it on disk.  flush_saves() returns when every such file is complete
+// and throws if a write failed; loading a file that is still being written waits for it.  Off by default, like the
+// reference, whose savebin returns with the file written.  `zkllm-driver batch` turns it on and flushes before it
+// answers a line.
+void set_deferred_saves(bool on);
+void flush_saves();
+
 // Throws std::runtime_error(msg) when a C-ABI call failed; dimension and
 // verifier failures carry the reference's message text.
 void check(int rc);
