@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(kAccWarps * 32, ZKB_ACC_MINBLOCKS) msm_accumul
     const unsigned beg = o[b], end = o[b + 1];
     const uint16_t* e = ent + list_id * (size_t)sh.seg;
     const size_t col0 = (rs % sh.nseg) * (size_t)sh.seg;
+#ifdef ZKB_ACC_JACOBIAN
     G1Jac acc = g1_identity();
     for (unsigned i = beg; i < end; ++i) {
         const unsigned code = e[i];
@@ -239,6 +240,16 @@ __global__ void __launch_bounds__(kAccWarps * 32, ZKB_ACC_MINBLOCKS) msm_accumul
         acc = g1_add_mixed(acc, p);
     }
     g1_store(buckets + list_id * kBuckets + b, acc);
+#else
+    G1Xyzz acc = xyzz_identity();                 // 10 products per mixed addition (11 in Jacobian coordinates)
+    for (unsigned i = beg; i < end; ++i) {
+        const unsigned code = e[i];
+        G1Aff p = g1_aff_load(bases + col0 + (code >> 1));
+        if (code & 1u) p = g1_aff_neg(p);
+        acc = xyzz_add_mixed(acc, p);
+    }
+    g1_store(buckets + list_id * kBuckets + b, xyzz_to_jac(acc));
+#endif
 }
 
 // One CTA of 64 threads per (row, segment) list: the spread buckets of the top window (MsmShape::top_spread)
