@@ -70,6 +70,9 @@ int zkb_bench_imad(int mode, unsigned iters, double* h_gops, void* stream);
  *      fr-tensor.cu:158-179, g1-tensor.cu:40-60,123-152) ------------------------- */
 int zkb_malloc(void** d_ptr, size_t bytes);   /* usable at once on any stream */
 int zkb_free(void* d_ptr);                     /* waits for the device first, like cudaFree */
+/* zkb_free for a buffer that only the default stream (and the library's calls on it) has used: waits for the
+ * default stream instead of the whole device, so openings in flight (zkb_me_open_begin) keep running. */
+int zkb_free_default_stream(void* d_ptr);
 /* Device memory of this library (zkb_malloc and the scratch memory of every call) comes from a
  * stream-ordered pool the library owns, which keeps freed blocks for reuse (no counterpart in the reference,
  * which calls cudaMalloc / cudaFree per tensor, fr-tensor.cu:158-179).  zkb_pool_trim waits for the device and
@@ -363,6 +366,16 @@ int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, 
  * this vector and drops it); *h_out is the opening. */
 int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
                 zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream);
+/* The same opening in two halves (no counterpart in the reference, whose me_open returns when it is done;
+ * commitment.cu:111-125 is what both halves compute).  zkb_me_open_begin orders the opening after the work already
+ * queued on `stream`, queues it on streams of its own and returns a handle; zkb_me_open_end waits for it, writes
+ * the 3 k + 1 proof elements and the opening, and releases the handle (call it exactly once per handle, also after
+ * an error elsewhere).  d_t and d_gens must stay as they are until then; h_u is read during begin only.  Up to four
+ * openings per device run side by side with whatever the caller queues meanwhile; a further begin runs its opening at
+ * once and end only hands over the results. */
+int zkb_me_open_begin(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k, void* stream,
+                      void** handle);
+int zkb_me_open_end(void* handle, zkb_g1_t* h_proof, zkb_fr_t* h_out);
 
 /* ---- multi-GPU: one process per GPU (no counterpart in the reference, which is single-GPU) ----
  * The process's communicator is an NCCL communicator on the device that is current when

@@ -309,10 +309,14 @@ int zkb_malloc(void** d_ptr, size_t bytes) {
     ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     return ZKB_OK;
 }
-int zkb_free(void* d_ptr) {
+static int free_after(void* d_ptr, bool whole_device);
+int zkb_free(void* d_ptr) { return free_after(d_ptr, true); }
+int zkb_free_default_stream(void* d_ptr) { return free_after(d_ptr, false); }
+static int free_after(void* d_ptr, bool whole_device) {
     if (!d_ptr) return ZKB_OK;
     AllocClock clock(2);
-    ZKB_CUDA(cudaDeviceSynchronize());
+    if (whole_device) ZKB_CUDA(cudaDeviceSynchronize());
+    else ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
     size_t guarded = 0;
     {
         std::lock_guard<std::mutex> lk(g_guard_mu);

@@ -1149,17 +1149,19 @@ int zkb_commit(const zkb_g1_t* d_gens, size_t n_gen, const zkb_fr_t* d_scalars, 
                           reinterpret_cast<G1Jac*>(d_out), scratch, s);
 }
 
-int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
-                zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
-    ZKB_API_RANGE();
-    cudaStream_t s = as_stream(stream);
-    if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
-    if (k > 62) return fail(ZKB_ERR_LIMIT, "Commitment::me_open - more than 62 rounds");
-    SideStream* side = side_stream();
-    if (!side) return ZKB_ERR_CUDA;
-    std::lock_guard<std::mutex> turn(side->busy);
-    Scratch keep(s);
-    Drain drain{side->st};   // destroyed before `keep`: nothing of the side stream outlives the buffers
+}  // extern "C"
+
+// What has to outlive the enqueueing of an opening: host arrays the copies read, and where the results are.
+struct OpenState {
+    std::vector<zkb_fr_t> coef, um;
+    G1Jac* d_proof = nullptr;      // 3 k + 1 proof elements
+    const Fr* cs = nullptr;        // the fully folded scalar
+};
+
+// Queues one opening on `s` (generator chain) and side->st (the MSMs); on return `s` has taken the side stream's
+// work back, and st says where the results will be.  Reads h_u only while it runs.
+static int me_open_enqueue(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
+                           cudaStream_t s, SideStream* side, Scratch& keep, OpenState& st) {
     // The chain that cannot be shortened is generators -> affine -> folded
     // generators, round after round, on the caller's stream.  The three-row MSM of
     // a round only reads that round's affine generators and scalar rows, so it runs
@@ -1203,7 +1205,7 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
         big_points = keep.get_n<G1Jac>(big_rows);
         if (!big_buckets || !big_points) return ZKB_ERR_CUDA;
     }
-    std::vector<zkb_fr_t> coef;                  // host copy of the combination scalars, alive until the last synchronisation
+    std::vector<zkb_fr_t>& coef = st.coef;       // host copy of the combination scalars, alive until the last synchronisation
     unsigned r = 0;
     size_t rows_done = 0;
     for (; r < n_big && rc == ZKB_OK; ++r) {
@@ -1292,7 +1294,8 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // the remaining K rounds and the final generator as one MSM over this round's generators
     const unsigned K = k - r;
     if (rc == ZKB_OK && K > 0) {
-        std::vector<zkb_fr_t> um(K);
+        std::vector<zkb_fr_t>& um = st.um;
+        um.assign(K, zkb_fr_t());
         for (unsigned t = 0; t < K; ++t) um[t] = hfr::store(hfr::to_mont(hfr::load(h_u[r + t])));
         Fr* d_um = keep.get_n<Fr>(K);
         Fr* S = keep.get_n<Fr>(((size_t)K + 1) * cur);
@@ -1310,15 +1313,156 @@ int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb
     // the caller's stream takes the side stream's work back before anything is read or released
     ZKB_CUDA(cudaEventRecord(side->join, side->st));
     ZKB_CUDA(cudaStreamWaitEvent(s, side->join, 0));
+    if (rc != ZKB_OK) return rc;
+    if (K == 0) ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k, cg, sizeof(G1Jac), cudaMemcpyDeviceToDevice, s));
+    st.d_proof = d_proof;
+    st.cs = cs;
+    return ZKB_OK;
+}
+
+// ---- openings in flight: zkb_me_open_begin / zkb_me_open_end -------------------------------
+// An opening is bound by the multiplier, a lookup proof by memory, and an opening's small rounds by latency: a caller
+// that starts an opening, goes on with other proofs and collects the result later overlaps all three.  Each opening in
+// flight has its own pair of non-blocking streams (a lane), its scratch memory bound to that lane, and a page-locked
+// block for the results; at most kOpenLanes per device, a further begin runs the opening at once instead.
+static constexpr int kOpenLanes = 4;
+struct OpenLane {
+    bool made = false, busy = false;
+    cudaStream_t a = nullptr;
+    SideStream side;
+    cudaEvent_t ready = nullptr;
+    char* pinned = nullptr;        // (3 * 62 + 1) proof elements and the opening
+};
+static constexpr size_t kOpenPinned = (3 * 62 + 1) * sizeof(G1Jac) + 32;
+struct OpenJob {
+    OpenLane* lane = nullptr;      // nullptr: the opening ran inside begin, results are in `done_*`
+    Scratch keep;
+    OpenState st;
+    unsigned k = 0;
+    std::vector<zkb_g1_t> done_proof;
+    zkb_fr_t done_out;
+    explicit OpenJob(cudaStream_t s) : keep(s) {}
+};
+static std::mutex g_lane_mu;
+static OpenLane g_lanes[64][kOpenLanes];
+
+static OpenLane* take_lane() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_lane_mu);
+    for (int i = 0; i < kOpenLanes; ++i) {
+        OpenLane& l = g_lanes[dev][i];
+        if (l.busy) continue;
+        if (!l.made) {
+            void* p = nullptr;
+            if (cudaStreamCreateWithFlags(&l.a, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaStreamCreateWithFlags(&l.side.st, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&l.side.fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&l.side.join, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&l.ready, cudaEventDisableTiming) != cudaSuccess ||
+                cudaHostAlloc(&p, kOpenPinned, cudaHostAllocDefault) != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+            l.pinned = static_cast<char*>(p);
+            l.made = true;
+        }
+        l.busy = true;
+        return &l;
+    }
+    return nullptr;
+}
+static void release_lane(OpenLane* l) {
+    std::lock_guard<std::mutex> lk(g_lane_mu);
+    l->busy = false;
+}
+
+extern "C" {
+
+int zkb_me_open(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k,
+                zkb_g1_t* h_proof, zkb_fr_t* h_out, void* stream) {
+    ZKB_API_RANGE();
+    cudaStream_t s = as_stream(stream);
+    if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
+    if (k > 62) return fail(ZKB_ERR_LIMIT, "Commitment::me_open - more than 62 rounds");
+    SideStream* side = side_stream();
+    if (!side) return ZKB_ERR_CUDA;
+    std::lock_guard<std::mutex> turn(side->busy);
+    Scratch keep(s);
+    Drain drain{side->st};   // destroyed before `keep`: nothing of the side stream outlives the buffers
+    OpenState st;
+    const int rc = me_open_enqueue(d_t, d_gens, n, h_u, k, s, side, keep, st);
     if (rc != ZKB_OK) {
         cudaStreamSynchronize(s);
         return rc;
     }
-    if (K == 0) ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * k, cg, sizeof(G1Jac), cudaMemcpyDeviceToDevice, s));
-    ZKB_CUDA(cudaMemcpyAsync(h_proof, d_proof, (3 * (size_t)k + 1) * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
-    ZKB_CUDA(cudaMemcpyAsync(h_out, cs, 32, cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_proof, st.d_proof, (3 * (size_t)k + 1) * sizeof(G1Jac), cudaMemcpyDeviceToHost, s));
+    ZKB_CUDA(cudaMemcpyAsync(h_out, st.cs, 32, cudaMemcpyDeviceToHost, s));
     ZKB_CUDA(cudaStreamSynchronize(s));
     return ZKB_OK;
+}
+
+int zkb_me_open_begin(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n, const zkb_fr_t* h_u, unsigned k, void* stream,
+                      void** handle) {
+    ZKB_API_RANGE();
+    if (!handle) return fail(ZKB_ERR_ARG, "me_open_begin: null handle");
+    *handle = nullptr;
+    if (n == 0) return fail(ZKB_ERR_DIM, "Commitment::me_open - Incompatible dimensions");
+    if (k > 62) return fail(ZKB_ERR_LIMIT, "Commitment::me_open - more than 62 rounds");
+    OpenLane* lane = take_lane();
+    if (!lane) {                    // every lane is in use: the opening runs now
+        OpenJob* job = new OpenJob(as_stream(stream));
+        job->k = k;
+        job->done_proof.resize(3 * (size_t)k + 1);
+        const int rc = zkb_me_open(d_t, d_gens, n, h_u, k, job->done_proof.data(), &job->done_out, stream);
+        if (rc != ZKB_OK) { delete job; return rc; }
+        *handle = job;
+        return ZKB_OK;
+    }
+    OpenJob* job = new OpenJob(lane->a);
+    job->lane = lane;
+    job->k = k;
+    int rc = ZKB_OK;
+    if (cudaEventRecord(lane->ready, as_stream(stream)) != cudaSuccess || cudaStreamWaitEvent(lane->a, lane->ready, 0) != cudaSuccess)
+        rc = fail(ZKB_ERR_CUDA, "me_open_begin: cannot order the opening after the caller's stream");
+    if (rc == ZKB_OK) rc = me_open_enqueue(d_t, d_gens, n, h_u, k, lane->a, &lane->side, job->keep, job->st);
+    if (rc == ZKB_OK) {
+        const size_t pb = (3 * (size_t)k + 1) * sizeof(G1Jac);
+        if (cudaMemcpyAsync(lane->pinned, job->st.d_proof, pb, cudaMemcpyDeviceToHost, lane->a) != cudaSuccess ||
+            cudaMemcpyAsync(lane->pinned + pb, job->st.cs, 32, cudaMemcpyDeviceToHost, lane->a) != cudaSuccess)
+            rc = fail(ZKB_ERR_CUDA, "me_open_begin: cannot queue the result copies");
+    }
+    if (rc != ZKB_OK) {
+        cudaStreamSynchronize(lane->side.st);
+        cudaStreamSynchronize(lane->a);
+        delete job;
+        release_lane(lane);
+        return rc;
+    }
+    *handle = job;
+    return ZKB_OK;
+}
+
+int zkb_me_open_end(void* handle, zkb_g1_t* h_proof, zkb_fr_t* h_out) {
+    if (!handle) return fail(ZKB_ERR_ARG, "me_open_end: null handle");
+    OpenJob* job = static_cast<OpenJob*>(handle);
+    const size_t pb = (3 * (size_t)job->k + 1) * sizeof(G1Jac);
+    int rc = ZKB_OK;
+    if (!job->lane) {
+        if (h_proof) memcpy(h_proof, job->done_proof.data(), pb);
+        if (h_out) *h_out = job->done_out;
+    } else {
+        const cudaError_t e1 = cudaStreamSynchronize(job->lane->a), e2 = cudaStreamSynchronize(job->lane->side.st);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) rc = cuda_fail(e1 != cudaSuccess ? e1 : e2, "me_open_end");
+        else {
+            if (h_proof) memcpy(h_proof, job->lane->pinned, pb);
+            if (h_out) memcpy(h_out, job->lane->pinned + pb, 32);
+        }
+    }
+    OpenLane* lane = job->lane;
+    delete job;                      // the scratch memory goes back in the lane's stream order
+    if (lane) release_lane(lane);
+    return rc;
 }
 
 }  // extern "C"

@@ -163,7 +163,9 @@ int run_rmsnorm(const Args& a) {
     proof(cost_sumcheck(Y.size),
           [&] { hadamard_product_sumcheck(g_rms_, X, random_vec(ceilLog2(Y.size)), random_vec(ceilLog2(Y.size))); });
     proof(cost_lookup(g_rms.size), [&] { rs_gain.prove(g_rms, g_rms_); });
-    proof(cost_weight_claim(embed), [&] { verifyWeightClaim(weight, gain.prove(rms_inv, g_rms)[0]); });
+    zkllm::WeightOpenings openings;
+    proof(cost_weight_claim(embed), [&] { openings.add(weight, gain.prove(rms_inv, g_rms)[0]); });
+    openings.finish();
     (void)seq;
     return 0;
 }
@@ -185,11 +187,12 @@ int run_self_attn(const Args& a) {
         scaled[0].save_int("temp_Q.bin");
         scaled[1].save_int("temp_K.bin");
         scaled[2].save_int("temp_V.bin");
-        for (int i = 0; i < 3; ++i) proof(cost_lookup(raw[i].size), [&] { layers[i]->rs.prove(raw[i], scaled[i]); });
-        // the reference opens k first, then q, then v
+        // the openings are started first (the reference opens k, then q, then v) and run beside the lookups
+        zkllm::WeightOpenings openings;
         for (int i : {1, 0, 2})
-            proof(cost_weight_claim((size_t)embed * embed),
-                  [&] { verifyWeightClaim(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]); });
+            proof(cost_weight_claim((size_t)embed * embed), [&] { openings.add(layers[i]->w, layers[i]->fc.prove(input, raw[i])[0]); });
+        for (int i = 0; i < 3; ++i) proof(cost_lookup(raw[i].size), [&] { layers[i]->rs.prove(raw[i], scaled[i]); });
+        openings.finish();
         for (auto* l : layers) delete l;
         cout << "QKV linear proof successfully verified!" << endl;
         return 0;
@@ -271,14 +274,14 @@ int run_ffn(const Args& a) {
     clk.mark("save");
 
     const size_t n_weights = (size_t)embed * hidden;
+    // the three matmul proofs first: their openings then run beside the lookups below
+    zkllm::WeightOpenings openings;
+    proof(cost_weight_claim(n_weights), [&] { openings.add(up.w, up.fc.prove(input, up_out)[0]); });
+    proof(cost_weight_claim(n_weights), [&] { openings.add(gate.w, gate.fc.prove(input, gate_out)[0]); });
+    proof(cost_weight_claim(n_weights), [&] { openings.add(down.w, down.fc.prove(down_in_, down_out)[0]); });
+    clk.mark("fc proofs, openings started");
     proof(cost_lookup(down_out.size), [&] { down.rs.prove(down_out, down_out_); });
     clk.mark("down rescale prove");
-    proof(cost_weight_claim(n_weights), [&] {
-        auto down_claim = down.fc.prove(down_in_, down_out)[0];
-        clk.mark("down fc prove");
-        verifyWeightClaim(down.w, down_claim);
-    });
-    clk.mark("down opening");
     proof(cost_lookup(down_in.size), [&] { hidden_rescale.prove(down_in, down_in_); });
     clk.mark("hidden rescale prove");
     proof(cost_lookup(gate_out_.size), [&] {
@@ -288,11 +291,10 @@ int run_ffn(const Args& a) {
     clk.mark("swiglu prove");
     proof(cost_lookup(gate_out.size), [&] { gate.rs.prove(gate_out, gate_out_); });
     clk.mark("gate rescale prove");
-    proof(cost_weight_claim(n_weights), [&] { verifyWeightClaim(gate.w, gate.fc.prove(input, gate_out)[0]); });
-    clk.mark("gate fc prove + opening");
     proof(cost_lookup(up_out.size), [&] { up.rs.prove(up_out, up_out_); });
-    proof(cost_weight_claim(n_weights), [&] { verifyWeightClaim(up.w, up.fc.prove(input, up_out)[0]); });
-    clk.mark("up rescale + fc prove + opening");
+    clk.mark("up rescale prove");
+    openings.finish();
+    clk.mark("openings finished");
     return 0;
 }
 

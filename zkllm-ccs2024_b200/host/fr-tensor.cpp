@@ -128,7 +128,7 @@ static void upload_and_convert(Fr_t* dst, const T* cpu, uint n, F convert) {
     int rc = zkb_memcpy_h2d(tmp, cpu, sizeof(T) * (size_t)n, nullptr);
     if (rc == ZKB_OK) rc = convert(static_cast<const T*>(tmp), dst);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
-    zkb_free(tmp);
+    zkb_free_default_stream(tmp);
     check(rc);
 }
 
@@ -159,7 +159,7 @@ FrTensor::FrTensor(const string& filename) : gpu_data(nullptr), size(findsize(fi
 }
 
 FrTensor::~FrTensor() {
-    zkb_free(gpu_data);
+    zkb_free_default_stream(gpu_data);
     gpu_data = nullptr;
 }
 
@@ -178,7 +178,7 @@ FrTensor FrTensor::from_int_bin(const string& filename) {
     loadbin(filename, tmp, sizeof(int) * n);
     int rc = zkb_fr_from_i32(static_cast<const int32_t*>(tmp), out.gpu_data, n, nullptr);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
-    zkb_free(tmp);
+    zkb_free_default_stream(tmp);
     check(rc);
     return out;
 }
@@ -191,7 +191,7 @@ FrTensor FrTensor::from_long_bin(const string& filename) {
     loadbin(filename, tmp, sizeof(long) * n);
     int rc = zkb_fr_from_i64(static_cast<const int64_t*>(tmp), out.gpu_data, n, nullptr);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
-    zkb_free(tmp);
+    zkb_free_default_stream(tmp);
     check(rc);
     return out;
 }
@@ -204,7 +204,7 @@ void FrTensor::save_int(const string& filename) const {
     int rc = zkb_fr_to_i32(gpu_data, static_cast<int32_t*>(tmp), size, nullptr);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
     if (rc == ZKB_OK) savebin(filename, tmp, sizeof(int) * size);
-    zkb_free(tmp);
+    zkb_free_default_stream(tmp);
     check(rc);
 }
 
@@ -214,7 +214,7 @@ void FrTensor::save_long(const string& filename) const {
     int rc = zkb_fr_to_i64(gpu_data, static_cast<int64_t*>(tmp), size, nullptr);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
     if (rc == ZKB_OK) savebin(filename, tmp, sizeof(long) * size);
-    zkb_free(tmp);
+    zkb_free_default_stream(tmp);
     check(rc);
 }
 

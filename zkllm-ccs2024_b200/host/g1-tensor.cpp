@@ -56,7 +56,7 @@ G1TensorAffine::G1TensorAffine(const string& filename) : G1Tensor(findsize(filen
     loadbin(filename, gpu_data, sizeof(G1Affine_t) * size);
 }
 G1TensorAffine::~G1TensorAffine() {
-    zkb_free(gpu_data);
+    zkb_free_default_stream(gpu_data);
     gpu_data = nullptr;
 }
 void G1TensorAffine::save(const string& filename) const { savebin(filename, gpu_data, sizeof(G1Affine_t) * size); }
@@ -97,7 +97,7 @@ G1TensorJacobian::G1TensorJacobian(const string& filename) : G1Tensor(findsize(f
     loadbin(filename, gpu_data, sizeof(G1Jacobian_t) * size);
 }
 G1TensorJacobian::~G1TensorJacobian() {
-    zkb_free(gpu_data);
+    zkb_free_default_stream(gpu_data);
     gpu_data = nullptr;
 }
 void G1TensorJacobian::save(const string& filename) const { savebin(filename, gpu_data, sizeof(G1Jacobian_t) * size); }

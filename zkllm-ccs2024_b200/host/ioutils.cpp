@@ -68,7 +68,7 @@ struct ResidentFiles {
     void drop(const string& name) {
         auto it = files.find(name);
         if (it == files.end()) return;
-        zkb_free(it->second.dev);
+        zkb_free_default_stream(it->second.dev);
         used -= it->second.bytes;
         lru.erase(it->second.age);
         files.erase(it);
@@ -83,7 +83,7 @@ struct ResidentFiles {
         while (used + bytes > limit && !lru.empty()) drop(lru.back());
         void* p = nullptr;
         if (zkb_malloc(&p, bytes) != ZKB_OK) return;          // no room: simply not cached
-        if (zkb_memcpy_d2d(p, d_src, bytes, nullptr) != ZKB_OK || zkb_sync(nullptr) != ZKB_OK) { zkb_free(p); return; }
+        if (zkb_memcpy_d2d(p, d_src, bytes, nullptr) != ZKB_OK || zkb_sync(nullptr) != ZKB_OK) { zkb_free_default_stream(p); return; }
         lru.push_front(name);
         Resident r;
         r.id = id; r.dev = p; r.bytes = bytes; r.age = lru.begin();

@@ -16,6 +16,68 @@ void verifyWeightClaim(const Weight& w, const Claim& c) {
     cout << "Opening complete" << endl;
 }
 
+// ---- openings in flight (zkllm_ext.hpp) ----------------------------------------------------
+struct zkllm::WeightOpenings::Pending {
+    void* handle = nullptr;
+    FrTensor* row = nullptr;          // the weights folded by the high challenges: input of the opening in flight
+    Fr_t expected;
+    size_t rounds = 0;
+};
+zkllm::WeightOpenings::WeightOpenings() {}
+zkllm::WeightOpenings::~WeightOpenings() {
+    for (Pending* p : pending_) {
+        if (p->handle) zkb_me_open_end(p->handle, nullptr, nullptr);
+        delete p->row;
+        delete p;
+    }
+}
+void zkllm::WeightOpenings::add(const Weight& w, const Claim& c) {
+    // verifyWeightClaim and Commitment::open up to the call of me_open
+    const vector<Fr_t> u_cat = concatenate(vector<vector<Fr_t>>({c.u[1], c.u[0]}));
+    auto w_padded = w.weight.pad({w.in_dim, w.out_dim});
+    const uint k_out = ceilLog2(w.com.size);
+    if (u_cat.size() < k_out) throw std::runtime_error("Commitment::open - not enough challenges");
+    const vector<Fr_t> u_out(u_cat.end() - k_out, u_cat.end());
+    const vector<Fr_t> u_in(u_cat.begin(), u_cat.end() - k_out);
+    Pending* p = new Pending;
+    pending_.push_back(p);
+    p->expected = c.claim;
+    p->rounds = u_in.size();
+    p->row = u_out.empty() ? new FrTensor(w_padded) : new FrTensor(w_padded.partial_me(u_out, w_padded.size / w.com.size));
+    if (p->row->size != w.generator.size)
+        throw std::runtime_error("Commitment::me_open - Incompatible dimensions " + std::to_string(p->row->size) + " " +
+                                 std::to_string(w.generator.size));
+    static const Fr_t dummy = {{0, 0, 0, 0, 0, 0, 0, 0}};
+    zkllm::check(zkb_me_open_begin(p->row->gpu_data, w.generator.gpu_data, p->row->size, u_in.empty() ? &dummy : u_in.data(),
+                                   (unsigned)u_in.size(), nullptr, &p->handle));
+}
+void zkllm::WeightOpenings::finish() {
+    std::vector<Pending*> todo;
+    todo.swap(pending_);
+    std::string failure;
+    for (Pending* p : todo) {
+        vector<G1Jacobian_t> elems(3 * p->rounds + 1);
+        Fr_t opening;
+        const int rc = p->handle ? zkb_me_open_end(p->handle, elems.data(), &opening) : ZKB_ERR_ARG;
+        p->handle = nullptr;
+        if (rc != ZKB_OK && failure.empty()) failure = zkb_last_error();
+        if (rc == ZKB_OK) {
+            if (auto* sink = zkllm::transcript_sink()) {
+                zkllm::Transcript::Entry e;
+                e.label = "me_open";
+                e.points = elems;
+                e.scalars.push_back(opening);
+                sink->entries.push_back(e);
+            }
+            if (opening != p->expected) { if (failure.empty()) failure = "verifyWeightClaim: opening != c.claim"; }
+            else cout << "Opening complete" << endl;
+        }
+        delete p->row;
+        delete p;
+    }
+    if (!failure.empty()) throw std::runtime_error(failure);
+}
+
 bool operator==(const Fr_t& a, const Fr_t& b) {
     for (int i = 0; i < 8; ++i)
         if (a.val[i] != b.val[i]) return false;

@@ -15,7 +15,7 @@ struct DevU32 {   // scoped device array of uint
         check(zkb_malloc(&q, sizeof(uint) * n));
         p = static_cast<uint*>(q);
     }
-    ~DevU32() { zkb_free(p); }
+    ~DevU32() { zkb_free_default_stream(p); }
 };
 const Fr_t kZero = {{0, 0, 0, 0, 0, 0, 0, 0}};
 }  // namespace

@@ -7,6 +7,9 @@
 
 #include "../../include/zkllm_b200.h"
 
+struct Weight;   // commitment.cuh
+struct Claim;    // proof.cuh
+
 namespace zkllm {
 
 // random_vec() draws from std::random_device like the reference
@@ -47,6 +50,24 @@ ResidentStats resident_stats();
 // answers a line.
 void set_deferred_saves(bool on);
 void flush_saves();
+
+// verifyWeightClaim (proof.cuh) in two halves: add() starts the opening of a weight commitment at a claim's point and
+// returns; finish() waits for every opening started, compares each with its claim (throwing the reference's
+// "verifyWeightClaim: opening != c.claim") and prints the reference's "Opening complete" line per opening.  Between the
+// two the caller goes on proving: an opening keeps the multipliers busy, a lookup proof the memory.  The Weight must
+// outlive finish(); the destructor waits without checking (use finish()).
+class WeightOpenings {
+public:
+    WeightOpenings();
+    ~WeightOpenings();
+    WeightOpenings(const WeightOpenings&) = delete;
+    WeightOpenings& operator=(const WeightOpenings&) = delete;
+    void add(const ::Weight& w, const ::Claim& c);
+    void finish();
+private:
+    struct Pending;
+    std::vector<Pending*> pending_;
+};
 
 // Throws std::runtime_error(msg) when a C-ABI call failed; dimension and
 // verifier failures carry the reference's message text.

@@ -54,7 +54,7 @@ FrTensor zkSoftmax::compute(const FrTensor& X, FrTensor& shift, FrTensor& X_shif
     Fr_t* digits = static_cast<Fr_t*>(raw);
     int rc = zkb_softmax_decompose(X_shifted.gpu_data, bs.data(), K, digits, N, nullptr);
     if (rc == ZKB_OK) rc = zkb_sync(nullptr);
-    if (rc != ZKB_OK) { zkb_free(raw); check(rc); }
+    if (rc != ZKB_OK) { zkb_free_default_stream(raw); check(rc); }
 
     FrTensor out(N);
     try {
@@ -74,10 +74,10 @@ FrTensor zkSoftmax::compute(const FrTensor& X, FrTensor& shift, FrTensor& X_shif
             }
         }
     } catch (...) {
-        zkb_free(raw);
+        zkb_free_default_stream(raw);
         throw;
     }
-    zkb_free(raw);
+    zkb_free_default_stream(raw);
     return out;
 }
 
