@@ -78,6 +78,15 @@ int zkb_free_default_stream(void* d_ptr);
  * which calls cudaMalloc / cudaFree per tensor, fr-tensor.cu:158-179).  zkb_pool_trim waits for the device and
  * returns cached memory to the driver down to keep_bytes. */
 int zkb_pool_trim(size_t keep_bytes);
+/* Streams (no counterpart in the reference, which works on the default stream only).  zkb_stream_create makes a
+ * non-blocking stream of the highest (or lowest) priority the device offers.  zkb_set_default_stream names the stream
+ * that a null `stream` argument stands for from then on, in every entry point and in zkb_malloc / zkb_free_default_stream
+ * (null again: the CUDA default stream).  A host that starts openings with zkb_me_open_begin and keeps proving can give
+ * its own work a high-priority stream this way: its short kernels are then scheduled ahead of the openings' long blocks.
+ * The setting is process-wide; change it only while nothing is in flight. */
+int zkb_stream_create(int high_priority, void** stream);
+int zkb_stream_destroy(void* stream);
+int zkb_set_default_stream(void* stream);
 /* Guard bands around every block the library hands out (debug aid, no counterpart in the reference; also switched on
  * by ZKLLM_GUARD=1 in the environment): 256 bytes of a fixed pattern before and after each scratch block and each
  * zkb_malloc buffer allocated while it is on, compared with the pattern when the block is released.

@@ -15,6 +15,7 @@ namespace zkb {
 
 static thread_local std::string g_last_error;
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<cudaStream_t> g_default_stream{nullptr};
 
 void set_error(const std::string& msg) { g_last_error = msg; }
 
@@ -299,14 +300,14 @@ int zkb_malloc(void** d_ptr, size_t bytes) {
     if (!bytes) bytes = 16;
     if (guard_on()) {
         void* base = nullptr;
-        ZKB_CUDA(pool_alloc(&base, guard_round(bytes) + 2 * kGuardBytes, (cudaStream_t)0));
-        *d_ptr = guard_arm(base, bytes, (cudaStream_t)0);
+        ZKB_CUDA(pool_alloc(&base, guard_round(bytes) + 2 * kGuardBytes, as_stream(nullptr)));
+        *d_ptr = guard_arm(base, bytes, as_stream(nullptr));
         std::lock_guard<std::mutex> lk(g_guard_mu);
         g_guarded[*d_ptr] = bytes;
     } else {
-        ZKB_CUDA(pool_alloc(d_ptr, bytes, (cudaStream_t)0));
+        ZKB_CUDA(pool_alloc(d_ptr, bytes, as_stream(nullptr)));
     }
-    ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
+    ZKB_CUDA(cudaStreamSynchronize(as_stream(nullptr)));
     return ZKB_OK;
 }
 static int free_after(void* d_ptr, bool whole_device);
@@ -316,7 +317,7 @@ static int free_after(void* d_ptr, bool whole_device) {
     if (!d_ptr) return ZKB_OK;
     AllocClock clock(2);
     if (whole_device) ZKB_CUDA(cudaDeviceSynchronize());
-    else ZKB_CUDA(cudaStreamSynchronize((cudaStream_t)0));
+    else ZKB_CUDA(cudaStreamSynchronize(as_stream(nullptr)));
     size_t guarded = 0;
     {
         std::lock_guard<std::mutex> lk(g_guard_mu);
@@ -325,11 +326,30 @@ static int free_after(void* d_ptr, bool whole_device) {
     }
     if (guarded) {
         void* base = static_cast<char*>(d_ptr) - kGuardBytes;
-        guard_verify(base, guarded, (cudaStream_t)0);
-        ZKB_CUDA(cudaFreeAsync(base, (cudaStream_t)0));
+        guard_verify(base, guarded, as_stream(nullptr));
+        ZKB_CUDA(cudaFreeAsync(base, as_stream(nullptr)));
         return ZKB_OK;
     }
-    ZKB_CUDA(cudaFreeAsync(d_ptr, (cudaStream_t)0));
+    ZKB_CUDA(cudaFreeAsync(d_ptr, as_stream(nullptr)));
+    return ZKB_OK;
+}
+int zkb_set_default_stream(void* stream) {
+    g_default_stream.store(reinterpret_cast<cudaStream_t>(stream));
+    return ZKB_OK;
+}
+int zkb_stream_create(int high_priority, void** stream) {
+    if (!stream) return fail(ZKB_ERR_ARG, "zkb_stream_create: null out pointer");
+    int least = 0, greatest = 0;
+    ZKB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    cudaStream_t st = nullptr;
+    ZKB_CUDA(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, high_priority ? greatest : least));
+    *stream = st;
+    return ZKB_OK;
+}
+int zkb_stream_destroy(void* stream) {
+    if (!stream) return ZKB_OK;
+    if (g_default_stream.load() == reinterpret_cast<cudaStream_t>(stream)) g_default_stream.store(nullptr);
+    ZKB_CUDA(cudaStreamDestroy(reinterpret_cast<cudaStream_t>(stream)));
     return ZKB_OK;
 }
 int zkb_guard_enable(int on) {

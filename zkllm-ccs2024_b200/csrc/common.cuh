@@ -63,7 +63,13 @@ struct ApiRange {
 };
 #define ZKB_API_RANGE() ::zkb::ApiRange api_range__(__func__)
 
-inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+// A null stream argument of the C ABI means the CUDA default stream, unless the host named a stream of its own for
+// that role (zkb_set_default_stream): e.g. a high-priority stream, so that its short kernels are scheduled ahead of
+// the long-running blocks of openings in flight on the library's own streams.
+extern std::atomic<cudaStream_t> g_default_stream;
+inline cudaStream_t as_stream(void* s) {
+    return s ? reinterpret_cast<cudaStream_t>(s) : g_default_stream.load(std::memory_order_relaxed);
+}
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

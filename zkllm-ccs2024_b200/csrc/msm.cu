@@ -1187,6 +1187,48 @@ static int me_open_enqueue(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n
     ZKB_TRY(generators_have_order_r(reinterpret_cast<const G1Jac*>(d_gens), n, &order_r, keep, s));
     unsigned n_big = 0;
     for (size_t c = n; n_big < k && (c > kTailLen || !order_r); c = (c + 1) / 2) ++n_big;
+    // The two small host arrays of an opening (combination scalars of the derived T rows, Montgomery forms of the
+    // tail's challenges) depend on h_u only.  They go to the device NOW, while both streams are still empty: a copy
+    // from pageable host memory waits for the work queued before it, which later on would be most of the opening.
+    std::vector<zkb_fr_t>& coef = st.coef;
+    Fr* d_coef = nullptr;
+    if (n_big > 1 && order_r) {
+        // coefficient of every point of big_points[0 .. 2 n_big - 1) in T of round t = 1 .. n_big - 1
+        const size_t n_pts = 2 * (size_t)n_big - 1, n_der = n_big - 1;
+        std::vector<hfr::H> a(n_big), b(n_big), c(n_big);
+        for (unsigned i = 0; i < n_big; ++i) {
+            hfr::H u = hfr::load(h_u[i]);
+            for (int pass = 0; pass < 2; ++pass)      // a raw value of r or more names the same multiple as its residue
+                if (hfr::geq(u, hfr::kMod)) { uint64_t bo; u = hfr::raw_sub(u, hfr::kMod, &bo); }
+            const hfr::H v = hfr::sub(hfr::from_u64(1), u);
+            a[i] = hfr::mul(u, v);
+            b[i] = hfr::mul(v, v);
+            c[i] = hfr::mul(u, u);
+        }
+        coef.assign(n_der * n_pts, hfr::store(hfr::zero()));
+        for (unsigned t = 1; t < n_big; ++t) {
+            zkb_fr_t* row = &coef[(size_t)(t - 1) * n_pts];
+            hfr::H run = hfr::from_u64(1);            // product of a_i for i in (j, t)
+            for (int j = (int)t - 1; j >= 0; --j) {
+                row[1 + 2 * (size_t)j] = hfr::store(hfr::mul(b[j], run));
+                row[2 + 2 * (size_t)j] = hfr::store(hfr::mul(c[j], run));
+                run = hfr::mul(run, a[j]);
+            }
+            row[0] = hfr::store(run);
+        }
+        d_coef = keep.get_n<Fr>(coef.size());
+        if (!d_coef) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemcpyAsync(d_coef, coef.data(), coef.size() * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    }
+    std::vector<zkb_fr_t>& um = st.um;
+    Fr* d_um = nullptr;
+    if (k > n_big) {
+        um.assign(k - n_big, zkb_fr_t());
+        for (unsigned t = 0; t < k - n_big; ++t) um[t] = hfr::store(hfr::to_mont(hfr::load(h_u[n_big + t])));
+        d_um = keep.get_n<Fr>(k - n_big);
+        if (!d_um) return ZKB_ERR_CUDA;
+        ZKB_CUDA(cudaMemcpyAsync(d_um, um.data(), (k - n_big) * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    }
     // Only the first big round forms T = sum s_i g_i by an MSM.  With a = u (1 - u), b = (1 - u)^2, c = u^2 of a
     // round, the next round's T is  a T + b T0 + c T1  (expand sum s'_j g'_j with the two folds above), so
     // every later T is a fixed combination of the first T and the T0, T1 of the rounds before it: rounds
@@ -1205,7 +1247,6 @@ static int me_open_enqueue(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n
         big_points = keep.get_n<G1Jac>(big_rows);
         if (!big_buckets || !big_points) return ZKB_ERR_CUDA;
     }
-    std::vector<zkb_fr_t>& coef = st.coef;       // host copy of the combination scalars, alive until the last synchronisation
     unsigned r = 0;
     size_t rows_done = 0;
     for (; r < n_big && rc == ZKB_OK; ++r) {
@@ -1255,34 +1296,10 @@ static int me_open_enqueue(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n
             ZKB_CUDA(cudaMemcpyAsync(d_proof + 3 * (size_t)t + 1, big_points + 3 + 2 * (size_t)(t - 1), 2 * sizeof(G1Jac),
                                      cudaMemcpyDeviceToDevice, side->st));
         if (rc == ZKB_OK && n_big > 1 && order_r) {
-            // coefficient of every point of big_points[0 .. 2 n_big - 1) in T of round t = 1 .. n_big - 1
+            // the derived T rows: one small MSM over the proof points so far, with the scalars copied at the start
             const size_t n_pts = 2 * (size_t)n_big - 1, n_der = n_big - 1;
-            std::vector<hfr::H> a(n_big), b(n_big), c(n_big);
-            for (unsigned i = 0; i < n_big; ++i) {
-                hfr::H u = hfr::load(h_u[i]);
-                for (int pass = 0; pass < 2; ++pass)      // a raw value of r or more names the same multiple as its residue
-                    if (hfr::geq(u, hfr::kMod)) { uint64_t bo; u = hfr::raw_sub(u, hfr::kMod, &bo); }
-                const hfr::H v = hfr::sub(hfr::from_u64(1), u);
-                a[i] = hfr::mul(u, v);
-                b[i] = hfr::mul(v, v);
-                c[i] = hfr::mul(u, u);
-            }
-            coef.assign(n_der * n_pts, hfr::store(hfr::zero()));
-            for (unsigned t = 1; t < n_big; ++t) {
-                zkb_fr_t* row = &coef[(size_t)(t - 1) * n_pts];
-                hfr::H run = hfr::from_u64(1);            // product of a_i for i in (j, t)
-                for (int j = (int)t - 1; j >= 0; --j) {
-                    row[1 + 2 * (size_t)j] = hfr::store(hfr::mul(b[j], run));
-                    row[2 + 2 * (size_t)j] = hfr::store(hfr::mul(c[j], run));
-                    run = hfr::mul(run, a[j]);
-                }
-                row[0] = hfr::store(run);
-            }
-            // everything of this step lives on the side stream, after its reduction
-            Fr* d_coef = fin.get_n<Fr>(coef.size());
             G1Jac* d_der = fin.get_n<G1Jac>(n_der);
-            if (!d_coef || !d_der) return ZKB_ERR_CUDA;
-            ZKB_CUDA(cudaMemcpyAsync(d_coef, coef.data(), coef.size() * sizeof(Fr), cudaMemcpyHostToDevice, side->st));
+            if (!d_der) return ZKB_ERR_CUDA;
             G1Aff* pts_aff = fin.get_n<G1Aff>(n_pts);
             if (!pts_aff) return ZKB_ERR_CUDA;
             rc = to_affine_device(big_points, pts_aff, n_pts, side->st);
@@ -1294,16 +1311,11 @@ static int me_open_enqueue(const zkb_fr_t* d_t, const zkb_g1_t* d_gens, size_t n
     // the remaining K rounds and the final generator as one MSM over this round's generators
     const unsigned K = k - r;
     if (rc == ZKB_OK && K > 0) {
-        std::vector<zkb_fr_t>& um = st.um;
-        um.assign(K, zkb_fr_t());
-        for (unsigned t = 0; t < K; ++t) um[t] = hfr::store(hfr::to_mont(hfr::load(h_u[r + t])));
-        Fr* d_um = keep.get_n<Fr>(K);
         Fr* S = keep.get_n<Fr>(((size_t)K + 1) * cur);
         Fr* Wt = keep.get_n<Fr>(((size_t)K + 1) * cur);
         Fr* tail_rows = keep.get_n<Fr>((3 * (size_t)K + 1) * cur);
         G1Aff* bases_t = bases + used;
         if (!d_um || !S || !Wt || !tail_rows) return ZKB_ERR_CUDA;
-        ZKB_CUDA(cudaMemcpyAsync(d_um, um.data(), K * sizeof(Fr), cudaMemcpyHostToDevice, s));
         ZKB_LAUNCH(me_open_tail_prep_kernel, 1, 1024, 0, s, cs, cur, d_um, K, S, Wt);
         ZKB_LAUNCH(me_open_tail_rows_kernel, grid_for((3 * (size_t)K + 1) * cur, 128), 128, 0, s, S, Wt, cur, K, tail_rows);
         ZKB_TRY(to_affine_device(cg, bases_t, cur, s));

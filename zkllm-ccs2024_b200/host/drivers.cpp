@@ -328,6 +328,12 @@ int run_batch(const Args& a) {
     // (every file is still written); ZKLLM_RESIDENT=0 reads every file from disk again, as separate processes do
     const char* res_env = std::getenv("ZKLLM_RESIDENT");
     zkllm::set_resident_files(!(res_env && res_env[0] == '0'));
+    // ZKLLM_PRIORITY_STREAM=1: this process's own work runs on a high-priority stream, so that while openings are in
+    // flight on the library's streams its short kernels are scheduled ahead of the openings' long-running blocks.  Off by
+    // default: the sumchecks then start sooner and the openings end later, and a layer takes the same time.
+    const char* prio_env = std::getenv("ZKLLM_PRIORITY_STREAM");
+    void* work_stream = nullptr;
+    if (prio_env && prio_env[0] == '1' && zkb_stream_create(1, &work_stream) == ZKB_OK) zkb_set_default_stream(work_stream);
     // output files go to the disk from a writer thread while the stage proves; each is complete before its line is answered
     const char* def_env = std::getenv("ZKLLM_DEFERRED_SAVES");
     zkllm::set_deferred_saves(!(def_env && def_env[0] == '0'));
