@@ -208,7 +208,11 @@ __global__ void __launch_bounds__(256) msm_schedule_kernel(const uint16_t* __res
 
 // One warp per (32 lists of similar length, window, bucket).  blockIdx.x
 // enumerates (list group, window, bucket) with the bucket fastest.
-static constexpr unsigned kAccWarps = 4;
+// (CTAs of 2 warps or of 1 warp, with the same number of warps per SM, measured 2 to 4 % slower on the opening)
+#ifndef ZKB_ACC_WARPS
+#define ZKB_ACC_WARPS 4
+#endif
+static constexpr unsigned kAccWarps = ZKB_ACC_WARPS;
 #ifndef ZKB_ACC_MINBLOCKS
 #define ZKB_ACC_MINBLOCKS 3
 #endif
