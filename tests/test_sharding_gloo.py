@@ -188,3 +188,56 @@ def test_cpp_multi_hadamard_combine_matches_the_reference_algorithm():
         with pytest.raises(z.ZkbError) as e:
             z.call("zkb_multi_hadamard_combine", *args(claim + 1))
         assert "multi_hadamard_sumchecks: claim != p(0) + p(1)" in str(e.value)
+
+
+def _layer_split_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import sys
+    import types
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    calls = []
+
+    def fake_layer_workload(impl, modes, seq, embed, hidden, tmpdir=None, log=None, device=None, workdir=None, params_dir=None,
+                            share=None):
+        calls.append({"modes": modes, "workdir": workdir, "params_dir": params_dir, "share": share, "device": device})
+        if not modes:                                   # the parameter set-up of rank 0
+            Path(workdir, "marker").write_text("params")
+            return {}
+        assert Path(params_dir, "marker").read_text() == "params"
+        return {"one resident driver process": {"seconds": 1.0 + share[0], "stages_s": {"ffn": 1.0 + share[0]},
+                                                "passes_s": [2.0, 1.0 + share[0]], "outputs_sha256": "same"}}
+
+    bench.layer_workload = fake_layer_workload
+    args = types.SimpleNamespace(seq=256, embed=256, hidden=512, tmpdir=None, layer_log=None)
+    out = bench.layer_split_over_ranks(dist, rank, world, str(rank), args)
+    q.put((rank, out, calls))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_layer_split_over_two_ranks_host_logic():
+    """bench.layer_split_over_ranks with the driver replaced by a stub: rank 0 sets the parameters up once where both can
+    read them, every rank proves as process r of 2 against that directory, the slowest rank's time is the layer's, the
+    output digests are compared, and the shared directory is gone afterwards."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_layer_split_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {r: (out, calls) for r, out, calls in (q.get(timeout=120) for _ in range(world))}
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(world):
+        out, calls = res[r]
+        assert out["seconds"] == 2.0 and out["seconds_per_gpu"] == [1.0, 2.0]
+        assert out["all_gpus_wrote_the_same_outputs"] is True and out["parity"] is None      # no recorded digest for this shape
+        prove = [c for c in calls if c["modes"]]
+        assert len(prove) == 1 and prove[0]["share"] == (r, world) and prove[0]["device"] == str(r)
+        assert len([c for c in calls if not c["modes"]]) == (1 if r == 0 else 0)
+    shared = res[0][1][0]["workdir"]
+    assert res[1][1][0]["params_dir"] == shared and not os.path.exists(shared)
