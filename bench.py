@@ -624,7 +624,8 @@ def run_ours(args) -> dict:
         try:
             blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=dev_id)
             mine = blk["one resident driver process"]
-            ok = mine["outputs_sha256"] == golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else True
+            gold_sha = layer_gold(args.seq, args.embed, args.hidden)
+            ok = mine["outputs_sha256"] == gold_sha if gold_sha else True
             secs = mine["seconds"]
         except Exception as ex:
             ok, secs = False, float("nan")
@@ -974,13 +975,19 @@ def layer_block(args) -> dict:
         blk = layer_workload("ours", [("batch", 2), ("process", 1)], args.seq, args.embed, args.hidden, args.tmpdir, args.layer_log)
     except Exception as ex:   # the headline line must still print
         return {"impl": "ours", "error": str(ex)[-600:]}
-    gold = golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else None
+    gold = layer_gold(args.seq, args.embed, args.hidden)
     shas = [v["outputs_sha256"] for v in blk.values() if isinstance(v, dict) and "outputs_sha256" in v]
     blk["reference_outputs_sha256"] = gold
     blk["parity"] = (all(x == gold for x in shas) and bool(shas)) if gold else None
     blk["note"] = ("like for like with the reference is 'one process per stage' (every process pays CUDA start-up and reloads "
                    "generators and weights); 'one resident driver process' is what this build adds; seconds are wall time")
     return blk
+
+
+def layer_gold(seq: int, embed: int, hidden: int):
+    """SHA-256 over the layer's integer outputs as the reference's own drivers wrote them for this shape, or None"""
+    key = {(2048, 4096, 11008): "layer_7b_outputs_sha256", (2048, 5120, 13824): "layer_13b_outputs_sha256"}.get((seq, embed, hidden))
+    return golden_fullsize().get(key) if key else None
 
 
 def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
@@ -1014,7 +1021,7 @@ def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
     dist.all_gather_object(per, mine)
     if rank == 0:
         shutil.rmtree(shared[0], ignore_errors=True)
-    gold = golden_fullsize().get("layer_7b_outputs_sha256") if (args.seq, args.embed, args.hidden) == (2048, 4096, 11008) else None
+    gold = layer_gold(args.seq, args.embed, args.hidden)
     ok = all(q["seconds"] is not None for q in per)
     shape = {(4096, 11008): "Llama-2-7B-shape", (5120, 13824): "Llama-2-13B-shape"}.get((args.embed, args.hidden), "decoder")
     return {"workload": f"one {shape} layer (seq {args.seq}) over {world} GPUs: every GPU computes the layer's outputs, each of its "
@@ -1052,8 +1059,13 @@ def run_layer(args) -> dict:
     key = "one resident driver process" if (args.layer_mode == "batch" and args.impl == "ours") else "one process per stage"
     inner = blk.get(key, {})
     shape = blk["workload"].split(" layer")[0]
-    return {"metric": f"{shape} layer prove time", "unit": "s", "value": inner.get("seconds"), "higher_is_better": False,
-            "impl": args.impl, "mode": key, **blk}
+    out = {"metric": f"{shape} layer prove time", "unit": "s", "value": inner.get("seconds"), "higher_is_better": False,
+           "impl": args.impl, "mode": key, **blk}
+    gold = layer_gold(args.seq, args.embed, args.hidden)
+    if gold and args.impl == "ours" and "outputs_sha256" in inner:
+        out["reference_outputs_sha256"] = gold
+        out["parity"] = inner["outputs_sha256"] == gold
+    return out
 
 
 def main():
