@@ -104,6 +104,16 @@ def test_layer_7b_outputs_equal_the_reference_drivers(tmp_path):
     assert got["outputs_sha256"] == gold, got["output_files_sha256_16"]
 
 
+def test_layer_13b_outputs_equal_the_reference_drivers(tmp_path):
+    import bench
+    gold = GOLD.get("layer_13b_outputs_sha256")
+    assert gold, "tests/golden/ref_fullsize.json has no layer_13b_outputs_sha256"
+    blk = bench.layer_workload("ours", [("batch", 1)], 2048, 5120, 13824, str(tmp_path))
+    assert "unavailable" not in blk, blk
+    got = blk["one resident driver process"]
+    assert got["outputs_sha256"] == gold, got["output_files_sha256_16"]
+
+
 def test_layer_7b_proofs_shared_by_two_driver_processes(tmp_path):
     """ZKLLM_PROOF_WORLD=2: both driver processes write the reference's outputs, every proof of the layer is run by
     exactly one of them, and each process reports its share.  (Run one after the other here: they exchange nothing.)"""
