@@ -622,7 +622,7 @@ def run_ours(args) -> dict:
         dist.barrier()
         t0 = time.perf_counter()
         try:
-            blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=dev_id)
+            blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, handoff_dir(args, world), device=dev_id)
             mine = blk["one resident driver process"]
             gold_sha = layer_gold(args.seq, args.embed, args.hidden)
             ok = mine["outputs_sha256"] == gold_sha if gold_sha else True
@@ -639,7 +639,8 @@ def run_ours(args) -> dict:
         layer_replicas = {"workload": f"{world} Llama-2-7B-shape layers, one resident driver process per GPU, at the same time "
                                       "(replicas: one whole layer per GPU)",
                           "layer_seconds_per_gpu": [x[0] for x in per], "layers_per_s": world / worst if worst == worst and worst > 0 else None,
-                          "wall_s_with_setup": max(x[1] for x in per), "all_outputs_equal_the_reference_sha": all(x[2] == 1.0 for x in per)}
+                          "wall_s_with_setup": max(x[1] for x in per), "all_outputs_equal_the_reference_sha": all(x[2] == 1.0 for x in per),
+                          "handoff_files_in": handoff_dir(args, world) or tempfile.gettempdir()}
 
     # ---- ONE layer on several GPUs: every GPU computes the outputs, each proof of the layer runs on one of them ----------
     layer_split = None
@@ -984,6 +985,21 @@ def layer_block(args) -> dict:
     return blk
 
 
+def handoff_dir(args, world: int):
+    """Where the driver processes of a multi-process layer run keep their hand-off files: --tmpdir when given; with more
+    than four processes on one box, shared memory when it has room (at eight, the 2.9 GB of output files per layer that the
+    processes write into one disk directory tree take longer than the proofs)."""
+    if args.tmpdir or world <= 4:
+        return args.tmpdir
+    import shutil
+    try:
+        if shutil.disk_usage("/dev/shm").free > (4 << 30) * world:
+            return "/dev/shm"
+    except OSError:
+        pass
+    return None
+
+
 def layer_gold(seq: int, embed: int, hidden: int):
     """SHA-256 over the layer's integer outputs as the reference's own drivers wrote them for this shape, or None"""
     key = {(2048, 4096, 11008): "layer_7b_outputs_sha256", (2048, 5120, 13824): "layer_13b_outputs_sha256"}.get((seq, embed, hidden))
@@ -996,9 +1012,10 @@ def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
     compute the layer's outputs, each proof is run by one of them; host/drivers.cpp).  Seconds = the slowest rank's second
     pass; every rank's output SHA is compared with the reference's (7B shape) and with rank 0's."""
     import shutil
+    tmpdir = handoff_dir(args, world)
     shared = [None]
     if rank == 0:
-        shared[0] = tempfile.mkdtemp(dir=args.tmpdir, prefix="zkllm-layer-")
+        shared[0] = tempfile.mkdtemp(dir=tmpdir, prefix="zkllm-layer-")
         try:
             layer_workload("ours", [], args.seq, args.embed, args.hidden, device=device, workdir=shared[0])
         except Exception as ex:
@@ -1010,7 +1027,7 @@ def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
         return {"error": "parameter setup failed on rank 0"}
     mine = {"seconds": None, "sha": None, "stages_s": {}, "passes_s": []}
     try:
-        blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, args.tmpdir, device=device,
+        blk = layer_workload("ours", [("batch", 2)], args.seq, args.embed, args.hidden, tmpdir, device=device,
                              params_dir=shared[0], share=(rank, world),
                              log=(f"{args.layer_log}.rank{rank}" if args.layer_log else None))
         got = blk["one resident driver process"]
@@ -1028,6 +1045,7 @@ def layer_split_over_ranks(dist, rank: int, world: int, device, args) -> dict:
                         "proofs (lookups, sumchecks, weight openings) is run by one GPU; no exchange between them",
             "seconds": max(q["seconds"] for q in per) if ok else None,
             "seconds_per_gpu": [q["seconds"] for q in per], "stages_s_rank0": per[0]["stages_s"],
+            "handoff_files_in": tmpdir or tempfile.gettempdir(),
             "outputs_sha256": per[0]["sha"], "all_gpus_wrote_the_same_outputs": ok and len({q["sha"] for q in per}) == 1,
             "reference_outputs_sha256": gold, "parity": (ok and all(q["sha"] == gold for q in per)) if gold else None}
 
