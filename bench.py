@@ -67,7 +67,7 @@ class ClockSampler(threading.Thread):
         self.proc = proc
         for line in proc.stdout:
             if line.strip():
-                self.rows.append([t.strip() for t in line.strip().split(",")])
+                self.rows.append((time.monotonic(), [t.strip() for t in line.strip().split(",")]))
             if self.stop_flag.is_set():
                 break
         proc.terminate()
@@ -79,13 +79,19 @@ class ClockSampler(threading.Thread):
             proc.terminate()      # the process this sampler started, by its own handle
         self.join(timeout=5)
 
-    def summary(self) -> dict:
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+    def summary(self, t0: float = None, t1: float = None) -> dict:
+        """median SM clock and the throttle reasons seen between t0 and t1 (time.monotonic); when the timed region was
+        too short for a sample of its own, the samples of the warm-up steps just before it (the same load) are used"""
+        inside = [r for t, r in self.rows if t0 is None or t0 <= t <= t1]
+        window = "timed region"
+        if not inside:
+            inside, window = [r for t, r in self.rows if t1 is None or t <= t1], "warm-up and timed region"
+        sm = sorted(int(r[0]) for r in inside if r[0].isdigit())
+        mx = [int(r[1]) for r in inside if r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [nm for k, nm in enumerate(names) if any(len(r) > 2 + k and r[2 + k] == "Active" for r in self.rows)]
+        reasons = [nm for k, nm in enumerate(names) if any(len(r) > 2 + k and r[2 + k] == "Active" for r in inside)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
-                "samples": len(self.rows)}
+                "samples": len(inside), "window": window}
 
 
 def ints_to_fr_limbs(v: np.ndarray) -> np.ndarray:
@@ -502,23 +508,25 @@ def run_ours(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    sampler = ClockSampler(local)          # started before the warm-up: nvidia-smi takes a few tenths of a second to come up
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
 
     # ---- device-timed region --------------------------------------------------------------
-    sampler = ClockSampler(local)
-    sampler.start()
     z.call("zkb_profile_reset")
     z.call("zkb_profile_enable", ctypes.c_int(1))
     launches0 = z.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    clock_t0 = time.monotonic()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    clock_t1 = time.monotonic()
     ms_total = e0.elapsed_time(e1)
     launches = z.launch_count() - launches0
     z.call("zkb_profile_enable", ctypes.c_int(0))
@@ -742,7 +750,7 @@ def run_ours(args) -> dict:
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
             "config": cfg, "algorithm": method,
-            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": sampler.summary(clock_t0, clock_t1), "e2e": e2e, "gpu_launches": int(launches),
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "kernel_time_share": shares, "parity_sample_ok": bool(parity and e2e_ok), "commit_sha256": commit_sha,
             "commit_sha256_equals_reference": sha_parity,
