@@ -714,7 +714,7 @@ def run_ours(args) -> dict:
         else:
             windows = 2 if max_abs < 8128 else 3
             additions = m * n * windows
-            fq_per_add, method = FQ_MULS_PER_MIXED_ADD, f"bucket method, {windows} signed 7-bit windows, Jacobian bucket sums"
+            fq_per_add, method = 10, f"bucket method, {windows} signed 7-bit windows, XYZZ bucket sums"
             algo_bytes = m * n * 4 + n * 96 + m * windows * 64 * 144     # scalars + affine bases in, bucket sums out
             traffic = int(m * n * NCU_DRAM_BYTES_PER_POINT)
             traffic_src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one 2048 x 11008 launch (160.7 MB), scaled by "
