@@ -31,7 +31,6 @@ sys.path.insert(0, str(ROOT))
 
 R_MOD = 0x73EDA753299D7D483339D80809A1D80553BDA402FFFE5BFEFFFFFFFF00000001
 SEED = 0x5EED0000 + 2 * 16
-FQ_MULS_PER_MIXED_ADD = 11
 MADS_PER_FQ_MUL = 576          # 4 * 12^2 32-bit multiply-add instructions (product + Montgomery reduction)
 
 
